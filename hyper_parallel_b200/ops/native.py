@@ -1,0 +1,142 @@
+"""ctypes binding to ``libhpb200.so`` (the hand-written sm_100a kernels).
+
+Every launcher is an ``extern "C"`` function taking raw device pointers and a
+CUDA stream; this module turns ``torch.Tensor`` arguments into those.  On a
+machine with a GPU the library MUST be present: a missing or unloadable library
+raises instead of silently falling back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+_status = {}  # device index -> int32[2] tensor written by kernels on bounded-wait expiry
+_sm_count = {}
+
+c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+_SIGNATURES = {
+    "hpb_gemm_bf16": [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int,
+                      c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "hpb_rmsnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                        c_float, c_void_p],
+    "hpb_rmsnorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_void_p, c_int, c_int, c_int64, c_int, c_void_p],
+    "hpb_swiglu_fwd": [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+    "hpb_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
+    "hpb_rope": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
+                 c_void_p],
+    "hpb_cross_entropy": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_float, c_void_p],
+    "hpb_adamw": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
+                  c_float, c_float, c_float, c_int, c_float, c_int, c_void_p],
+}
+
+
+def available() -> bool:
+    """True when the compiled library exists on disk (it may still need a GPU to run)."""
+    return _build.LIB_PATH.exists()
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the native library; raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            path = _build.LIB_PATH
+            if not path.exists():
+                if os.environ.get("HPB_BUILD_ON_IMPORT", "0") == "1":
+                    _build.build()
+                else:
+                    raise RuntimeError(
+                        f"{path} is missing: run `python -m hyper_parallel_b200.ops.build` "
+                        "(the CUDA kernels are required on a GPU machine)")
+            handle = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+            for name, argtypes in _SIGNATURES.items():
+                if hasattr(handle, name):
+                    fn = getattr(handle, name)
+                    fn.argtypes = argtypes
+                    fn.restype = c_int
+            _lib = handle
+    return _lib
+
+
+def bind(name: str, argtypes, restype=c_int):
+    """Declare the signature of an additional exported symbol and return it."""
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def use_native(t: torch.Tensor) -> bool:
+    """Kernels run for CUDA tensors; CPU tensors take the PyTorch reference path."""
+    return t.is_cuda
+
+
+def ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def stream(device=None):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _sm_count[idx] = n
+    return n
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32[2] that kernels write when a bounded wait expires."""
+    idx = torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(2, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+_STATUS_TEXT = {
+    1: "timeout waiting for a TMA stage (full barrier)",
+    2: "timeout waiting for a free smem stage (empty barrier)",
+    3: "timeout waiting for an accumulator (tmem full)",
+    4: "timeout waiting for accumulator drain (tmem empty)",
+    5: "timeout waiting for a peer flag",
+    6: "bad argument seen on device",
+}
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel recorded a bounded-wait expiry."""
+    for idx, t in list(_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code, detail = t.tolist()
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(
+                f"hyper_parallel_b200 kernel error on cuda:{idx}: "
+                f"{_STATUS_TEXT.get(code, code)} (detail={detail})")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")

@@ -1,0 +1,148 @@
+"""Numerics of every hand-written CUDA kernel against a plain PyTorch fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from hyper_parallel_b200 import ops
+from hyper_parallel_b200.ops import functional as Fn
+from hyper_parallel_b200.ops import native
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (200, 264, 136),
+                                   (1024, 4096, 4096)])
+def test_gemm_bf16(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
+    c = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    native.check_status()
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert _rel_err(c, ref) < 5e-3
+    # fp32 output + accumulate
+    c32 = torch.ones((M, N), device=_dev(), dtype=torch.float32)
+    Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c32, accumulate=True)
+    native.check_status()
+    assert _rel_err(c32, ref + 1.0) < 1e-3
+
+
+def test_linear_autograd():
+    torch.manual_seed(1)
+    x = torch.randn(4, 96, 512, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(768, 512, device=_dev(), dtype=torch.bfloat16) * 0.05).requires_grad_()
+    y = Fn.linear(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 5e-3
+    assert _rel_err(x.grad, xr.grad) < 5e-3
+    assert _rel_err(w.grad, wr.grad) < 5e-3
+
+
+@pytest.mark.parametrize("H", [512, 4096, 5120, 7168])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(H, with_res):
+    torch.manual_seed(2)
+    T = 300
+    x = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=_dev())).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16)
+    dh = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16)
+    if with_res:
+        y, h = Fn.add_rmsnorm(x, r, w, 1e-5)
+        (y.float() * dy.float()).sum().add((h.float() * dh.float()).sum()).backward()
+    else:
+        y = Fn.rmsnorm(x, w, 1e-5)
+        (y.float() * dy.float()).sum().backward()
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = xr + rr if with_res else xr
+    if with_res:
+        hr = hr.to(torch.bfloat16).float() + (hr - hr.detach())  # kernel normalises the rounded sum
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    loss = (yr * dy.float()).sum()
+    if with_res:
+        loss = loss + (hr * dh.float()).sum()
+    loss.backward()
+    assert _rel_err(y, yr) < 5e-3
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    if with_res:
+        assert _rel_err(r.grad, rr.grad) < 1e-2
+
+
+def test_swiglu():
+    torch.manual_seed(3)
+    gu = torch.randn(257, 2 * 1024, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    d = torch.randn(257, 1024, device=_dev(), dtype=torch.bfloat16)
+    out = Fn.swiglu(gu)
+    out.backward(d)
+    gr = gu.detach().float().requires_grad_()
+    g, u = gr.chunk(2, -1)
+    ref = torch.nn.functional.silu(g) * u
+    ref.backward(d.float())
+    assert _rel_err(out, ref) < 5e-3
+    assert _rel_err(gu.grad, gr.grad) < 5e-3
+
+
+def test_rope_roundtrip_and_reference():
+    torch.manual_seed(4)
+    T, NH, D, S = 256, 8, 128, 64
+    x = torch.randn(T, NH, D, device=_dev(), dtype=torch.bfloat16)
+    ref = Fn._rope_ref(x.cpu(), S, 500000.0)
+    y = x.clone()
+    Fn.rope_(y, S, 500000.0)
+    assert _rel_err(y.cpu(), ref) < 5e-3
+    Fn.rope_(y, S, 500000.0, inverse=True)
+    assert _rel_err(y, x) < 1e-2
+
+
+@pytest.mark.parametrize("V", [1000, 32000, 128256])
+def test_cross_entropy(V):
+    torch.manual_seed(5)
+    T = 64
+    logits = (torch.randn(T, V, device=_dev()) * 2).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device=_dev())
+    tgt[3] = -100
+    lr = logits.float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(lr, tgt, ignore_index=-100, reduction="sum") / T
+    ref.backward()
+    work = logits.clone().requires_grad_()
+    buf = work.detach().clone()
+    loss = Fn.cross_entropy_fwd_bwd(buf, tgt, 1.0 / T)
+    assert abs(loss.sum().item() / T - ref.item()) < 2e-3 * abs(ref.item())
+    assert _rel_err(buf, lr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("grad_dtype", [torch.bfloat16, torch.float32])
+def test_adamw(grad_dtype):
+    torch.manual_seed(6)
+    n = 1_000_003
+    master = torch.randn(n, device=_dev())
+    p = master.to(torch.bfloat16)
+    m = torch.zeros(n, device=_dev())
+    v = torch.zeros(n, device=_dev())
+    ref_p = master.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        g = torch.randn(n, device=_dev()).to(grad_dtype)
+        ref_p.grad = g.float()
+        opt.step()
+        Fn.adamw_step_(p, master, m, v, g, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8,
+                       weight_decay=0.1, step=step)
+    assert torch.allclose(master, ref_p.detach(), rtol=1e-5, atol=1e-6)
+    assert torch.equal(p, master.to(torch.bfloat16))
