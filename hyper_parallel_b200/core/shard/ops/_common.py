@@ -1,0 +1,63 @@
+"""Helpers shared by the layout rules."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+from ...layout import Layout
+
+
+def norm_dim(dim: int, ndim: int) -> int:
+    d = dim + ndim if dim < 0 else dim
+    if not 0 <= d < max(ndim, 1):
+        raise IndexError(f"dim {dim} out of range for a {ndim}-D tensor")
+    return d
+
+
+def norm_dims(dims, ndim: int) -> List[int]:
+    if dims is None:
+        return list(range(ndim))
+    if isinstance(dims, int):
+        dims = [dims]
+    return sorted({norm_dim(int(d), ndim) for d in dims})
+
+
+def make(like: Layout, dim_axes, partial=None) -> Layout:
+    """New layout on the mesh of ``like``."""
+    return Layout._make(like.mesh, dim_axes, partial)
+
+
+def keep_partial(like: Layout) -> List[Optional[str]]:
+    return list(like.partial)
+
+
+def no_partial(like: Layout) -> List[Optional[str]]:
+    return [None] * like.mesh.ndim
+
+
+def split_shapes(extra_args) -> Tuple[list, Optional[list]]:
+    """Separate the trailing input-shape list (``WithShape`` convention) from the scalars."""
+    if extra_args and isinstance(extra_args[-1], list) and all(
+            s is None or isinstance(s, tuple) for s in extra_args[-1]):
+        return list(extra_args[:-1]), extra_args[-1]
+    return list(extra_args), None
+
+
+def require_unsharded(op_name: str, layout: Layout, dims: Sequence[int], what: str = "operating") -> None:
+    for d in dims:
+        if layout.dim_axes[d]:
+            names = [layout.alias_name[a] for a in layout.dim_axes[d]]
+            raise ValueError(f"For {op_name}, the {what} dim {d} must not be sharded, "
+                             f"but it is sharded on mesh axes {names}")
+
+
+def merge_partials(op_name: str, layouts: Sequence[Optional[Layout]]) -> List[Optional[str]]:
+    """All partial inputs must agree per mesh axis."""
+    ref = None
+    for lay in layouts:
+        if lay is None:
+            continue
+        if ref is None:
+            ref = list(lay.partial)
+        elif list(lay.partial) != ref:
+            raise ValueError(f"For {op_name}, inputs have different Partial status: {ref} vs {lay.partial}")
+    return ref or []
