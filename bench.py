@@ -1,0 +1,204 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3-8B training tokens/s with hsdp full shard (level3) on N B200.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Prints ONE JSON line from rank 0.  ``value`` is total tokens/s over all GPUs, timed on the
+device with CUDA events (max over ranks) with inputs resident on the device; ``e2e`` is the
+same metric through the public API with the per-step host->device copy of the token batch
+from pinned memory and a device->host read of the loss inside the timed region.
+``--impl reference`` runs the unmodified reference package installed under baseline/_ref.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3_8b", choices=["llama3_8b", "llama2_13b", "tiny"])
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--batch-per-gpu", type=int, default=2)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
+    return ap.parse_args()
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+def model_config(args):
+    from hyper_parallel_b200.models.llama import LlamaConfig
+    cfg = {"llama3_8b": LlamaConfig.llama3_8b, "llama2_13b": LlamaConfig.llama2_13b,
+           "tiny": LlamaConfig.tiny}[args.model]()
+    if args.layers is not None:
+        cfg.num_layers = args.layers
+    return cfg
+
+
+def make_batches(cfg, args, rank, n):
+    g = torch.Generator().manual_seed(0 + rank)
+    toks = torch.randint(0, cfg.vocab_size, (n, args.batch_per_gpu, args.seq_len + 1), generator=g,
+                         dtype=torch.int64)
+    return toks.pin_memory()
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200.models.llama import Llama
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.optim import FusedAdamW
+    from hyper_parallel_b200.utils.clocks import ClockSampler
+
+    rank, local, world = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = model_config(args)
+
+    # public API: build on meta, shard with hsdp (full shard, level3), deferred init
+    model = Llama(cfg, device="meta")
+    for layer in model.layers:
+        hp.hsdp(layer, shard_size=world, optimizer_level="level3", comm_fusion=world > 1,
+                comm_async=world > 1)
+    hp.hsdp(model, shard_size=world, optimizer_level="level3", comm_async=world > 1)
+    for i, layer in enumerate(model.layers):
+        if i + 1 < len(model.layers):
+            layer.set_forward_prefetch_cells([model.layers[i + 1]])
+        if i > 0:
+            layer.set_backward_prefetch_cells([model.layers[i - 1]])
+    hp.init_parameters(model, device=dev, seed=0)
+    opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opt.init_state()
+    if world == 1:
+        opt.fuse_into_backward(model)
+
+    n_total = args.warmup + args.steps
+    host = make_batches(cfg, args, rank, n_total)
+    tokens_per_step = world * args.batch_per_gpu * args.seq_len
+
+    def step(tok_dev):
+        inp, tgt = tok_dev[:, :-1], tok_dev[:, 1:]
+        model.zero_grads()
+        loss = model(inp, tgt)
+        loss.backward()
+        hp.hsdp_sync_stream()
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # ---- device-timed loop (inputs resident) --------------------------------
+    dev_batches = host.to(dev)
+    for i in range(args.warmup):
+        step(dev_batches[i])
+    native.check_status()
+    barrier()
+    launches0 = native.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for i in range(args.steps):
+            loss = step(dev_batches[args.warmup + i])
+        ev1.record()
+        barrier()
+    launches = native.launch_count - launches0
+    ms = max_over_ranks(ev0.elapsed_time(ev1))
+    native.check_status()
+    last_loss = loss.item()
+
+    # ---- end-to-end loop: H2D of the batch and D2H of the loss every step ----
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h2d = host[0].numel() * host.element_size()
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        tok = host[args.warmup + i].to(dev, non_blocking=True)
+        loss = step(tok)
+        _ = loss.item()
+    e1.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
+
+    ms_per_step = ms / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+    e2e_value = tokens_per_step / (e2e_ms / args.steps / 1e3)
+    flops = cfg.flops_per_token(args.seq_len) * tokens_per_step / world
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak_tflops = peaks.get("bf16_tflops_sustained", 1400.0)
+    mfu = flops / (ms_per_step / 1e3) / (peak_tflops * 1e12)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "train tokens/sec (device-timed, max over ranks)", "value": value,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform token ids, seed 0; random-init N(0,0.02) weights)",
+            "impl": "ours",
+            "config": {"model": args.model, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
+                       "global_batch": world * args.batch_per_gpu, "seq_len": args.seq_len,
+                       "parallelism": f"hsdp level3 full shard x{world}",
+                       "optimizer": "AdamW, fp32 master/m/v",
+                       "l2": "no flush needed: each step streams >100 GB of weights/activations, far above the 126 MB L2"},
+            "mfu_of_measured_sustained_bf16": mfu, "loss": last_loss,
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        try:
+            from reference_arm import run_reference
+        except Exception as e:  # noqa: BLE001
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"reference harness failed to import: {e}"}))
+            return
+        run_reference(args)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -36,6 +36,7 @@ class HSDPParam:
         self.prefetch_handle = None
         self._unsharded_persistent: Optional[torch.Tensor] = None
         self.grad_ready = False
+        self.grad_consumer = None   # optional callable(hp, reduced_grad) run as soon as the grad exists
         self._init_rank_space()
         self._init_shard_size()
         self._init_groups()

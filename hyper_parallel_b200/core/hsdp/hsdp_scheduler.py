@@ -134,6 +134,10 @@ class HSDPScheduler:
             pending = self.hsdp_state.reduce_grad(hp, grad)
             if pending is not None:
                 _PENDING.append(pending)
+            elif hp.reduced_grad is not None and hp.grad_consumer is not None:
+                # e.g. the optimizer fused into backward: use the shard gradient now, then drop it
+                g, hp.reduced_grad = hp.reduced_grad, None
+                hp.grad_consumer(hp, g)
         return hook
 
     @staticmethod

@@ -76,8 +76,11 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.wgrad_into = wgrad_into
-        y = gemm(x2, w)
-        return y.view(*x.shape[:-1], w.shape[0])
+        # allocate with the final shape: the result must not be a view created inside the Function
+        # (callers may update it in place, e.g. RoPE on the fused QKV buffer)
+        y = torch.empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16, device=x.device)
+        gemm(x2, w, out=y.view(-1, w.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):

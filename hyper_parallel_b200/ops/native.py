@@ -137,6 +137,11 @@ def check_status(device=None) -> None:
                 f"{_STATUS_TEXT.get(code, code)} (detail={detail})")
 
 
+launch_count = 0   # number of native launcher calls made by this process
+
+
 def check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")

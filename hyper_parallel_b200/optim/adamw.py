@@ -1,0 +1,118 @@
+"""AdamW with fp32 master weights on (sharded) bf16 parameters, one fused kernel per tensor.
+
+The reference has no optimizer of its own (its tests use ``torch.optim.SGD``); this one
+exists because the headline configuration trains bf16 weights with fp32 master states.
+State per parameter shard: fp32 master copy, ``exp_avg``, ``exp_avg_sq``.
+
+``fuse_into_backward(model)`` makes HSDP hand each reduced gradient shard to the optimizer
+the moment it is ready, so the update overlaps the rest of backward and the gradient is
+freed immediately; ``step()`` then only finishes the parameters that were not handled and
+advances the step counter.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, Optional
+
+import torch
+
+from ..core.dtensor import DTensor
+from ..ops import functional as Fn
+
+
+def _leaf(p: torch.Tensor) -> torch.Tensor:
+    return p._local_tensor if isinstance(p, DTensor) else p
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 1e-2, master_weights: bool = True):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self.master_weights = master_weights
+        self._step_count = 0
+        self._done_in_backward = set()
+        self._group_of: Dict[int, dict] = {}
+        for g in self.param_groups:
+            for p in g["params"]:
+                self._group_of[id(p)] = g
+
+    # -------------------------------------------------------------- state --
+    def _state_for(self, p) -> dict:
+        st = self.state[p]
+        if not st:
+            data = _leaf(p).data
+            keep_master = self.master_weights and data.dtype != torch.float32
+            st["master"] = data.detach().float().clone() if keep_master else None
+            st["exp_avg"] = torch.zeros(data.shape, dtype=torch.float32, device=data.device)
+            st["exp_avg_sq"] = torch.zeros(data.shape, dtype=torch.float32, device=data.device)
+        return st
+
+    def init_state(self) -> None:
+        """Allocate all optimizer state now (instead of lazily on the first step)."""
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.requires_grad:
+                    self._state_for(p)
+
+    def _update(self, p, grad: torch.Tensor, step: int) -> None:
+        g = self._group_of[id(p)]
+        st = self._state_for(p)
+        data = _leaf(p).data
+        grad = grad.reshape(data.shape)
+        if not grad.is_contiguous():
+            grad = grad.contiguous()
+        master = st["master"]
+        if master is None:
+            # fp32 parameters: the parameter itself is the master copy
+            if data.is_cuda:
+                Fn.adamw_step_(None, data.view(-1), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1),
+                               grad.view(-1), lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1],
+                               eps=g["eps"], weight_decay=g["weight_decay"], step=step)
+            else:
+                Fn.adamw_step_(None, data.view(-1), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1),
+                               grad.reshape(-1), lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1],
+                               eps=g["eps"], weight_decay=g["weight_decay"], step=step)
+            return
+        Fn.adamw_step_(data.view(-1), master.view(-1), st["exp_avg"].view(-1), st["exp_avg_sq"].view(-1),
+                       grad.view(-1) if grad.is_contiguous() else grad.reshape(-1),
+                       lr=g["lr"], beta1=g["betas"][0], beta2=g["betas"][1], eps=g["eps"],
+                       weight_decay=g["weight_decay"], step=step)
+
+    # ------------------------------------------------------- backward fusion --
+    def fuse_into_backward(self, model: torch.nn.Module) -> None:
+        """Consume each HSDP-reduced gradient as soon as it exists (update overlaps backward)."""
+        for p in model.parameters():
+            hp = getattr(p, "_hsdp_param", None)
+            if hp is not None and id(p) in self._group_of:
+                hp.grad_consumer = self._consume
+
+    def _consume(self, hp, grad: torch.Tensor) -> None:
+        p = hp.param
+        self._update(p, grad, self._step_count + 1)
+        self._done_in_backward.add(id(p))
+
+    # ------------------------------------------------------------------ step --
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        self._step_count += 1
+        for g in self.param_groups:
+            for p in g["params"]:
+                if id(p) in self._done_in_backward:
+                    continue
+                grad = _leaf(p).grad
+                if grad is None:
+                    continue
+                self._update(p, grad, self._step_count)
+        self._done_in_backward.clear()
+        return loss
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for g in self.param_groups:
+            for p in g["params"]:
+                lf = _leaf(p)
+                if lf.grad is not None:
+                    if set_to_none:
+                        lf.grad = None
+                    else:
+                        lf.grad.zero_()

@@ -72,7 +72,7 @@ def test_rmsnorm(H, with_res):
     xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
     hr = xr + rr if with_res else xr
     if with_res:
-        hr = hr.to(torch.bfloat16).float() + (hr - hr.detach())  # kernel normalises the rounded sum
+        hr = hr.detach().to(torch.bfloat16).float() + (hr - hr.detach())  # kernel normalises the rounded sum
     yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     loss = (yr * dy.float()).sum()
     if with_res:
