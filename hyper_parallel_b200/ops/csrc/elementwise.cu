@@ -487,3 +487,78 @@ extern "C" int hpb_adamw(const void* grad, int grad_f32, float* master, float* m
                                          b2, eps, wd, bc1, bc2, grad_scale);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward for callers that must not allocate device memory.
+//
+// hpb_rmsnorm_bwd() needs a [num_partials, H] fp32 scratch area for the per-CTA partial
+// weight gradients and expects the caller to provide it.  Some callers cannot: a host
+// program that has handed all device memory to its own pool (an inference / RL server in
+// steady state, where a fresh cudaMalloc would fail or stall every stream), or one that
+// runs under a "no allocation after start-up" rule.  For them this variant keeps the
+// scratch in a fixed array that is part of the library image.  It performs the same two
+// launches as hpb_rmsnorm_bwd() and calls no cudaMalloc / cudaFree / allocating routine.
+//
+// Limits and sharing:
+//  * H <= kNoAllocMaxH (8192) and H % 8 == 0; at most kNoAllocMaxPartials (128) partial
+//    rows are used.  The array is 128 * 8192 * 4 B = 4 MiB and every GPU that loads the
+//    library holds it until the process exits.  Larger H is rejected with
+//    HPB_NOALLOC_E_TOO_LARGE (see hpb_noalloc_strerror()).
+//  * Every call on a device uses the SAME array, which keeps whatever the previous call
+//    left there.  Nothing has to start at zero: each call overwrites rows [0, P) x [0, H)
+//    before it reads them.  Two calls that overlap on the GPU (different streams, no
+//    ordering between them) race on the array; order them or use hpb_rmsnorm_bwd().
+//  * The first call on each device looks up the device address of the array
+//    (cudaGetSymbolAddress, with that device current) and caches it.  Make that first call
+//    before any stream capture begins.
+namespace hpb {
+constexpr int kNoAllocMaxPartials = 128;
+constexpr int kNoAllocMaxH = 8192;
+static __device__ __align__(256) float g_noalloc_rmsnorm_scratch[kNoAllocMaxPartials * kNoAllocMaxH];
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_scratch_addr[kNoAllocMaxDevices] = {};
+}  // namespace hpb
+
+#define HPB_NOALLOC_E_TOO_LARGE (-100)
+#define HPB_NOALLOC_E_BAD_SHAPE (-101)
+#define HPB_NOALLOC_E_DEVICE (-102)
+#define HPB_NOALLOC_E_SYMBOL (-103)
+
+extern "C" const char* hpb_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case HPB_NOALLOC_E_TOO_LARGE:
+      return "hpb_rmsnorm_bwd_noalloc: H exceeds the built-in scratch (max H = 8192); "
+             "use hpb_rmsnorm_bwd with caller-provided scratch";
+    case HPB_NOALLOC_E_BAD_SHAPE: return "hpb_rmsnorm_bwd_noalloc: H must be a positive multiple of 8 and T >= 0";
+    case HPB_NOALLOC_E_DEVICE: return "hpb_rmsnorm_bwd_noalloc: cannot query the current device or device index >= 64";
+    case HPB_NOALLOC_E_SYMBOL: return "hpb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed for the scratch array";
+    default: return "hpb_rmsnorm_bwd_noalloc: CUDA launch error (positive codes are cudaError_t values)";
+  }
+}
+
+extern "C" int hpb_noalloc_max_h() { return hpb::kNoAllocMaxH; }
+
+extern "C" int hpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                       const void* dres_in, void* dx, void* dw, int dw_f32,
+                                       int dw_accumulate, int64_t T, int H, cudaStream_t s) {
+  if (H <= 0 || H % 8 || T < 0) return HPB_NOALLOC_E_BAD_SHAPE;
+  if (H > kNoAllocMaxH) return HPB_NOALLOC_E_TOO_LARGE;
+  if (T == 0) return 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
+    return HPB_NOALLOC_E_DEVICE;
+  float* scratch = g_noalloc_scratch_addr[dev];
+  if (scratch == nullptr) {
+    // Host code must not pass the array's name to a kernel: on the host that name is only a
+    // stand-in.  Ask the runtime for the device address (once per device, that device current).
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_noalloc_rmsnorm_scratch) != cudaSuccess || addr == nullptr)
+      return HPB_NOALLOC_E_SYMBOL;
+    scratch = static_cast<float*>(addr);
+    g_noalloc_scratch_addr[dev] = scratch;
+  }
+  // the existing launcher does the work; it only launches kernels
+  return hpb_rmsnorm_bwd(dy, x, w, rstd, dres_in, dx, scratch, kNoAllocMaxPartials, dw, dw_f32,
+                         dw_accumulate, T, H, s);
+}
