@@ -16,6 +16,9 @@ from .core.shard import (ShardingPlan, custom_shard, parallelize_value_and_grad,
 from .core.shard.ops.parallel_ops import DistributedOp
 from .core.hsdp import HSDPCell, hsdp, hsdp_sync_stream
 from .core.parameter_init import init_parameters
+from .core.pipeline_parallel import (BatchDimSpec, MetaStep, MetaStepType, PipelineStage, Schedule1F1B,
+                                     ScheduleGPipe, ScheduleInterleaved1F1B, SharedParameterInfo,
+                                     validate_pipeline_execution)
 
 __all__ = [
     "get_platform", "hsdp", "hsdp_sync_stream", "HSDPCell", "Layout", "DTensor", "DeviceMesh",
@@ -24,4 +27,6 @@ __all__ = [
     "Shard", "Replicate", "Partial", "Placement", "distribute_tensor", "ones", "zeros", "empty", "full",
     "init_process_group", "destroy_process_group", "get_process_group_ranks", "get_backend",
     "split_group",
+    "MetaStep", "MetaStepType", "BatchDimSpec", "PipelineStage", "SharedParameterInfo",
+    "ScheduleInterleaved1F1B", "Schedule1F1B", "ScheduleGPipe", "validate_pipeline_execution",
 ]
