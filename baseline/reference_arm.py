@@ -233,6 +233,8 @@ def run_reference(args):
         barrier()
         e2e_ms = mx(max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3))
     except Exception as e:  # noqa: BLE001
+        import traceback
+        traceback.print_exc(file=sys.stderr)
         msg = f"reference run failed at N={world}: {type(e).__name__}: {e}"
         try:
             dist.destroy_process_group()

@@ -153,7 +153,7 @@ class _RMSNorm(torch.autograd.Function):
         dy2 = dy.reshape(T, H).contiguous()
         dh2 = dh.reshape(T, H).contiguous() if (ctx.has_res and dh is not None) else None
         dx = torch.empty_like(src)
-        P = min(T, native.sm_count(src.device) * 2)
+        P = min(T, native.sm_count(src.device) * 8)
         part = torch.empty((P, H), dtype=torch.float32, device=src.device)
         dw = torch.empty_like(w)
         rc = native.lib().hpb_rmsnorm_bwd(dy2.data_ptr(), src.data_ptr(), w.data_ptr(), rstd.data_ptr(),
@@ -300,23 +300,31 @@ class _FusedCE(torch.autograd.Function):
     """Mean token cross-entropy whose backward was already computed in the forward kernel."""
 
     @staticmethod
-    def forward(ctx, logits, target, denom):
+    def forward(ctx, logits, target, denom, unit_grad):
         loss = cross_entropy_fwd_bwd(logits, target, 1.0 / denom)
         ctx.save_for_backward(logits)  # now holds dlogits (for grad_out == 1)
+        ctx.unit_grad = unit_grad
         return loss.sum() / denom
 
     @staticmethod
     def backward(ctx, g):
         (dlogits,) = ctx.saved_tensors
-        # g is a scalar tensor; avoid a device sync: multiply only when it is not 1
-        return dlogits * g.to(dlogits.dtype), None, None
+        if ctx.unit_grad:
+            # the caller promised that this loss is what backward() is called on (upstream
+            # gradient 1): the stored dlogits are final and a 2 GB rescale pass is skipped
+            return dlogits, None, None, None
+        return dlogits * g.to(dlogits.dtype), None, None, None
 
 
-def fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor,
-                        denom: Optional[float] = None) -> torch.Tensor:
-    """``sum(CE(logits, target)) / denom``; consumes (overwrites) ``logits``."""
+def fused_cross_entropy(logits: torch.Tensor, target: torch.Tensor, denom: Optional[float] = None,
+                        unit_grad: bool = False) -> torch.Tensor:
+    """``sum(CE(logits, target)) / denom``; consumes (overwrites) ``logits``.
+
+    ``unit_grad=True`` states that ``backward()`` will be called on this very value (upstream
+    gradient exactly 1; scale the loss through ``denom`` instead of multiplying it afterwards).
+    """
     T = logits.shape[0]
-    return _FusedCE.apply(logits, target, float(denom if denom is not None else T))
+    return _FusedCE.apply(logits, target, float(denom if denom is not None else T), unit_grad)
 
 
 # -------------------------------------------------------------------- AdamW --

@@ -1,0 +1,129 @@
+"""Distributed checkpoint: save/load round trips, resharding on load (save on 4 ranks, load on 2),
+on-disk layout, rank-local metadata, offline ReshardHandler, layout json, single-file helpers."""
+import os
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+from dist_utils import run_distributed
+
+
+def _full(name, shape):
+    g = torch.Generator().manual_seed(sum(ord(c) for c in name))
+    return torch.randn(*shape, generator=g)
+
+
+SPECS = {"w_col": ((8, 12), ("None", "tp")), "w_row": ((8, 12), ("tp", "None")), "w_dp": ((8, 12), ("dp", "None")),
+         "w_both": ((8, 12), ("dp", "tp")), "w_rep": ((8, 12), ("None", "None")), "w_multi": ((16, 4), (("dp", "tp"), "None"))}
+
+
+def _state(mesh_shape, plain=True):
+    from hyper_parallel_b200 import Layout, distribute_tensor
+    layout = Layout(mesh_shape, ("dp", "tp"))
+    sd = {}
+    for name, (shape, spec) in SPECS.items():
+        sd[name] = distribute_tensor(_full(name, shape), layout(*spec))
+    if plain:
+        sd["plain"] = _full("plain", (5, 3))
+        sd["nested"] = {"step": 7, "lr": 0.5, "t": _full("nested.t", (4,))}
+    return sd, layout
+
+
+def _save_worker(rank, world, path, mesh_shape, use_collectives):
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    sd, _ = _state(mesh_shape)
+    md = ckpt.save(sd, checkpoint_id=path, use_collectives=use_collectives)
+    assert set(md.state_dict_metadata) >= set(SPECS)
+    if use_collectives and rank == 0:
+        assert md.state_dict_metadata["w_rep"].chunks and len(md.state_dict_metadata["w_rep"].chunks) == 1
+        assert len(md.state_dict_metadata["w_both"].chunks) == world
+
+
+def _load_worker(rank, world, path, mesh_shape):
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    sd, layout = _state(mesh_shape)
+    expect = {k: v.to_local().clone() if hasattr(v, "to_local") else v for k, v in sd.items() if k in SPECS}
+    for k in SPECS:
+        sd[k].to_local().zero_()
+    sd["plain"] = torch.zeros(5, 3)
+    sd["nested"] = {"step": 0, "lr": 0.0, "t": torch.zeros(4)}
+    ckpt.load(sd, checkpoint_id=path)
+    for k in SPECS:
+        assert torch.allclose(sd[k].to_local(), expect[k], atol=1e-5), k
+        assert torch.allclose(sd[k].full_tensor(), _full(k, SPECS[k][0]), atol=1e-5), k
+    assert torch.allclose(sd["plain"], _full("plain", (5, 3)))
+    assert sd["nested"]["step"] == 7 and sd["nested"]["lr"] == 0.5
+    assert torch.allclose(sd["nested"]["t"], _full("nested.t", (4,)))
+
+
+def test_save_4_ranks_layout_on_disk_then_load_4_and_2(tmp_path):
+    path = str(tmp_path / "ckpt")
+    run_distributed(_save_worker, 4, path, (2, 2), True)
+    files = sorted(os.listdir(path))
+    assert ".metadata" in files
+    assert all(f"_rank{r}_.safetensors" in files for r in range(4))
+    assert any(f.endswith(".bytes") and "_rank" in f for f in files)
+    assert not any(f.endswith(".tmp") for f in files)
+    run_distributed(_load_worker, 4, path, (2, 2))
+    run_distributed(_load_worker, 2, path, (1, 2))       # resharding on load
+    run_distributed(_load_worker, 2, path, (2, 1))
+
+
+def test_rank_local_metadata_without_collectives(tmp_path):
+    path = str(tmp_path / "ckpt_local")
+    run_distributed(_save_worker, 2, path, (1, 2), False)
+    files = os.listdir(path)
+    assert ".rank0_metadata" in files and ".rank1_metadata" in files and ".metadata" not in files
+
+
+def test_metadata_pickle_names_reference_modules_and_reads_back(tmp_path):
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    sd = {"a": torch.arange(6.0).reshape(2, 3), "meta": {"epoch": 3}}
+    ckpt.save(sd, checkpoint_id=str(tmp_path), no_dist=True)
+    raw = open(tmp_path / ".metadata", "rb").read()
+    assert b"hyper_parallel.core.checkpoint.metadata" in raw       # readable by the reference
+    out = {"a": torch.zeros(2, 3), "meta": {"epoch": 0}}
+    ckpt.load(out, checkpoint_id=str(tmp_path), no_dist=True)
+    assert torch.equal(out["a"], sd["a"]) and out["meta"]["epoch"] == 3
+    with pytest.raises(KeyError):
+        ckpt.load({"missing": torch.zeros(1)}, checkpoint_id=str(tmp_path), no_dist=True)
+    ckpt.load({"missing": torch.zeros(1)}, checkpoint_id=str(tmp_path), no_dist=True,
+              planner=ckpt.StandardLoadPlanner(allow_partial_load=True))
+
+
+def test_reshard_handler_and_slice_area():
+    from hyper_parallel_b200 import Layout
+    from hyper_parallel_b200.core.checkpoint import ReshardHandler, infer_intersection, infer_slice_area_by_rank
+    full = np.arange(8 * 12, dtype=np.float32).reshape(8, 12)
+    src = Layout((2, 2), ("dp", "tp"), init_backend=False)("dp", "tp")
+    dst = Layout((1, 4), ("dp", "tp"), init_backend=False)("tp", "None")
+    shards = {}
+    for r in range(4):
+        a = infer_slice_area_by_rank(src.mesh_shape, src.tensor_map, r, full.shape)
+        shards[r] = full[tuple(slice(b, e) for b, e in a)]
+    for r in range(4):
+        h = ReshardHandler("w", full.shape, src, dst, r)
+        got = h.get_real_tensor(shards)
+        a = infer_slice_area_by_rank(dst.mesh_shape, dst.tensor_map, r, full.shape)
+        assert np.array_equal(got, full[tuple(slice(b, e) for b, e in a)])
+    assert infer_intersection([(0, 4), (0, 4)], [(4, 8), (0, 4)]) is None
+    with pytest.raises(ValueError):
+        infer_slice_area_by_rank((2, 2), (1, 0), 0, (7, 12))
+
+
+def test_layout_json_and_single_file_helpers(tmp_path):
+    from hyper_parallel_b200 import Layout, distribute_tensor
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    layout = Layout((1, 1), ("dp", "tp"), init_backend=False)
+    lin = torch.nn.Linear(4, 4)
+    lin.weight = torch.nn.Parameter(distribute_tensor(lin.weight.detach(), layout("None", "tp")))
+    cur = ckpt.get_current_layout(lin)
+    assert cur["weight"]["tensor_map"] == [-1, 0] and cur["weight"]["alias_name"] == ["dp", "tp"]
+    ckpt.save_layout(cur, str(tmp_path / "rank0.layout"))
+    assert ckpt.combine_layout(str(tmp_path))["rank0"] == cur
+    ckpt.save_checkpoint({"x": torch.ones(2)}, str(tmp_path / "one.pt"))
+    assert torch.equal(ckpt.load_checkpoint(str(tmp_path / "one.pt"))["x"], torch.ones(2))
+    with pytest.raises(ValueError):
+        ckpt.save_checkpoint({}, str(tmp_path / "bad.txt"))
