@@ -80,7 +80,9 @@ class RefLlama(nn.Module):
         self.final_norm = nn.RMSNorm(c["hidden"], eps=1e-5, dtype=dtype)
         self.lm_head = nn.Linear(c["hidden"], c["vocab"], bias=False, dtype=dtype)
 
-    def forward(self, tokens, targets):
+    def forward(self, anchor, tokens, targets):
+        # `anchor` is an unused float tensor: the reference's forward pre-hook sets
+        # requires_grad on the first positional input, which integer token ids cannot take
         x = self.embed(tokens)
         for layer in self.layers:
             x = layer(x)
@@ -181,8 +183,10 @@ def run_reference(args):
         masters = [p.detach().float().clone().requires_grad_() for p in params]
         opt = torch.optim.AdamW(masters, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
 
+        anchor = torch.zeros(1, device=dev)
+
         def step(tok):
-            loss = model(tok[:, :-1], tok[:, 1:])
+            loss = model(anchor, tok[:, :-1], tok[:, 1:])
             loss.backward(torch.ones_like(loss))
             hsdp_sync_stream()
             for p, m in zip(params, masters):

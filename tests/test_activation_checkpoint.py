@@ -1,0 +1,109 @@
+"""Activation checkpoint / swap: identical losses and gradients with and without it (CPU)."""
+import copy
+
+import torch
+from torch import nn
+
+from hyper_parallel_b200.core.activation_checkpoint import (AsyncSaveOnCpu, CheckpointPolicy, SwapManager,
+                                                            SwapState, SwapTensor, checkpoint,
+                                                            checkpoint_wrapper, swap_wrapper)
+
+
+class Block(nn.Module):
+    def __init__(self, d=32):
+        super().__init__()
+        self.a, self.b = nn.Linear(d, 4 * d), nn.Linear(4 * d, d)
+
+    def forward(self, x):
+        return x + self.b(torch.nn.functional.gelu(self.a(x)))
+
+
+def _run(model, x, steps=3):
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    losses = []
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = model(x).pow(2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    return losses, [p.detach().clone() for p in model.parameters()]
+
+
+def _models(wrap):
+    torch.manual_seed(0)
+    base = nn.Sequential(*[Block() for _ in range(4)])
+    other = copy.deepcopy(base)
+    wrapped = nn.Sequential(*[wrap(b) for b in other])
+    return base, wrapped
+
+
+def _same(a, b):
+    la, pa = a
+    lb, pb = b
+    assert all(abs(x - y) < 1e-6 for x, y in zip(la, lb)), (la, lb)
+    assert all(torch.allclose(x, y, atol=1e-6) for x, y in zip(pa, pb))
+
+
+def test_full_recompute_matches():
+    x = torch.randn(8, 32)
+    base, wrapped = _models(lambda b: checkpoint_wrapper(b))
+    _same(_run(base, x), _run(wrapped, x))
+    assert set(wrapped.state_dict()) == set(base.state_dict())       # wrapper prefix is stripped
+
+
+def test_selective_policy_save_matmul_swap_gelu():
+    calls = {"mm": 0}
+
+    def policy(op, *args, **kwargs):
+        name = str(op)
+        if "addmm" in name or "mm" in name:
+            calls["mm"] += 1
+            return CheckpointPolicy.MUST_SAVE
+        if "gelu" in name:
+            return CheckpointPolicy.MUST_SWAP
+        return CheckpointPolicy.PREFER_RECOMPUTE
+    x = torch.randn(8, 32)
+    base, wrapped = _models(lambda b: checkpoint_wrapper(b, policy_fn=policy))
+    _same(_run(base, x), _run(wrapped, x))
+    assert calls["mm"] > 0
+
+
+def test_swap_inputs_and_functional_checkpoint():
+    torch.manual_seed(1)
+    blk = Block()
+    x = torch.randn(4, 32, requires_grad=True)
+    y1 = blk(x).sum()
+    (g1,) = torch.autograd.grad(y1, x)
+    y2 = checkpoint(blk, x, swap_inputs=True).sum()
+    (g2,) = torch.autograd.grad(y2, x)
+    assert torch.allclose(g1, g2, atol=1e-6) and abs(y1.item() - y2.item()) < 1e-6
+
+
+def test_swap_wrapper_and_manager_prefetch_chain():
+    SwapManager().reset()
+    x = torch.randn(8, 32)
+    base, wrapped = _models(lambda b: swap_wrapper(b, policy_fn=lambda t: t.numel() >= 64))
+    mgr = SwapManager()
+    for a, b in zip(wrapped[:-1], wrapped[1:]):
+        mgr.set_forward_prefetch_layer(a, b)
+    _same(_run(base, x), _run(wrapped, x))
+    assert set(wrapped.state_dict()) == set(base.state_dict())
+
+
+def test_swap_tensor_state_machine():
+    t = torch.arange(2048.0)
+    st = SwapTensor(t)
+    assert st.state == SwapState.DEVICE
+    st.launch_offload()
+    assert st.state == SwapState.D2H
+    st.wait_offload()
+    assert st.state == SwapState.HOST
+    st.launch_load()
+    assert st.state == SwapState.H2D
+    assert torch.equal(st.wait_load(), t) and st.state == SwapState.DEVICE
+    with AsyncSaveOnCpu(min_numel=1):
+        a = torch.randn(64, 64, requires_grad=True)
+        b = (a * a).sum()
+    b.backward()
+    assert torch.allclose(a.grad, 2 * a)
