@@ -171,9 +171,12 @@ def run_reference(args):
         for p in model.parameters():
             if p.dim() > 1:
                 nn.init.normal_(p, 0.0, 0.02)
+        # comm_async=False: with torch 2.11 the reference's asynchronous gradient hook raises
+        # "The size of tensor a (N) must match the size of tensor b (N/2)" in backward for every
+        # optimizer level as soon as a parameter is sharded; its synchronous hook runs.
         for layer in model.layers:
-            hsdp(layer, shard_size=world, optimizer_level="level3", comm_async=True)
-        hsdp(model, shard_size=world, optimizer_level="level3", comm_async=True)
+            hsdp(layer, shard_size=world, optimizer_level="level3", comm_async=False)
+        hsdp(model, shard_size=world, optimizer_level="level3", comm_async=False)
         for i, layer in enumerate(model.layers):
             if i + 1 < len(model.layers):
                 layer.set_forward_prefetch_cells([model.layers[i + 1]])

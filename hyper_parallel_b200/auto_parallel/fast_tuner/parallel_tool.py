@@ -1,0 +1,117 @@
+"""``fast-tuner-parallel``: search (dp, tp, cp, pp, ep, fsdp, vpp, mbs, sp) for a model on a cluster.
+
+Pipeline of hyper_parallel/auto_parallel/fast-tuner/fast_tuner/parallel_tool.py:42-158 of the
+reference: read the trainer/model config -> build the N-D space -> rule pruning -> memory pruning
+(-> stop here with ``--alg_phase 1``) -> profile a handful of shrunk candidates (or, with
+``--dryrun``, use the analytic cost model) -> balance the pipeline of every surviving candidate ->
+write the ranked CSV.
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import os
+import sys
+from typing import List, Optional
+
+from .config import ModelSpec, Strategy, TunerConfig, load_model_spec
+from .cost_model import Hardware, estimate_step_time
+from .memory_model import filter_oom, write_candidate_csv
+from .pipeline_balance import LayerProfile, balance_pipeline
+from .profiling import (ProfileInfo, launch_profile, parse_layer_records, select_profile_candidates,
+                        write_profile_config)
+from .space import (Config, build_initial_spaces, dp_of, ep_of, expert_filter_configs, mbs_of, op_of, pp_of,
+                    sp_of, tp_of, vp_of)
+
+
+def taylor_search_tool(cfg: TunerConfig, spec: Optional[ModelSpec] = None, hw: Optional[Hardware] = None,
+                       top_k: int = 20) -> List[dict]:
+    spec = spec or load_model_spec(cfg)
+    hw = hw or Hardware(gpus_per_node=cfg.gpus_per_node)
+    os.makedirs(cfg.output_path, exist_ok=True)
+    space = build_initial_spaces(spec, cfg.strategy)
+    n0 = len(space)
+    space = expert_filter_configs(space, spec, cfg.gbs)
+    space = [c for c in space if ep_of(c) <= cfg.max_expert_parallel]
+    n1 = len(space)
+    space, rows = filter_oom(space, spec, cfg.max_mem_gib, recompute=cfg.select_recompute)
+    write_candidate_csv(rows, cfg.output_path)
+    summary = {"initial": n0, "after_expert_rules": n1, "after_memory": len(space)}
+    with open(os.path.join(cfg.output_path, "search_summary.json"), "w") as f:
+        json.dump(summary, f)
+    if cfg.alg_phase == 1 or not space:
+        return [{"summary": summary}]
+    # profile (or estimate) ------------------------------------------------------------
+    profile = None
+    if not cfg.dryrun and cfg.trainer_path:
+        for i, cand in enumerate(select_profile_candidates(space, cfg.rank_num)):
+            path = write_profile_config(cand, spec, os.path.join(cfg.output_path, "profile"), i)
+            rc = launch_profile(path, cfg.trainer_path, cfg.rank_num)
+            rec = path.replace(".json", ".records.jsonl")
+            if rc == 0 and os.path.exists(rec):
+                profile = parse_layer_records(rec)
+                break
+    ranked = []
+    scored = sorted(space, key=lambda c: estimate_step_time(spec, c, hw))[: max(top_k * 5, 50)]
+    for c in scored:
+        t = estimate_step_time(spec, c, hw)
+        pp, vp = pp_of(c), vp_of(c)
+        entry = {"dp": dp_of(c), "tp": tp_of(c), "pp": pp, "ep": ep_of(c), "op": op_of(c), "vp": vp,
+                 "mbs": mbs_of(c), "sp": sp_of(c), "step_time_us": t * 1e6}
+        if pp > 1:
+            micro = max(cfg.gbs // (dp_of(c) * mbs_of(c)), 1)
+            lp = profile.to_layer_profile() if profile is not None else LayerProfile(
+                dense_fw=1.0, dense_bw=2.0, moe_fw=1.0 / max(0.3, 1.0), moe_bw=2.0)
+            bal = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp)
+            entry.update({"layers": bal.layers, "offset": bal.offset, "recompute": bal.recompute,
+                          "bubble": round(bal.bubble_ratio, 4)})
+            even = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp, max_offset=0)
+            entry["step_time_us"] = t * 1e6 * bal.makespan / max(even.makespan, 1e-9)
+        ranked.append(entry)
+    ranked.sort(key=lambda e: e["step_time_us"])
+    ranked = ranked[:top_k]
+    out_csv = os.path.join(cfg.output_path, "pipeline_output")
+    os.makedirs(out_csv, exist_ok=True)
+    with open(os.path.join(out_csv, "ranked_configs.csv"), "w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["rank", "dp", "tp", "pp", "ep", "op", "vp", "mbs", "sp", "step_time(us)", "layers", "offset",
+                    "recompute", "bubble"])
+        for i, e in enumerate(ranked):
+            w.writerow([i, e["dp"], e["tp"], e["pp"], e["ep"], e["op"], e["vp"], e["mbs"], e["sp"],
+                        round(e["step_time_us"]), e.get("layers", ""), e.get("offset", ""), e.get("recompute", ""),
+                        e.get("bubble", "")])
+    return ranked
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="fast-tuner-parallel", description=__doc__)
+    ap.add_argument("--config", help="json file with the keys below")
+    ap.add_argument("--toml_path"); ap.add_argument("--yaml_path"); ap.add_argument("--shell_path")
+    ap.add_argument("--model_json")
+    ap.add_argument("--torchtitan_path", "--mindformers_dir", "--mindspeed_path", dest="trainer_path")
+    ap.add_argument("--rank_num", type=int); ap.add_argument("--gbs", type=int)
+    ap.add_argument("--nnodes", type=int); ap.add_argument("--npus_per_node", "--gpus_per_node", dest="gpus_per_node", type=int)
+    ap.add_argument("--output_path")
+    ap.add_argument("--strategy", nargs="*", choices=["DP", "TP", "PP", "EP", "CP", "FSDP"])
+    ap.add_argument("--alg_phase", type=int, choices=[0, 1, 2])
+    ap.add_argument("--max_expert_parallel", type=int)
+    ap.add_argument("--select_recompute", action="store_true")
+    ap.add_argument("--solver_name", default=None)
+    ap.add_argument("--dryrun", action="store_true"); ap.add_argument("--check", action="store_true")
+    ns = ap.parse_args(argv)
+    cfg = TunerConfig.from_json(ns.config) if ns.config else TunerConfig()
+    for k, v in vars(ns).items():
+        if k in ("config", "strategy") or v in (None, False):
+            continue
+        setattr(cfg, k, v)
+    if ns.strategy is not None:
+        cfg.strategy = Strategy(**{k: (k in ns.strategy) for k in ("DP", "TP", "PP", "EP", "CP", "FSDP")})
+    result = taylor_search_tool(cfg)
+    for i, e in enumerate(result[:10]):
+        print(i, e)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,165 @@
+"""Layer-to-stage balancing for pipeline parallelism with two layer types and recomputation.
+
+The reference formulates this as a MILP (OR-Tools -> MPS -> HiGHS,
+hyper_parallel/auto_parallel/fast-tuner/fast_tuner/pipeline_conductor/math_model.py:30-486): integer
+layer counts per (stage, virtual chunk) for dense ("type 1") and MoE ("type 2") layers, dense
+layers occupying a prefix of the (chunk, stage) sequence, a number of fully recomputed layers per
+slot, per-stage memory limits, objective = end of the last backward under a fixed 1F1B / VPP
+order.  Neither solver is installed here, so the same model is solved natively: a bounded
+depth-first search over the layer distribution with the discrete-event simulator as the exact
+objective, pruned by the load lower bound, followed by a greedy choice of the recompute counts
+that makes each stage fit its memory limit at the least extra time.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+from .pp_simulator import compute_order, simulate
+
+
+@dataclass
+class LayerProfile:
+    """Per-layer times (any unit) and memory (MB) of the two layer types."""
+    dense_fw: float = 1.0
+    dense_bw: float = 2.0
+    moe_fw: float = 1.0
+    moe_bw: float = 2.0
+    head_fw: float = 0.0          # output head + loss on the last virtual stage
+    head_bw: float = 0.0
+    embed_fw: float = 0.0         # embedding on the first virtual stage
+    embed_bw: float = 0.0
+    recompute_extra: float = 1.0  # extra backward time of a fully recomputed layer, in units of its forward
+    act_mem: float = 1.0          # activation MB per layer per live micro-batch
+    recomp_mem: float = 0.1       # the same for a fully recomputed layer
+    layer_mem: float = 1.0        # static MB per layer (weights + optimizer)
+    static_mem: float = 0.0       # static MB per stage
+    lm_head_mem: float = 0.0
+
+
+@dataclass
+class BalanceResult:
+    layers: List[List[int]]                # [chunk][stage] total layers
+    dense: List[List[int]]                 # [chunk][stage] dense layers
+    recompute: List[List[int]]             # [chunk][stage] fully recomputed layers
+    makespan: float
+    bubble_ratio: float
+    peak_mem: List[float]
+    offset: List[List[int]] = field(default_factory=list)   # deviation from the even split
+
+
+def _slot_times(dense, moe, rec, prof: LayerProfile, S: int, V: int):
+    fwd, bwd = [], []
+    for v in range(S * V):
+        c, s = divmod(v, S)
+        d, m, r = dense[c][s], moe[c][s], rec[c][s]
+        f = d * prof.dense_fw + m * prof.moe_fw
+        b = d * prof.dense_bw + m * prof.moe_bw
+        total = d + m
+        if total and r:
+            avg_fw = f / total
+            b += r * avg_fw * prof.recompute_extra
+        if v == 0:
+            f += prof.embed_fw
+            b += prof.embed_bw
+        if v == S * V - 1:
+            f += prof.head_fw
+            b += prof.head_bw
+        fwd.append(f)
+        bwd.append(b)
+    return fwd, bwd
+
+
+def _split_types(layers, n_dense: int):
+    """Dense layers fill the (chunk, stage) sequence from the front; the rest is MoE."""
+    dense = [[0] * len(layers[0]) for _ in layers]
+    moe = [[0] * len(layers[0]) for _ in layers]
+    left = n_dense
+    for c in range(len(layers)):
+        for s in range(len(layers[0])):
+            d = min(left, layers[c][s])
+            dense[c][s] = d
+            moe[c][s] = layers[c][s] - d
+            left -= d
+    return dense, moe
+
+
+def balance_pipeline(num_layers: int, num_dense: int, stages: int, chunks: int, micro: int,
+                     prof: LayerProfile, mem_limit_mb: Optional[float] = None, p2p: float = 0.0,
+                     max_offset: int = 2, max_nodes: int = 4000) -> BalanceResult:
+    S, V = stages, chunks
+    slots = S * V
+    kind = "vpp" if V > 1 else "1f1b"
+    order = compute_order(kind, micro, S, V)
+    base, rem = divmod(num_layers, slots)
+    even = [base + (1 if i < rem else 0) for i in range(slots)]
+    best = {"t": float("inf"), "x": None}
+    nodes = [0]
+
+    def evaluate(flat: Sequence[int]):
+        layers = [[flat[c * S + s] for s in range(S)] for c in range(V)]
+        dense, moe = _split_types(layers, num_dense)
+        zero = [[0] * S for _ in range(V)]
+        fwd, bwd = _slot_times(dense, moe, zero, prof, S, V)
+        return simulate(order, fwd, bwd, S, p2p), layers, dense, moe
+
+    avg_layer = ((prof.dense_fw + prof.dense_bw) * num_dense +
+                 (prof.moe_fw + prof.moe_bw) * (num_layers - num_dense)) / max(num_layers, 1)
+
+    def dfs(i: int, flat: List[int], left: int):
+        if nodes[0] >= max_nodes:
+            return
+        if i == slots - 1:
+            if left < 0 or abs(left - even[i]) > max_offset + 1:
+                return
+            cand = flat + [left]
+            nodes[0] += 1
+            res, *_ = evaluate(cand)
+            if res.makespan < best["t"]:
+                best["t"], best["x"] = res.makespan, cand
+            return
+        for delta in sorted(range(-max_offset, max_offset + 1), key=abs):
+            n = even[i] + delta
+            if n < 0 or n > left:
+                continue
+            # lower bound: the most loaded stage cannot finish before its own work
+            stage_load = sum(flat[j] for j in range(len(flat)) if j % S == i % S) + n
+            if stage_load * avg_layer * micro >= best["t"]:
+                continue
+            dfs(i + 1, flat + [n], left - n)
+
+    res0, *_ = evaluate(even)
+    best["t"], best["x"] = res0.makespan, list(even)
+    dfs(0, [], num_layers)
+    res, layers, dense, moe = evaluate(best["x"])
+    rec = [[0] * S for _ in range(V)]
+    peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V)
+    if mem_limit_mb is not None:
+        # greedy: recompute one more layer on the stage that exceeds its limit the most
+        for _ in range(num_layers):
+            over = [(peak_mem[s] - mem_limit_mb, s) for s in range(S) if peak_mem[s] > mem_limit_mb]
+            if not over:
+                break
+            _, s = max(over)
+            cands = [(c, s) for c in range(V) if rec[c][s] < layers[c][s]]
+            if not cands:
+                break
+            c, _ = max(cands, key=lambda cs: layers[cs[0]][cs[1]] - rec[cs[0]][cs[1]])
+            rec[c][s] += 1
+            peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V)
+        fwd, bwd = _slot_times(dense, moe, rec, prof, S, V)
+        res = simulate(order, fwd, bwd, S, p2p)
+    offset = [[layers[c][s] - even[c * S + s] for s in range(S)] for c in range(V)]
+    return BalanceResult(layers, dense, rec, res.makespan, res.bubble_ratio, peak_mem, offset)
+
+
+def _stage_memory(layers, rec, peak_live, prof: LayerProfile, S: int, V: int) -> List[float]:
+    out = []
+    for s in range(S):
+        n = sum(layers[c][s] for c in range(V))
+        r = sum(rec[c][s] for c in range(V))
+        live = max(peak_live[s], 1) / max(V, 1)
+        act = ((n - r) * prof.act_mem + r * prof.recomp_mem) * live
+        static = prof.static_mem + n * prof.layer_mem + (prof.lm_head_mem if s == S - 1 else 0.0)
+        out.append(static + act)
+    return out

@@ -1,0 +1,95 @@
+"""Fast-Tuner: space sizes, rule pruning, memory model, simulator, balancer, CLI dry-run."""
+import json
+import os
+
+import pytest
+
+from hyper_parallel_b200.auto_parallel.fast_tuner import ModelSpec, Strategy, TunerConfig, taylor_search_tool
+from hyper_parallel_b200.auto_parallel.fast_tuner import config as ftc
+from hyper_parallel_b200.auto_parallel.fast_tuner.memory_model import (dense_layer_params, estimate_peak_memory,
+                                                                       filter_oom, grey_box_memory_prune)
+from hyper_parallel_b200.auto_parallel.fast_tuner.pipeline_balance import LayerProfile, balance_pipeline
+from hyper_parallel_b200.auto_parallel.fast_tuner.pp_simulator import compute_order, simulate
+from hyper_parallel_b200.auto_parallel.fast_tuner.space import (build_initial_spaces, expert_filter_configs,
+                                                                factorizations4, pp_of, tp_of)
+
+LLAMA8B = ModelSpec(num_layers=32, hidden_size=4096, ffn_hidden_size=14336, num_attention_heads=32, num_kv_heads=8,
+                    vocab_size=128256, seq_length=4096, world_size=8, global_batch_size=16)
+
+
+def test_space_sizes_and_rules():
+    assert len(factorizations4(8)) == 20            # ordered 4-factorisations of 2^3: C(6,3)
+    space = build_initial_spaces(LLAMA8B)
+    assert len(space) == len({json.dumps(c) for c in space})
+    assert all(c[0][0][0] * c[0][0][1] * c[0][0][2] * c[0][0][3] == 8 for c in space)
+    assert any(c[1] for c in space) and all(tp_of(c) > 1 for c in space if c[1])      # sp only with tp > 1
+    pruned = expert_filter_configs(space, LLAMA8B, 16)
+    assert 0 < len(pruned) < len(space)
+    assert all(c[0][0][2] == 1 for c in pruned)                                         # cp == 1 rule
+    assert all(pp_of(c) <= 16 // c[0][0][0] // c[0][1][3] for c in pruned)              # pp <= gbs/dp/mbs
+    no_pp = build_initial_spaces(LLAMA8B, Strategy(PP=False, CP=False, EP=False))
+    assert all(pp_of(c) == 1 for c in no_pp)
+
+
+def test_memory_model_orders_and_prunes():
+    assert abs(dense_layer_params(LLAMA8B) * 32 / 1e9 - 6.98) < 0.1
+    base = [[(8, 1, 1, 1), (1, 1, 1, 1)], False]          # pure DP: 18 B/param -> ~145 GB > 80
+    fsdp = [[(8, 1, 1, 1), (1, 8, 1, 1)], False]
+    assert estimate_peak_memory(LLAMA8B, base) > estimate_peak_memory(LLAMA8B, fsdp)
+    kept, rows = filter_oom([base, fsdp], LLAMA8B, max_mem_gib=80.0)
+    assert kept == [fsdp] and len(rows) == 1 and len(rows[0]) == 7
+    moe = ModelSpec(expert_num=64, world_size=64)
+    out = grey_box_memory_prune(moe, [[8, 1, 8, 4, 90000], [8, 1, 8, 8, 60000]], [4, 8], 16, max_mem_mib=70000)
+    assert out and all(r[3] <= 16 and r[4] <= 70000 for r in out)
+
+
+def test_simulator_matches_closed_forms():
+    S, M = 4, 8
+    res = simulate(compute_order("1f1b", M, S), [1.0] * S, [2.0] * S, S)
+    assert abs(res.makespan - (M + S - 1) * 3.0) < 1e-9            # classic 1F1B makespan
+    assert res.peak_live[0] == S and res.peak_live[-1] == 1         # in-flight activations
+    g = simulate(compute_order("gpipe", M, S), [1.0] * S, [2.0] * S, S)
+    assert abs(g.makespan - res.makespan) < 1e-9 and g.peak_live[0] == M
+    v = simulate(compute_order("vpp", M, S, 2), [0.5] * (2 * S), [1.0] * (2 * S), S)
+    assert v.makespan < res.makespan                                 # interleaving shrinks the bubble
+    assert 0 < v.bubble_ratio < res.bubble_ratio
+
+
+def test_balancer_moves_layers_off_the_loaded_last_stage():
+    prof = LayerProfile(dense_fw=1.0, dense_bw=2.0, moe_fw=1.0, moe_bw=2.0, head_fw=2.0, head_bw=4.0)
+    even = balance_pipeline(32, 32, 4, 1, 8, prof, max_offset=0)
+    bal = balance_pipeline(32, 32, 4, 1, 8, prof, max_offset=2)
+    assert sum(sum(r) for r in bal.layers) == 32
+    assert bal.makespan < even.makespan and bal.layers[0][-1] < 8
+    tight = balance_pipeline(32, 32, 4, 1, 8, LayerProfile(act_mem=10.0, recomp_mem=1.0, layer_mem=1.0),
+                             mem_limit_mb=200.0)
+    assert any(any(r) for r in tight.recompute) and max(tight.peak_mem) <= 200.0 + 1e-6
+
+
+def test_config_ingestion(tmp_path):
+    toml = tmp_path / "m.toml"
+    toml.write_text('[model]\nn_layers = 8\ndim = 256\nn_heads = 16\nvocab_size = 2048\n[training]\nseq_len = 2048\n')
+    s = ftc.model_from_toml(str(toml))
+    assert (s.num_layers, s.hidden_size, s.seq_length) == (8, 256, 2048)
+    sh = tmp_path / "run.sh"
+    sh.write_text('NL=12\npython pretrain.py --num-layers ${NL} --hidden-size 1024 \\\n  --num-attention-heads 8 --seq-length 4096\n')
+    s = ftc.model_from_shell(str(sh))
+    assert (s.num_layers, s.hidden_size, s.num_attention_heads) == (12, 1024, 8)
+    ya = tmp_path / "m.yaml"
+    ya.write_text("model:\n  model_config:\n    num_layers: 6\n    hidden_size: 512\n    num_heads: 8\n"
+                  "parallel_config:\n  data_parallel: 2\n  model_parallel: 2\n  pipeline_stage: 2\n")
+    s = ftc.model_from_yaml(str(ya))
+    assert s.num_layers == 6 and s.world_size == 8
+
+
+def test_cli_dryrun_ranks_candidates(tmp_path):
+    mj = tmp_path / "model.json"
+    mj.write_text(json.dumps({k: getattr(LLAMA8B, k) for k in LLAMA8B.__dataclass_fields__}))
+    cfg = TunerConfig(rank_num=8, gbs=16, gpus_per_node=8, nnodes=1, output_path=str(tmp_path / "out"),
+                      dryrun=True, model_json=str(mj), strategy=Strategy(EP=False, CP=False))
+    ranked = taylor_search_tool(cfg, top_k=5)
+    assert 1 <= len(ranked) <= 5 and ranked == sorted(ranked, key=lambda e: e["step_time_us"])
+    assert os.path.exists(tmp_path / "out" / "nd_candidate_config.csv")
+    assert os.path.exists(tmp_path / "out" / "pipeline_output" / "ranked_configs.csv")
+    cfg.alg_phase = 1
+    assert "summary" in taylor_search_tool(cfg)[0]
