@@ -79,9 +79,10 @@ def run_ours(args):
     # public API: build on meta, shard with hsdp (full shard, level3), deferred init
     model = Llama(cfg, device="meta")
     for layer in model.layers:
-        hp.hsdp(layer, shard_size=world, optimizer_level="level3", comm_fusion=world > 1,
+        hp.hsdp(layer, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
                 comm_async=world > 1)
-    hp.hsdp(model, shard_size=world, optimizer_level="level3", comm_async=world > 1)
+    hp.hsdp(model, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
+            comm_async=world > 1)
     for i, layer in enumerate(model.layers):
         if i + 1 < len(model.layers):
             layer.set_forward_prefetch_cells([model.layers[i + 1]])
@@ -89,9 +90,8 @@ def run_ours(args):
             layer.set_backward_prefetch_cells([model.layers[i - 1]])
     hp.init_parameters(model, device=dev, seed=0)
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    opt.fuse_into_backward(model)       # optimizer update runs inside backward, per wrapped module
     opt.init_state()
-    if world == 1:
-        opt.fuse_into_backward(model)
 
     n_total = args.warmup + args.steps
     host = make_batches(cfg, args, rank, n_total)

@@ -99,6 +99,8 @@ def hsdp_sync_stream() -> None:
     """
     _drain_pending()
     for sch in _ALL_SCHEDULERS:
+        for buf in sch.hsdp_state.symm_buffers:
+            buf.wait()
         _install_grads(sch.hsdp_state)
 
 
@@ -111,8 +113,22 @@ class HSDPScheduler:
         self.forward_prefetch_cells: List = []
         self.backward_prefetch_cells: List = []
         self.level3 = config.shard_level == OptimizerLevel.SHARD_OPT_GRAD_PARAM
+        self._bind_symm_buffers()
         self._register_hooks()
         _ALL_SCHEDULERS.append(self)
+
+    def _bind_symm_buffers(self) -> None:
+        """Let the wgrad GEMM write straight into the symmetric gradient buffers."""
+        for buf in self.hsdp_state.symm_buffers:
+            buf.on_all_ready = (lambda b=buf: self._symm_ready(b))
+            for i, hp in enumerate(buf.params):
+                hp.param._hpb_symm = (buf, i)
+
+    def _symm_ready(self, buf) -> None:
+        for hp in buf.params:
+            hp.grad_ready = True
+        self._queue_root_callback()
+        self.hsdp_state.symm_bucket_done(buf)
 
     # ---------------------------------------------------------------- hooks --
     def _register_hooks(self) -> None:
@@ -131,6 +147,12 @@ class HSDPScheduler:
                 return
             hp.grad_ready = True
             self._queue_root_callback()
+            symm = getattr(hp, "_symm", None)
+            if symm is not None:
+                buf, i = symm
+                if buf.store_grad(i, grad):
+                    self.hsdp_state.symm_bucket_done(buf)
+                return
             pending = self.hsdp_state.reduce_grad(hp, grad)
             if pending is not None:
                 _PENDING.append(pending)

@@ -161,6 +161,7 @@ class HSDPState:
         self.sharded_params = [p for p in self.hsdp_params if p.sharded]
         self.grad_hook = HSDPGradHook(config)
         self.param_buffers: List[HSDPParamBuffer] = []
+        self.symm_buffers: list = []
         self.grad_buffers: List[HSDPGradBuffer] = []
         self._bucket_of: Dict[int, HSDPGradBuffer] = {}
         self.is_sharded = True
@@ -174,21 +175,33 @@ class HSDPState:
         for p in self.sharded_params:
             groups.setdefault((p.sharded_group_info.ranks, p.shard.dtype, p.shard.device), []).append(p)
         self._in_buffer = set()
+        from ...parallel import fused_hsdp
+        level3 = self.config.shard_level == OptimizerLevel.SHARD_OPT_GRAD_PARAM
         for plist in groups.values():
-            if len(plist) > 1:
+            if plist[0].shard.device.type == "cuda" and fused_hsdp.can_use(plist):
+                buf = fused_hsdp.SymmParamBuffer(plist, level3)      # NVLink P2P gather + fused RS/AdamW
+                self.symm_buffers.append(buf)
+                self.param_buffers.append(buf)
+                self._in_buffer.update(id(p) for p in plist)
+            elif len(plist) > 1:
                 self.param_buffers.append(HSDPParamBuffer(plist))
                 self._in_buffer.update(id(p) for p in plist)
 
     def rebuild_param_buffers(self) -> None:
         """Re-create the flat parameter buffers from the current shards (after materialisation)."""
-        if self.param_buffers:
-            self.param_buffers = []
+        if self.config.comm_fusion:
+            for b in self.symm_buffers:
+                b.symm.close()
+            self.param_buffers, self.symm_buffers = [], []
             self._init_param_buffers()
+            if self.config.grad_fusion:
+                self.grad_buffers, self._bucket_of = [], {}
+                self._init_grad_buffers()
 
     def _init_grad_buffers(self) -> None:
         groups: Dict[tuple, List[HSDPParam]] = {}
         for p in self.hsdp_params:
-            if not p.param.requires_grad:
+            if not p.param.requires_grad or getattr(p, "_symm", None) is not None:
                 continue
             key = (p.sharded_group_info.ranks, p.unsharded_group_info.ranks, p.leaf.dtype, p.shard_size)
             groups.setdefault(key, []).append(p)
@@ -252,7 +265,21 @@ class HSDPState:
             return bucket.reduce(self.grad_hook.requires_grad_sync)
         return None
 
+    def symm_bucket_done(self, buf) -> None:
+        """Every gradient of a symmetric buffer has been written: reduce (and step) it."""
+        sync = self.grad_hook.requires_grad_sync
+        if buf.reduce_and_step(sync, self.config.grad_scale):
+            return
+        # no fused optimizer attached: reduce-scatter each parameter's gradient with NCCL
+        for hp, view in zip(buf.params, buf.grad_views):
+            if hp.param.requires_grad:
+                self.grad_hook.process(hp, view)
+        buf.grad_fresh = True
+
     def zero_grads(self) -> None:
+        for b in self.symm_buffers:
+            b.grad_fresh = True
+            b.ready = set()
         for p in self.hsdp_params:
             p.zero_acc_grad()
             p.reduced_grad = None

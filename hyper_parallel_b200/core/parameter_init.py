@@ -127,3 +127,4 @@ def init_parameters(module: nn.Module, stage_index: int = 0, *, device=None,
         sch = sub.__dict__.get("hsdp_scheduler")
         if sch is not None:
             sch.hsdp_state.rebuild_param_buffers()
+            sch._bind_symm_buffers()

@@ -71,11 +71,12 @@ class _Linear(torch.autograd.Function):
     """y = x W^T with all three GEMMs on the tcgen05 kernel (no transposes)."""
 
     @staticmethod
-    def forward(ctx, x, w, wgrad_into):
+    def forward(ctx, x, w, wgrad_into, symm):
         x2 = x.reshape(-1, x.shape[-1])
         ctx.save_for_backward(x2, w)
         ctx.x_shape = x.shape
         ctx.wgrad_into = wgrad_into
+        ctx.symm = symm
         # allocate with the final shape: the result must not be a view created inside the Function
         # (callers may update it in place, e.g. RoPE on the fused QKV buffer)
         y = torch.empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16, device=x.device)
@@ -91,7 +92,15 @@ class _Linear(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
+        if ctx.needs_input_grad[1] and ctx.symm is not None:
+            # HSDP over symmetric memory: the epilogue writes dW into the flat gradient buffer that
+            # the fused reduce-scatter + AdamW kernel of every peer reads
+            buf, i = ctx.symm
+            view, acc = buf.wgrad_target(i)
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=view, accumulate=acc)
+            if buf.mark_ready(i):
+                buf.on_all_ready()
+        elif ctx.needs_input_grad[1]:
             tgt = ctx.wgrad_into
             if tgt is not None:
                 # fused gradient accumulation: dW is added straight into the
@@ -100,14 +109,15 @@ class _Linear(torch.autograd.Function):
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            wgrad_into: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w.T (+ bias)``; bf16 CUDA inputs use the tcgen05 GEMM for fwd/dgrad/wgrad."""
     if native.use_native(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        y = _Linear.apply(x, w, wgrad_into)
+        symm = getattr(w, "_hpb_symm", None) if (w.requires_grad and torch.is_grad_enabled()) else None
+        y = _Linear.apply(x, w, wgrad_into, symm)
         return y if bias is None else y + bias
     return F.linear(x, w, bias)
 

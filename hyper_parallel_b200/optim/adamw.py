@@ -31,6 +31,8 @@ class FusedAdamW(torch.optim.Optimizer):
         self.master_weights = master_weights
         self._step_count = 0
         self._done_in_backward = set()
+        self._fused_params = set()
+        self._flat_states: Dict[int, dict] = {}
         self._group_of: Dict[int, dict] = {}
         for g in self.param_groups:
             for p in g["params"]:
@@ -51,7 +53,13 @@ class FusedAdamW(torch.optim.Optimizer):
         """Allocate all optimizer state now (instead of lazily on the first step)."""
         for g in self.param_groups:
             for p in g["params"]:
-                if p.requires_grad:
+                if not p.requires_grad:
+                    continue
+                hp = getattr(p, "_hsdp_param", None)
+                symm = getattr(hp, "_symm", None) if hp is not None else None
+                if symm is not None and symm[0].optimizer is self:
+                    self.flat_state_for(symm[0])
+                else:
                     self._state_for(p)
 
     def _update(self, p, grad: torch.Tensor, step: int) -> None:
@@ -80,11 +88,33 @@ class FusedAdamW(torch.optim.Optimizer):
 
     # ------------------------------------------------------- backward fusion --
     def fuse_into_backward(self, model: torch.nn.Module) -> None:
-        """Consume each HSDP-reduced gradient as soon as it exists (update overlaps backward)."""
+        """Consume each HSDP-reduced gradient as soon as it exists (update overlaps backward).
+
+        Parameters held in symmetric-memory buffers are updated by the fused reduce-scatter +
+        AdamW kernel (one launch per wrapped module); the others by one AdamW launch each."""
         for p in model.parameters():
             hp = getattr(p, "_hsdp_param", None)
-            if hp is not None and id(p) in self._group_of:
+            if hp is None or id(p) not in self._group_of:
+                continue
+            symm = getattr(hp, "_symm", None)
+            if symm is not None:
+                symm[0].optimizer = self
+                self._fused_params.add(id(p))
+            else:
                 hp.grad_consumer = self._consume
+
+    def flat_state_for(self, buf) -> dict:
+        """fp32 master / moments for the flat shard of a symmetric buffer."""
+        st = self._flat_states.get(id(buf))
+        if st is None:
+            st = {"master": buf.flat_shard.float().clone(),
+                  "exp_avg": torch.zeros(buf.shard_numel, dtype=torch.float32, device=buf.device),
+                  "exp_avg_sq": torch.zeros(buf.shard_numel, dtype=torch.float32, device=buf.device)}
+            self._flat_states[id(buf)] = st
+        return st
+
+    def group_for(self, buf) -> dict:
+        return self._group_of[id(buf.params[0].param)]
 
     def _consume(self, hp, grad: torch.Tensor) -> None:
         p = hp.param
@@ -98,7 +128,7 @@ class FusedAdamW(torch.optim.Optimizer):
         self._step_count += 1
         for g in self.param_groups:
             for p in g["params"]:
-                if id(p) in self._done_in_backward:
+                if id(p) in self._done_in_backward or id(p) in self._fused_params:
                     continue
                 grad = _leaf(p).grad
                 if grad is None:

@@ -1,0 +1,103 @@
+"""Multi-GPU tests (need >= 2 CUDA devices): the symmetric-memory HSDP path (P2P all-gather,
+fused reduce-scatter + AdamW) must train like the torch.distributed path, and a peer wait that
+nothing satisfies must time out with a status code instead of hanging."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _train(rank, world, fused, steps, out):
+    import torch.distributed as dist
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200.models.llama import Llama, LlamaConfig
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.optim import FusedAdamW
+    os.environ["HPB_FUSED_COMM"] = "1" if fused else "0"
+    dev = torch.device("cuda", rank)
+    cfg = LlamaConfig.tiny(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=4, num_kv_heads=2,
+                           head_dim=128, ffn_size=1024)
+    model = Llama(cfg, device="meta")
+    for layer in model.layers:
+        hp.hsdp(layer, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=True, comm_async=True)
+    hp.hsdp(model, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=True, comm_async=True)
+    hp.init_parameters(model, device=dev, seed=0)
+    n_symm = sum(len(m.hsdp_scheduler.hsdp_state.symm_buffers) for m in model.modules() if "hsdp_scheduler" in m.__dict__)
+    assert (n_symm > 0) == fused
+    opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    opt.fuse_into_backward(model)
+    g = torch.Generator().manual_seed(100 + rank)
+    losses = []
+    for _ in range(steps):
+        tok = torch.randint(0, cfg.vocab_size, (2, 129), generator=g).to(dev)
+        model.zero_grads()
+        loss = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        hp.hsdp_sync_stream()
+        opt.step()
+        losses.append(loss.item())
+    native.check_status()
+    torch.cuda.synchronize()
+    # gather the final weights of one parameter for comparison
+    w = model.layers[0].wqkv.detach().float().contiguous()
+    parts = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(parts, w)
+    if rank == 0:
+        torch.save({"losses": losses, "w": torch.cat(parts, 0).cpu()}, out)
+
+
+def _worker(rank, world, port, tmp):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from hyper_parallel_b200.core.hsdp.hsdp_scheduler import reset_hsdp_registry
+    _train(rank, world, False, 3, os.path.join(tmp, "ref.pt"))
+    reset_hsdp_registry()
+    _train(rank, world, True, 3, os.path.join(tmp, "fused.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_symmetric_hsdp_matches_nccl_path(tmp_path, world):
+    _need(world)
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    a, b = torch.load(tmp_path / "ref.pt"), torch.load(tmp_path / "fused.pt")
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2 * abs(x), (a["losses"], b["losses"])
+    rel = (a["w"] - b["w"]).norm() / a["w"].norm()
+    assert rel < 5e-3, rel.item()
+
+
+def test_peer_wait_times_out_with_status_not_a_hang():
+    """Single GPU: wait on a flag that nothing sets, with a 20 ms limit; the kernel must return and
+    record status code 5 (peer flag timeout), and the context must stay usable."""
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.parallel.symm import SymmetricMemory
+    sm = SymmetricMemory(None, 1024)
+    st = native.status_word(sm.device)
+    st.zero_()
+    sm.world = 2                       # pretend there is a peer whose flag never arrives
+    import ctypes
+    arr = (ctypes.c_void_p * 2)(sm.pad_ptrs[0], sm.pad_ptrs[0])
+    rc = sm.lib.hpb_symm_barrier(arr, 0, 2, 5, 7, 20_000_000, 0, st.data_ptr(), native.stream(sm.device))
+    assert rc == 0
+    torch.cuda.synchronize()
+    code, detail = st.tolist()
+    assert code == 5 and (detail >> 8) == 5
+    with pytest.raises(RuntimeError, match="peer flag"):
+        native.check_status()
+    assert torch.ones(4, device="cuda").sum().item() == 4.0      # context still healthy
+    sm.world = 1
+    sm.close()
