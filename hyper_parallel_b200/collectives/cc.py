@@ -345,10 +345,18 @@ def _all_to_all(x: torch.Tensor, split_dim: int, concat_dim: int, group) -> torc
     send = x.reshape(shape[:split_dim] + [n, local] + shape[split_dim + 1:]).movedim(split_dim, 0).contiguous()
     recv = torch.empty_like(send)
     if dist.get_backend(group) == "gloo":
-        ins = [c.contiguous() for c in send.unbind(0)]
-        outs = [torch.empty_like(c) for c in ins]
-        dist.all_to_all(outs, ins, group=group)
-        recv = torch.stack(outs, 0)
+        # gloo has no all-to-all: exchange the chunks with point-to-point messages
+        me = dist.get_rank(group)
+        ranks = dist.get_process_group_ranks(group)
+        reqs = []
+        for r in range(n):
+            if r == me:
+                recv[r].copy_(send[r])
+            else:
+                reqs.append(dist.isend(send[r].contiguous(), dst=ranks[r], group=group))
+                reqs.append(dist.irecv(recv[r], src=ranks[r], group=group))
+        for q in reqs:
+            q.wait()
     else:
         dist.all_to_all_single(recv, send, group=group)
     # recv[r] = chunk that rank r held for me, shaped like x with split_dim -> local
