@@ -40,11 +40,30 @@ constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
+// mode 0: plain GEMM.
+// mode 1: grouped-M.  Rows of A (and C) are grouped by expert, every group padded to a multiple
+//         of BLOCK_M; block_group[m_blk] names the expert of each 128-row block; operand B holds
+//         all experts stacked along its row axis, b_group_rows rows per expert.
+// mode 2: grouped-K (expert weight gradients).  One [M, N] output per expert, stacked in C; the
+//         contraction runs over the expert's rows [group_offsets[e], group_offsets[e+1]) of the
+//         two MN-major operands (offsets are multiples of BLOCK_K; padding rows are zero).
 struct GemmParams {
   int M, N, K;
   void* C;
   int64_t ldc;
   int* status;
+  int mode;
+  const int* block_group;
+  const int* group_offsets;
+  int num_groups;
+  int b_group_rows;
+};
+
+struct TileInfo {
+  int m0, n0;        // tile origin in C (mode 2: inside the expert's [M, N] block)
+  int group;         // expert (0 for mode 0)
+  int k_row0;        // first contraction row (mode 2), else 0
+  int num_k;         // number of BLOCK_K steps
 };
 
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_blk, int& n_blk) {
@@ -55,6 +74,33 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& m_
   const int r = t - group * per_group;
   m_blk = first_m + r % gsz;
   n_blk = r / gsz;
+}
+
+__device__ __forceinline__ int total_tiles(const GemmParams& p) {
+  const int num_m = (p.M + BLOCK_M - 1) / BLOCK_M, num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  return (p.mode == 2 ? p.num_groups : 1) * num_m * num_n;
+}
+
+__device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p) {
+  const int num_m = (p.M + BLOCK_M - 1) / BLOCK_M, num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  TileInfo ti;
+  int m_blk, n_blk;
+  if (p.mode == 2) {
+    const int per = num_m * num_n;
+    ti.group = t / per;
+    tile_coords(t - ti.group * per, num_m, num_n, m_blk, n_blk);
+    const int r0 = p.group_offsets[ti.group], r1 = p.group_offsets[ti.group + 1];
+    ti.k_row0 = r0;
+    ti.num_k = (r1 - r0 + BLOCK_K - 1) / BLOCK_K;
+  } else {
+    tile_coords(t, num_m, num_n, m_blk, n_blk);
+    ti.group = p.mode == 1 ? p.block_group[m_blk] : 0;
+    ti.k_row0 = 0;
+    ti.num_k = (p.K + BLOCK_K - 1) / BLOCK_K;
+  }
+  ti.m0 = m_blk * BLOCK_M;
+  ti.n0 = n_blk * BLOCK_N;
+  return ti;
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
@@ -74,10 +120,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + BLOCK_M - 1) / BLOCK_M;
-  const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = num_m * num_n;
-  const int num_k = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const int num_tiles = total_tiles(p);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -111,9 +154,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       long issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
-        const int m0 = m_blk * BLOCK_M, n0 = n_blk * BLOCK_N;
+        const TileInfo ti = tile_info(t, p);
+        const int m0 = ti.m0, n0 = ti.n0;
+        const int num_k = ti.num_k;
+        // row offset of this tile's expert inside the stacked B operand (mode 1)
+        const int b_row_off = p.mode == 1 ? ti.group * p.b_group_rows : 0;
         for (int kb = 0; kb < num_k; ++kb) {
           ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, p.status,
                                  kTimeoutEmptyBarrier, blockIdx.x);
@@ -121,7 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          const int k0 = kb * BLOCK_K;
+          const int k0 = ti.k_row0 + kb * BLOCK_K;
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
           } else {
@@ -130,11 +175,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tma_load_2d(sa + j * ATOM_BYTES, &tmap_a, &full_bar[stage], m0 + 64 * j, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, b_row_off + n0);
           } else {
 #pragma unroll
             for (int j = 0; j < BLOCK_N / 64; ++j)
-              tma_load_2d(sb + j * ATOM_BYTES, &tmap_b, &full_bar[stage], n0 + 64 * j, k0);
+              tma_load_2d(sb + j * ATOM_BYTES, &tmap_b, &full_bar[stage], n0 + 64 * j, b_row_off + k0);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -169,6 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * BLOCK_N;
+        const int num_k = tile_info(t, p).num_k;
         for (int kb = 0; kb < num_k; ++kb) {
           ok = mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
                                  kTimeoutFullBarrier, blockIdx.x);
@@ -206,26 +252,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int local_tile = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
-      int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      const TileInfo ti = tile_info(t, p);
       const int buf = local_tile & 1;
       const uint32_t buf_phase = (local_tile >> 1) & 1;
       ok = mbar_wait_bounded(&tmem_full[buf], buf_phase, abort_flag, p.status, kTimeoutTmemFull,
                              blockIdx.x);
       if (!ok) break;
       tc_fence_after();
-      const int row = m_blk * BLOCK_M + q * 32 + lane;
-      const int col0 = n_blk * BLOCK_N;
+      const int row_local = ti.m0 + q * 32 + lane;           // row inside the [M, N] problem
+      const int64_t row = (p.mode == 2 ? static_cast<int64_t>(ti.group) * p.M : 0) + row_local;
+      const int col0 = ti.n0;
+      const bool empty_k = ti.num_k == 0;                    // expert without tokens: the tile is zero
       const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BLOCK_N / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
+        if (empty_k) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         const int col = col0 + c * 32;
-        if (row < p.M && col < p.N) {
+        if (row_local < p.M && col < p.N) {
           if constexpr (OUT_F32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<int64_t>(row) * p.ldc + col;
+            float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
             if (col + 32 <= p.N && (p.ldc & 3) == 0) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -247,7 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           } else {
             __nv_bfloat16* dst =
-                reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<int64_t>(row) * p.ldc + col;
+                reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
             if (col + 32 <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -345,7 +396,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int num_tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N);
+  const int num_tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) *
+                        (p.mode == 2 ? p.num_groups : 1);
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
   kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
@@ -379,7 +431,7 @@ extern "C" int hpb_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B
   else
     r = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, 64, BLOCK_K);
   if (r) return r;
-  GemmParams p{M, N, K, C, ldc, status};
+  GemmParams p{M, N, K, C, ldc, status, 0, nullptr, nullptr, 1, 0};
   const int key = (a_mn ? 8 : 0) | (b_mn ? 4 : 0) | (out_f32 ? 2 : 0) | (accumulate ? 1 : 0);
   switch (key) {
 #define HPB_CASE(k, a, b, o, c) \
@@ -397,6 +449,62 @@ extern "C" int hpb_gemm_bf16(const void* A, int a_mn, int64_t lda, const void* B
     HPB_CASE(9, true, false, false, true)
     HPB_CASE(10, true, false, true, false)
     HPB_CASE(11, true, false, true, true)
+    HPB_CASE(12, true, true, false, false)
+    HPB_CASE(13, true, true, false, true)
+    HPB_CASE(14, true, true, true, false)
+    HPB_CASE(15, true, true, true, true)
+#undef HPB_CASE
+  }
+  return -3;
+}
+
+
+// Grouped GEMMs of an expert layer (see GemmParams).
+//   mode 1: C[Mtot, N] = A[Mtot, K] * B_e^T, expert of each 128-row block from block_group;
+//           B stacked [E * b_group_rows, ...] (K-major: [E*N, K]; MN-major: [E*K, N]).
+//   mode 2: C[e] [M, N] (+)= A[rows_e, M]^T * B[rows_e, N] for every expert e (both MN-major);
+//           lda/ldb are the row strides of the [rows_total, M] / [rows_total, N] operands.
+extern "C" int hpb_gemm_bf16_grouped(const void* A, int a_mn, int64_t lda, int64_t a_rows,
+                                     const void* B, int b_mn, int64_t ldb, int64_t b_rows, void* C,
+                                     int64_t ldc, int out_f32, int accumulate, int M, int N, int K,
+                                     int mode, const int* block_group, const int* group_offsets,
+                                     int num_groups, int b_group_rows, int* status, int num_sms,
+                                     cudaStream_t stream) {
+  using namespace hpb;
+  if (M <= 0 || N <= 0 || num_groups <= 0) return 0;
+  if (mode != 1 && mode != 2) return -4;
+  if (mode == 2 && !(a_mn && b_mn)) return -5;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  cudaFree(nullptr);
+  CUtensorMap ta, tb;
+  int r;
+  // tensor maps cover the whole stacked operands; a_rows / b_rows are their outer extents
+  if (!a_mn)
+    r = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, a_rows, lda, BLOCK_K, BLOCK_M);
+  else
+    r = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, a_rows, lda, 64, BLOCK_K);
+  if (r) return r;
+  if (!b_mn)
+    r = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, b_rows, ldb, BLOCK_K, BLOCK_N);
+  else
+    r = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, b_rows, ldb, 64, BLOCK_K);
+  if (r) return r;
+  GemmParams p{M, N, K, C, ldc, status, mode, block_group, group_offsets, num_groups, b_group_rows};
+  const int key = (a_mn ? 8 : 0) | (b_mn ? 4 : 0) | (out_f32 ? 2 : 0) | (accumulate ? 1 : 0);
+  switch (key) {
+#define HPB_CASE(k, a, b, o, c) \
+  case k:                       \
+    return launch<a, b, o, c>(ta, tb, p, num_sms, stream);
+    HPB_CASE(0, false, false, false, false)
+    HPB_CASE(1, false, false, false, true)
+    HPB_CASE(2, false, false, true, false)
+    HPB_CASE(3, false, false, true, true)
+    HPB_CASE(4, false, true, false, false)
+    HPB_CASE(5, false, true, false, true)
+    HPB_CASE(6, false, true, true, false)
+    HPB_CASE(7, false, true, true, true)
     HPB_CASE(12, true, true, false, false)
     HPB_CASE(13, true, true, false, true)
     HPB_CASE(14, true, true, true, false)
