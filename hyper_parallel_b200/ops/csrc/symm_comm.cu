@@ -123,9 +123,15 @@ p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict
       const uint4* src = reinterpret_cast<const uint4*>(
           reinterpret_cast<const __nv_bfloat16*>(shards.ptr[r]) + sg.shard_off);
       uint4* dst = reinterpret_cast<uint4*>(full + sg.full_off + static_cast<long long>(r) * sg.n);
-      for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
-           i += static_cast<long long>(gridDim.x) * blockDim.x)
-        dst[i] = src[i];
+      const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+      long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+      // four independent 16-byte loads in flight per thread: NVLink latency is ~2 us, so the
+      // bytes in flight, not the CTA count, set the achieved bandwidth
+      for (; i + 3 * stride < nv; i += 4 * stride) {
+        const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
+        dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
+      }
+      for (; i < nv; i += stride) dst[i] = src[i];
       // tail elements
       if (blockIdx.x == 0)
         for (long long i = (nv << 3) + threadIdx.x; i < sg.n; i += blockDim.x)
@@ -262,6 +268,16 @@ fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict
   }
 }
 
+// The persistent GEMM needs ~200 KB of shared memory per SM.  A kernel that prefers L1 would
+// force every SM it touches to be re-partitioned before a GEMM CTA can land there (the GEMM CTA
+// then waits for the communication CTA to finish).  Asking for the maximum shared-memory
+// carve-out keeps both kernels co-resident.
+template <typename K>
+static void prefer_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                       cudaSharedmemCarveoutMaxShared);
+}
+
 static PeerTable make_table(void* const* ptrs, int n) {
   PeerTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = (ptrs != nullptr && i < n) ? ptrs[i] : nullptr;
@@ -300,6 +316,7 @@ extern "C" int hpb_symm_barrier(void* const* pads, int rank, int n, int slot, un
                                 unsigned long long limit_ns, int do_signal, int* status,
                                 cudaStream_t s) {
   if (n > kMaxPeers) return -2;
+  prefer_shared(symm_barrier_kernel);
   symm_barrier_kernel<<<1, 32, 0, s>>>(make_table(pads, n), rank, n, slot, epoch, limit_ns,
                                        do_signal, status);
   return static_cast<int>(cudaGetLastError());
@@ -310,6 +327,7 @@ extern "C" int hpb_p2p_allgather(void* const* shard_ptrs, void* const* pads, con
                                  unsigned long long limit_ns, int* status, unsigned* done_counter,
                                  int num_ctas, cudaStream_t s) {
   if (n > kMaxPeers) return -2;
+  prefer_shared(p2p_allgather_kernel);
   p2p_allgather_kernel<<<num_ctas, 512, 0, s>>>(make_table(shard_ptrs, n), make_table(pads, n),
                                                 reinterpret_cast<const Segment*>(segs), num_segs,
                                                 reinterpret_cast<__nv_bfloat16*>(full), rank, n,
@@ -326,6 +344,7 @@ extern "C" int hpb_fused_rs_adamw(void* const* grad_ptrs, void* const* pads, con
   if (n > kMaxPeers) return -2;
   AdamArgs a{lr, b1, b2, eps, wd, 1.f - powf(b1, (float)step), 1.f - powf(b2, (float)step), grad_scale};
 #define HPB_RS(NN)                                                                              \
+  prefer_shared(fused_rs_adamw_kernel<NN>);                                                     \
   fused_rs_adamw_kernel<NN><<<num_ctas, 512, 0, s>>>(                                           \
       make_table(grad_ptrs, n), make_table(pads, n), reinterpret_cast<const Segment*>(segs),    \
       num_segs, master, m, v, reinterpret_cast<__nv_bfloat16*>(param_shard), a, rank, n, epoch, \

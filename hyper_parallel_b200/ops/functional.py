@@ -22,6 +22,17 @@ __all__ = [
 
 
 # --------------------------------------------------------------------- GEMM --
+import os as _os
+
+_PAIR_MODE = _os.environ.get("HPB_GEMM_PAIR", "0")     # "0" single-CTA kernel, "1" CTA pairs, "auto" by size
+
+
+def set_gemm_pair_mode(mode: str) -> None:
+    """Select the GEMM kernel: ``"0"`` 128x256 single-CTA, ``"1"`` 256x256 CTA pairs, ``"auto"``."""
+    global _PAIR_MODE
+    _PAIR_MODE = mode
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          accumulate: bool = False) -> torch.Tensor:
@@ -59,11 +70,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             out.zero_()
         return out
     dev = a.device
-    rc = native.lib().hpb_gemm_bf16(
-        a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
-        out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
-        M, N, K, native.status_word(dev).data_ptr(), native.sm_count(dev), native.stream(dev))
-    native.check(rc, "hpb_gemm_bf16")
+    lib = native.lib()
+    # CTA-pair (256x256, cta_group::2) kernel for large problems, single-CTA 128x256 otherwise
+    use_pair = _PAIR_MODE == "1" or (_PAIR_MODE == "auto" and M >= 512 and N >= 512 and hasattr(lib, "hpb_gemm2_bf16"))
+    fn = lib.hpb_gemm2_bf16 if use_pair else lib.hpb_gemm_bf16
+    rc = fn(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
+            out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+            M, N, K, native.status_word(dev).data_ptr(), native.sm_count(dev), native.stream(dev))
+    native.check(rc, "hpb_gemm2_bf16" if use_pair else "hpb_gemm_bf16")
     return out
 
 

@@ -10,6 +10,7 @@ all-to-all of ``redistribute`` (hyper_parallel/core/tensor_redistribution.py:84-
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional, Tuple
 
 import torch
@@ -40,11 +41,58 @@ def route_reference(logits: torch.Tensor, bias: torch.Tensor, top_k: int, n_grou
     return idx, w
 
 
+class _RouteKernel(torch.autograd.Function):
+    """Router top-k on the CUDA kernel; the backward (a [T, k]-sized computation) is plain tensor math."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, top_k, n_group, topk_group, scale):
+        T, E = logits.shape
+        logits = logits.contiguous()
+        idx = torch.empty((T, top_k), dtype=torch.int64, device=logits.device)
+        w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+        lib = native.lib()
+        vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+        lib.hpb_moe_route.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, cf, vp]
+        lib.hpb_moe_route.restype = ci
+        rc = lib.hpb_moe_route(logits.data_ptr(), bias.float().contiguous().data_ptr(), idx.data_ptr(),
+                               w.data_ptr(), None, T, E, top_k, n_group, topk_group, float(scale),
+                               native.stream(logits.device))
+        native.check(rc, "hpb_moe_route")
+        ctx.save_for_backward(logits, idx)
+        ctx.scale = scale
+        ctx.mark_non_differentiable(idx)
+        return idx, w
+
+    @staticmethod
+    def backward(ctx, _gidx, gw):
+        logits, idx = ctx.saved_tensors
+        sel = torch.sigmoid(logits.gather(1, idx))
+        S = sel.sum(-1, keepdim=True) + 1e-20
+        gs = ctx.scale * (gw - (gw * sel).sum(-1, keepdim=True) / S) / S
+        dl = torch.zeros_like(logits).scatter_(1, idx, gs * sel * (1.0 - sel))
+        return dl, None, None, None, None, None
+
+
+def _kernel_route_ok(E: int, top_k: int, n_group: int) -> bool:
+    if E % 32 or E > 512 or top_k > 32 or E % n_group:
+        return False
+    if n_group > 1:
+        vpl, epg = E // 32, E // n_group
+        if epg % vpl:
+            return False
+        lpg = epg // vpl
+        if lpg & (lpg - 1) or 32 % lpg:
+            return False
+    return (E // 32) in (1, 2, 4, 8, 16)
+
+
 def route(x: torch.Tensor, gate_w: torch.Tensor, bias: torch.Tensor, top_k: int, n_group: int,
           topk_group: int, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
     """Gate GEMM + group-limited top-k.  Gradients flow to ``gate_w`` and ``x`` through the weights."""
     if x.is_cuda and x.dtype == torch.bfloat16:
         logits = Fn.linear(x, gate_w.to(torch.bfloat16)).float()
+        if _kernel_route_ok(logits.shape[1], top_k, n_group):
+            return _RouteKernel.apply(logits, bias, top_k, n_group, topk_group, scale)
     else:
         logits = F.linear(x.float(), gate_w.float())
     return route_reference(logits, bias, top_k, n_group, topk_group, scale)

@@ -26,6 +26,8 @@ c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int6
 _SIGNATURES = {
     "hpb_gemm_bf16": [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int,
                       c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "hpb_gemm2_bf16": [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int,
+                       c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "hpb_rmsnorm_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                         c_float, c_void_p],
     "hpb_rmsnorm_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

@@ -199,3 +199,42 @@ def test_deepseek_tiny_gpu_matches_cpu_reference():
     err = (gpu.layers[1].ffn.w_down.grad.float().cpu() - ref.layers[1].ffn.w_down.grad).norm() / \
         ref.layers[1].ffn.w_down.grad.norm()
     assert err < 0.15, err.item()     # routing ties under bf16 can move a few tokens between experts
+
+
+@pytest.mark.parametrize("E,k,G,KG", [(256, 8, 8, 4), (64, 6, 1, 1), (32, 4, 4, 2), (128, 8, 8, 3)])
+def test_moe_router_kernel_matches_reference(E, k, G, KG):
+    from hyper_parallel_b200.ops import moe
+    torch.manual_seed(11)
+    T = 333
+    logits = torch.randn(T, E, device=_dev(), requires_grad=True)
+    bias = torch.randn(E, device=_dev()) * 0.2
+    idx, w = moe._RouteKernel.apply(logits, bias, k, G, KG, 2.5)
+    lr = logits.detach().clone().requires_grad_()
+    ridx, rw = moe.route_reference(lr, bias, k, G, KG, 2.5)
+    # same set of experts per token (order of equal-rank picks follows the score order in both)
+    assert torch.equal(idx.sort(-1).values, ridx.sort(-1).values)
+    o1, o2 = idx.argsort(-1), ridx.argsort(-1)
+    assert torch.allclose(w.gather(1, o1), rw.gather(1, o2), atol=1e-5)
+    gw = torch.randn(T, k, device=_dev())
+    (w.gather(1, o1) * gw).sum().backward()
+    (rw.gather(1, o2) * gw).sum().backward()
+    assert torch.allclose(logits.grad, lr.grad, atol=1e-5)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (1000, 520, 136), (2048, 4096, 1024)])
+def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
+    Fn.set_gemm_pair_mode("1")
+    try:
+        c = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        c32 = torch.ones((M, N), device=_dev(), dtype=torch.float32)
+        Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c32, accumulate=True)
+        native.check_status()
+    finally:
+        Fn.set_gemm_pair_mode("0")
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert _rel_err(c, ref) < 5e-3
+    assert _rel_err(c32, ref + 1.0) < 1e-3
