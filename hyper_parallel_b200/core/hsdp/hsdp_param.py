@@ -58,7 +58,11 @@ class HSDPParam:
         if self.is_dtensor:
             layout = self.param.layout
             mesh = layout.mesh
-            used = layout.sharded_axes
+            used = set(layout.sharded_axes)
+            # axes over which the owner already synchronises this parameter's gradient itself
+            # (e.g. tensor-parallel replicas whose gradients are all-reduced inside the TP region)
+            for name in getattr(self.param, "hsdp_exclude_axes", ()):
+                used.add(mesh._dim_index(name))
             coord = mesh.get_coordinate()
             if coord is None:
                 raise RuntimeError(f"rank {me} is not in the mesh of parameter {self.name}")

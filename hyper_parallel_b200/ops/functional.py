@@ -24,7 +24,7 @@ __all__ = [
 # --------------------------------------------------------------------- GEMM --
 import os as _os
 
-_PAIR_MODE = _os.environ.get("HPB_GEMM_PAIR", "0")     # "0" single-CTA kernel, "1" CTA pairs, "auto" by size
+_PAIR_MODE = _os.environ.get("HPB_GEMM_PAIR", "auto")     # "0" single-CTA kernel, "1" CTA pairs, "auto" by size
 
 
 def set_gemm_pair_mode(mode: str) -> None:

@@ -26,14 +26,18 @@ def test_gemm_bf16(M, N, K, a_mn, b_mn):
     torch.manual_seed(0)
     a = torch.randn((K, M) if a_mn else (M, K), device=_dev(), dtype=torch.bfloat16)
     b = torch.randn((K, N) if b_mn else (N, K), device=_dev(), dtype=torch.bfloat16)
-    c = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
-    native.check_status()
+    Fn.set_gemm_pair_mode("0")        # the single-CTA 128x256 kernel
+    try:
+        c = Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        native.check_status()
+        # fp32 output + accumulate
+        c32 = torch.ones((M, N), device=_dev(), dtype=torch.float32)
+        Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c32, accumulate=True)
+        native.check_status()
+    finally:
+        Fn.set_gemm_pair_mode("auto")
     ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
     assert _rel_err(c, ref) < 5e-3
-    # fp32 output + accumulate
-    c32 = torch.ones((M, N), device=_dev(), dtype=torch.float32)
-    Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c32, accumulate=True)
-    native.check_status()
     assert _rel_err(c32, ref + 1.0) < 1e-3
 
 
@@ -234,7 +238,7 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
         Fn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=c32, accumulate=True)
         native.check_status()
     finally:
-        Fn.set_gemm_pair_mode("0")
+        Fn.set_gemm_pair_mode("auto")
     ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
     assert _rel_err(c, ref) < 5e-3
     assert _rel_err(c32, ref + 1.0) < 1e-3
