@@ -267,6 +267,49 @@ __global__ void rope_kernel(bf16* __restrict__ x, const int* __restrict__ pos, i
   }
 }
 
+// Table-driven, vectorised variant: cs_table[S, D/2] holds (cos, sin) of position * inv_freq, so
+// the kernel is pure streaming: 16-byte loads of both halves, 8 rotations per thread.
+__global__ void rope_table_init_kernel(float2* __restrict__ table, int S, int half, int D, float theta_log2) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S * half) return;
+  const int j = i % half, pos = i / half;
+  const float inv_freq = exp2f(-theta_log2 * (2.f * j) / D);
+  float sn, cs;
+  sincosf(pos * inv_freq, &sn, &cs);
+  table[i] = make_float2(cs, sn);
+}
+
+__global__ void rope_vec_kernel(bf16* __restrict__ x, const float2* __restrict__ table,
+                                const int* __restrict__ pos, int64_t T, int S, int NH, int D, int64_t ld,
+                                float sign) {
+  const int half = D >> 1, hv = half >> 3;
+  const int64_t total = T * NH * hv;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % hv);
+    const int64_t th = i / hv;
+    const int h = static_cast<int>(th % NH);
+    const int64_t t = th / NH;
+    const int p = pos ? pos[t] : static_cast<int>(t % S);
+    bf16* base = x + t * ld + static_cast<int64_t>(h) * D + c * 8;
+    const float4* tb = reinterpret_cast<const float4*>(table + static_cast<int64_t>(p) * half + c * 8);
+    float a[8], b[8], oa[8], ob[8];
+    unpack8(*reinterpret_cast<const uint4*>(base), a);
+    unpack8(*reinterpret_cast<const uint4*>(base + half), b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 cs2 = tb[e];              // (cos0, sin0, cos1, sin1)
+      const float s0 = cs2.y * sign, s1 = cs2.w * sign;
+      oa[2 * e] = a[2 * e] * cs2.x - b[2 * e] * s0;
+      ob[2 * e] = b[2 * e] * cs2.x + a[2 * e] * s0;
+      oa[2 * e + 1] = a[2 * e + 1] * cs2.z - b[2 * e + 1] * s1;
+      ob[2 * e + 1] = b[2 * e + 1] * cs2.z + a[2 * e + 1] * s1;
+    }
+    *reinterpret_cast<uint4*>(base) = pack8(oa);
+    *reinterpret_cast<uint4*>(base + half) = pack8(ob);
+  }
+}
+
 // ------------------------------------------------------- cross entropy ----
 // One CTA per token row.  Reads logits[row, :V] (bf16), writes loss[row] (fp32) and
 // overwrites the row IN PLACE with d(loss_sum * grad_scale)/dlogits =
@@ -561,4 +604,23 @@ extern "C" int hpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   // the existing launcher does the work; it only launches kernels
   return hpb_rmsnorm_bwd(dy, x, w, rstd, dres_in, dx, scratch, kNoAllocMaxPartials, dw, dw_f32,
                          dw_accumulate, T, H, s);
+}
+
+// cos/sin table for positions [0, S): table is float2[S * D/2]
+extern "C" int hpb_rope_table(float* table, int S, int D, float theta, cudaStream_t s) {
+  const int n = S * (D / 2);
+  if (n <= 0) return 0;
+  rope_table_init_kernel<<<(n + 255) / 256, 256, 0, s>>>(reinterpret_cast<float2*>(table), S, D / 2, D,
+                                                         log2f(theta));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// In-place RoPE using a precomputed table; needs D % 16 == 0, ld % 8 == 0 and 16-byte aligned x.
+extern "C" int hpb_rope_vec(void* x, const float* table, const int* pos, int64_t T, int S, int NH, int D,
+                            int64_t ld, int backward, int num_sms, cudaStream_t s) {
+  if (D % 16 || ld % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+  if (T == 0) return 0;
+  rope_vec_kernel<<<grid_for(T * NH * (D / 16), 256, num_sms), 256, 0, s>>>(
+      (bf16*)x, reinterpret_cast<const float2*>(table), pos, T, S, NH, D, ld, backward ? -1.f : 1.f);
+  return static_cast<int>(cudaGetLastError());
 }

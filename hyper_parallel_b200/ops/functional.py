@@ -254,6 +254,21 @@ def _rope_ref(x, seq_len, theta, positions=None, inverse=False):
     return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1).to(x.dtype)
 
 
+_ROPE_TABLES = {}
+
+
+def _rope_table(seq_len: int, D: int, theta: float, device) -> torch.Tensor:
+    """(cos, sin) of every (position, frequency) pair, built once per configuration on the device."""
+    key = (seq_len, D, theta, str(device))
+    t = _ROPE_TABLES.get(key)
+    if t is None:
+        t = torch.empty(seq_len * (D // 2) * 2, dtype=torch.float32, device=device)
+        rc = native.lib().hpb_rope_table(t.data_ptr(), seq_len, D, theta, native.stream(device))
+        native.check(rc, "hpb_rope_table")
+        _ROPE_TABLES[key] = t
+    return t
+
+
 def rope_(x: torch.Tensor, seq_len: int, theta: float, positions: Optional[torch.Tensor] = None,
           inverse: bool = False) -> torch.Tensor:
     """In-place rotary embedding of ``x[T, NH, D]`` (token stride may exceed ``NH*D``)."""
@@ -266,6 +281,12 @@ def rope_(x: torch.Tensor, seq_len: int, theta: float, positions: Optional[torch
     if positions is not None:
         positions = positions.to(torch.int32).contiguous()
         pos_ptr = positions.data_ptr()
+    if D % 16 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and positions is None:
+        table = _rope_table(seq_len, D, float(theta), x.device)
+        rc = native.lib().hpb_rope_vec(x.data_ptr(), table.data_ptr(), None, T, seq_len, NH, D, x.stride(0),
+                                       int(inverse), native.sm_count(x.device), native.stream(x.device))
+        native.check(rc, "hpb_rope_vec")
+        return x
     rc = native.lib().hpb_rope(x.data_ptr(), pos_ptr, T, seq_len, NH, D, x.stride(0), float(theta),
                                int(inverse), native.sm_count(x.device), native.stream(x.device))
     native.check(rc, "hpb_rope")

@@ -36,6 +36,8 @@ _SIGNATURES = {
     "hpb_swiglu_bwd": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p],
     "hpb_rope": [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_float, c_int, c_int,
                  c_void_p],
+    "hpb_rope_table": [c_void_p, c_int, c_int, c_float, c_void_p],
+    "hpb_rope_vec": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p],
     "hpb_cross_entropy": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_float, c_void_p],
     "hpb_adamw": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                   c_float, c_float, c_float, c_int, c_float, c_int, c_void_p],

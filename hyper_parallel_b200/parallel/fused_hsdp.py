@@ -32,7 +32,11 @@ from ..ops import native
 from .symm import DEFAULT_WAIT_NS, SymmetricMemory
 
 _COMM_STREAMS: Dict[int, torch.cuda.Stream] = {}
-_NUM_COMM_CTAS = int(os.environ.get("HPB_COMM_CTAS", "32"))
+# CTAs of the communication kernels.  Both are bandwidth kernels (the fused reduce-scatter + AdamW
+# moves 26 B of optimizer state per parameter through HBM on top of the NVLink reads), so they
+# need most of the machine's memory-level parallelism; they co-reside with the GEMM CTAs.
+_NUM_COMM_CTAS = int(os.environ.get("HPB_COMM_CTAS", "96"))
+_NUM_RS_CTAS = int(os.environ.get("HPB_RS_CTAS", os.environ.get("HPB_COMM_CTAS", "148")))
 
 
 def comm_stream(device: torch.device) -> torch.cuda.Stream:
@@ -205,7 +209,7 @@ class SymmParamBuffer:
                 st["master"].data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(),
                 self.flat_shard.data_ptr(), g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
                 opt._step_count + 1, grad_scale, self.rank, self.n, ep, DEFAULT_WAIT_NS, self.status.data_ptr(),
-                self.symm.done_counter.data_ptr() + 8, _NUM_COMM_CTAS, cs.cuda_stream)
+                self.symm.done_counter.data_ptr() + 8, _NUM_RS_CTAS, cs.cuda_stream)
             native.check(rc, "hpb_fused_rs_adamw")
             self.reduce_event = torch.cuda.Event()
             self.reduce_event.record(cs)
