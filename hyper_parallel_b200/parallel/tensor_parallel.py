@@ -47,6 +47,17 @@ def _scatter_sum_tokens(x: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
+def _workspace(group, x: torch.Tensor, shard_rows: int, k: int, n_out: int):
+    """Symmetric-memory workspace of the fused kernels, or ``None`` when they do not apply."""
+    n = cc.group_size(group)
+    if n == 1 or n > 8 or not _fused_enabled() or not x.is_cuda or x.dtype != torch.bfloat16:
+        return None
+    if cc.get_backend(group) != "nccl" or (k % 8) or (n_out % 8) or (shard_rows * k) % 8:
+        return None
+    from .tp_fused import TPWorkspace
+    return TPWorkspace.get(group, shard_rows * k * 2, n * shard_rows * n_out * 2)
+
+
 def _mm(a, b, **kw):
     """GEMM on the tcgen05 kernel for bf16 CUDA tensors, PyTorch otherwise (CPU tests)."""
     return Fn.gemm(a, b, **kw)
@@ -56,8 +67,12 @@ class _ColumnParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, group, symm):
         ctx.group, ctx.symm = group, symm
-        x = _gather_tokens(x_shard, group)
         ctx.save_for_backward(x_shard, w)
+        ws = _workspace(group, x_shard, x_shard.shape[0], x_shard.shape[1], w.shape[0])
+        if ws is not None:
+            # one kernel: peers' token panels are pulled over NVLink while the first panels multiply
+            return ws.ag_gemm(x_shard.contiguous(), w.contiguous())
+        x = _gather_tokens(x_shard, group)
         y = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
         if x.is_cuda and x.dtype == torch.bfloat16:
             _mm(x, w, out=y)
@@ -97,6 +112,11 @@ class _RowParallel(torch.autograd.Function):
     def forward(ctx, a, w, group, symm):
         ctx.group, ctx.symm = group, symm
         ctx.save_for_backward(a, w)
+        n = cc.group_size(group)
+        ws = _workspace(group, a, a.shape[0] // max(n, 1), a.shape[1], w.shape[0]) if a.shape[0] % max(n, 1) == 0 else None
+        if ws is not None:
+            # one kernel: partial tiles go straight into the owner's receive area, then are summed
+            return ws.gemm_rs(a.contiguous(), w.contiguous())
         if a.is_cuda and a.dtype == torch.bfloat16:
             y = _mm(a, w)
         else:

@@ -101,3 +101,47 @@ def test_peer_wait_times_out_with_status_not_a_hang():
     assert torch.ones(4, device="cuda").sum().item() == 4.0      # context still healthy
     sm.world = 1
     sm.close()
+
+
+def _tp_worker(rank, world, port, tmp):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.parallel.tp_fused import TPWorkspace
+    Ms, K, N = 384, 512, 640
+    ws = TPWorkspace(dist.group.WORLD, Ms * K * 2, world * Ms * N * 2)
+    ok = True
+    for call in range(3):                       # three calls: exercises both buffer parities
+        g = torch.Generator(device=dev).manual_seed(50 + call)
+        xs = [torch.randn(Ms, K, device=dev, generator=g).to(torch.bfloat16) for _ in range(world)]
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        # all-gather -> GEMM: every rank contributes xs[rank]
+        y = ws.ag_gemm(xs[rank], w)
+        ref = torch.cat(xs).float() @ w.float().t()
+        ok &= ((y.float() - ref).norm() / ref.norm()).item() < 5e-3
+        # GEMM -> reduce-scatter: rank r holds a_r; the sum over ranks of a_r @ w^T, my row block
+        a_all = [torch.randn(world * Ms, K, device=dev, generator=g).to(torch.bfloat16) for _ in range(world)]
+        z = ws.gemm_rs(a_all[rank], w)
+        full = sum(a.float() @ w.float().t() for a in a_all)
+        refz = full[rank * Ms:(rank + 1) * Ms]
+        ok &= ((z.float() - refz).norm() / refz.norm()).item() < 1e-2
+    torch.cuda.synchronize()
+    native.check_status()
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"ok": bool(t.item())}, os.path.join(tmp, "tp.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_ag_gemm_and_gemm_rs_match_reference(tmp_path):
+    _need(2)
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    mp.spawn(_tp_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert torch.load(tmp_path / "tp.pt")["ok"]
