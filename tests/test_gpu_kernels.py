@@ -242,3 +242,29 @@ def test_gemm_cta_pair_kernel(M, N, K, a_mn, b_mn):
     ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
     assert _rel_err(c, ref) < 5e-3
     assert _rel_err(c32, ref + 1.0) < 1e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (384, 200, 512), (1024, 2048, 7168)])
+def test_fp8_blockscale_gemm_and_quantisers(M, N, K):
+    from hyper_parallel_b200.ops import fp8
+    torch.manual_seed(13)
+    x = (torch.randn(M, K, device=_dev()) * torch.rand(M, 1, device=_dev()) * 4).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=_dev()) * 0.05).to(torch.bfloat16)
+    aq, sa = fp8.quantize_act_1x128(x)
+    bq, sb = fp8.quantize_weight_128x128(w)
+    # quantisers agree with the PyTorch formulation
+    aq_r, sa_r = fp8.quantize_act_1x128(x.cpu())
+    bq_r, sb_r = fp8.quantize_weight_128x128(w.cpu())
+    assert torch.allclose(sa.cpu(), sa_r, rtol=1e-6) and torch.allclose(sb.cpu(), sb_r, rtol=1e-6)
+    assert (aq.cpu().float() != aq_r.float()).float().mean() < 1e-3      # rounding ties only
+    assert _rel_err(fp8.dequantize(aq, scale_act=sa), x) < 4e-2
+    # the GEMM equals the fp32 product of the dequantised operands
+    c = fp8.gemm_fp8(aq, sa, bq, sb)
+    native.check_status()
+    ref = fp8.dequantize(aq, scale_act=sa) @ fp8.dequantize(bq, scale_w=sb).t()
+    assert _rel_err(c, ref) < 5e-3
+    # and is close to the bf16 product
+    assert _rel_err(c, x.float() @ w.float().t()) < 6e-2
+    y = fp8.fp8_linear(x.requires_grad_(), w.requires_grad_())
+    y.sum().backward()
+    assert x.grad is not None and w.grad is not None
