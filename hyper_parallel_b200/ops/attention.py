@@ -3,6 +3,8 @@
 ``causal_attention(q[B,S,H,D], k[B,S,Hkv,D], v[B,S,Hkv,D]) -> [B,S,H,D]`` with
 grouped-query support.  The backend is chosen by ``HPB_ATTN``:
 
+* ``hpb``: this library's tcgen05 flash-attention kernels (``attention_sm100.cu``; head
+  dimension 128);
 * ``cudnn`` (default on CUDA): the fused cuDNN flash-attention graph through
   ``torch.nn.functional.scaled_dot_product_attention``;
 * ``flash``: the generic flash backend of the same call;
@@ -30,10 +32,46 @@ def _math_attention(q, k, v):
     return o.transpose(1, 2).to(q.dtype)
 
 
+def _strides_ok(t: torch.Tensor) -> bool:
+    return (t.stride(3) == 1 and t.stride(2) == t.shape[3] and t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
+
+
+def flash_attention_forward(q, k, v, causal: bool = True, scale: float = None):
+    """tcgen05 flash attention forward: ``(out [B,S,H,128] bf16, lse [B,H,S] fp32)``.
+
+    ``q/k/v`` may be views into a packed projection output (token and batch strides are free, the
+    128 head elements must be contiguous and heads 128 elements apart).
+    """
+    import ctypes
+    from . import native
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    assert D == 128 and q.dtype == torch.bfloat16 and k.shape[1] == S
+    q, k, v = [t if _strides_ok(t) else t.contiguous() for t in (q, k, v)]
+    lib = native.lib()
+    if not getattr(lib, "_hpb_fa_bound", False):
+        vp, ci, cll, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.hpb_flash_attn_fwd.argtypes = [vp, cll, cll, vp, cll, cll, vp, cll, cll, vp, vp, ci, ci, ci, ci, cf, ci,
+                                           vp, vp]
+        lib.hpb_flash_attn_fwd.restype = ci
+        lib._hpb_fa_bound = True
+    out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    rc = lib.hpb_flash_attn_fwd(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1),
+                                v.data_ptr(), v.stride(0), v.stride(1), out.data_ptr(), lse.data_ptr(), B, S, H, Hkv,
+                                float(scale if scale is not None else 1.0 / math.sqrt(D)), int(causal),
+                                native.status_word(q.device).data_ptr(), native.stream(q.device))
+    native.check(rc, "hpb_flash_attn_fwd")
+    return out, lse
+
+
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     backend = os.environ.get("HPB_ATTN", "cudnn" if q.is_cuda else "math")
     if backend == "math" or not q.is_cuda:
         return _math_attention(q, k, v)
+    if backend == "hpb" and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
+        return _FlashAttention.apply(q, k, v)
     from torch.nn.attention import SDPBackend, sdpa_kernel
     H, Hkv = q.shape[2], k.shape[2]
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
@@ -43,3 +81,59 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
     with sdpa_kernel(be):
         o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=(H != Hkv))
     return o.transpose(1, 2)
+
+
+def flash_attention_backward(q, k, v, out, lse, do, causal: bool = True, scale: float = None):
+    """tcgen05 flash attention backward: ``(dq, dk, dv)`` bf16, contiguous ``[B,S,H,128]``."""
+    import ctypes
+    from . import native
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    q, k, v, do = [t if _strides_ok(t) else t.contiguous() for t in (q, k, v, do)]
+    out = out.contiguous()
+    lib = native.lib()
+    if not getattr(lib, "_hpb_fa_bwd_bound", False):
+        vp, ci, cll, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        lib.hpb_flash_attn_bwd.argtypes = [vp, cll, cll, vp, cll, cll, vp, cll, cll, vp, vp, vp, cll, cll, vp, vp, vp,
+                                           vp, vp, ci, ci, ci, ci, cf, ci, vp, vp]
+        lib.hpb_flash_attn_bwd.restype = ci
+        lib._hpb_fa_bwd_bound = True
+    dev = q.device
+    dq = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=dev)
+    dk = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
+    dv = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
+    dq_acc = torch.empty((B, S, H, D), dtype=torch.float32, device=dev)
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+    rc = lib.hpb_flash_attn_bwd(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1),
+                                v.data_ptr(), v.stride(0), v.stride(1), out.data_ptr(), lse.data_ptr(),
+                                do.data_ptr(), do.stride(0), do.stride(1), dq.data_ptr(), dk.data_ptr(),
+                                dv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, S, H, Hkv,
+                                float(scale if scale is not None else 1.0 / math.sqrt(D)), int(causal),
+                                native.status_word(dev).data_ptr(), native.stream(dev))
+    native.check(rc, "hpb_flash_attn_bwd")
+    return dq, dk, dv
+
+
+class _FlashAttention(torch.autograd.Function):
+    """Forward and backward on this library's kernels (``HPB_ATTN_BWD=lib`` recomputes the backward
+    through the library call instead)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        out, lse = flash_attention_forward(q, k, v, causal=True)
+        ctx.save_for_backward(q, k, v, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse = ctx.saved_tensors
+        if os.environ.get("HPB_ATTN_BWD", "hpb") == "hpb":
+            return flash_attention_backward(q, k, v, out, lse, do, causal=True)
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        with torch.enable_grad():
+            qd, kd, vd = [t.detach().requires_grad_() for t in (q, k, v)]
+            with sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION]):
+                o = F.scaled_dot_product_attention(qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
+                                                   is_causal=True, enable_gqa=(q.shape[2] != k.shape[2]))
+            dq, dk, dv = torch.autograd.grad(o, (qd, kd, vd), do.transpose(1, 2))
+        return dq, dk, dv

@@ -1,0 +1,959 @@
+// Flash attention for sm_100a (head dimension 128, bf16, optional causal mask, grouped-query
+// heads): S = Q K^T and O += P V run on tcgen05 with the score tile and the output accumulator
+// in tensor memory; the online softmax runs on CUDA cores between the two.
+//
+// Forward kernel.  One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that
+// ping-pong: while the softmax warps of tile 0 turn S0 into P0, the tensor core computes
+// S1 / O1 and vice versa.
+//
+//   warp 0      TMA producer: Q0, Q1 once; then K_0, V_0, K_1, V_1, ... through a 3-stage ring
+//   warp 1      MMA issuer (one elected thread): S_t = Q_t K_j^T, O_t += P_t V_j
+//   warps 2-5   softmax of tile 0: thread = row; reads S from TMEM, writes bf16 P into
+//   warps 6-9   softmax of tile 1      swizzled shared memory (A operand of the PV product)
+//
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.
+// The row maximum is only raised when it grows by more than 2^8 (P stays bounded by 256 and
+// the accumulator in TMEM is rescaled rarely); the result is exact after the final 1/l.
+//
+// All tiles are [128 rows x 128 bf16] stored as two 64-column halves of 16 KB with the 128-byte
+// swizzle, rows contiguous by 128 B -- the layout serves as K-major operand (Q, K, P) and as
+// MN-major operand (V) alike.
+//
+// Every wait is bounded; on expiry a status code is recorded and all roles unwind.
+#include "sm100_common.cuh"
+
+#include <mutex>
+
+namespace hpb {
+namespace fa {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int HD = 128;
+constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KB
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int KV_STAGES = 3;
+constexpr int FWD_THREADS = 320;
+constexpr int FWD_SMEM = (2 + KV_STAGES + 2) * TILE_BYTES + 1024 + 256;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdParams {
+  int B, S, Hq, Hkv;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  __nv_bfloat16* O;  // [B, S, Hq, 128] contiguous
+  float* lse;        // [B, Hq, S] natural-log sum-exp
+  int* status;
+};
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Number of key tiles that query tile `qt` (tile index) attends to.
+__device__ __forceinline__ int kv_tiles_for(int qt, int S, int causal) {
+  const int total = (S + BN - 1) / BN;
+  if (qt * BM >= S) return 0;
+  return causal ? min(total, qt + 1) : total;
+}
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;                                  // 2 tiles
+  uint8_t* sKV = smem + 2 * TILE_BYTES;                // KV_STAGES tiles
+  uint8_t* sP = sKV + KV_STAGES * TILE_BYTES;          // 2 tiles
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
+  uint64_t* kv_full = q_full + 1;           // [KV_STAGES]
+  uint64_t* kv_empty = kv_full + KV_STAGES; // [KV_STAGES]
+  uint64_t* s_full = kv_empty + KV_STAGES;  // [2]
+  uint64_t* p_full = s_full + 2;            // [2]
+  uint64_t* pv_done = p_full + 2;           // [2]
+  uint64_t* drain_bar = pv_done + 2;        // [1]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // heavy (late) query blocks first: they have the most key tiles under a causal mask
+  const int num_pairs = (p.S + 2 * BM - 1) / (2 * BM);
+  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  const int n0 = kv_tiles_for(2 * pair, p.S, p.causal);
+  const int n1 = kv_tiles_for(2 * pair + 1, p.S, p.causal);
+  const int n_kv = max(n0, n1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 4);   // one arrive per softmax warp
+      mbar_init(&pv_done[t], 1);
+    }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(sQ + t * TILE_BYTES + h * HALF_BYTES, &tmap_q, q_full, head * HD + h * 64,
+                      (2 * pair + t) * BM, batch);
+      int issued = 0;
+      bool ok = true;
+      for (int idx = 0; idx < 2 * n_kv && ok; ++idx) {
+        const int stage = idx % KV_STAGES;
+        const uint32_t phase = (idx / KV_STAGES) & 1;
+        ok = mbar_wait_bounded(&kv_empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier,
+                               blockIdx.x);
+        if (!ok) break;
+        const int j = idx >> 1;
+        const CUtensorMap* tm = (idx & 1) ? &tmap_v : &tmap_k;
+        uint8_t* dst = sKV + stage * TILE_BYTES;
+        mbar_arrive_expect_tx(&kv_full[stage], TILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(dst + h * HALF_BYTES, tm, &kv_full[stage], kv_head * HD + h * 64, j * BN, batch);
+        ++issued;
+      }
+      if (!ok) {
+        // wait (bounded) for the copies already issued, so that none lands after the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(q_full, 0) && globaltimer_ns() - t0 < 100000000ull) {}
+        for (int b = 1; b <= min(issued, KV_STAGES); ++b) {
+          const int idx = issued - b;
+          const uint64_t t1 = globaltimer_ns();
+          while (!mbar_try_wait(&kv_full[idx % KV_STAGES], (idx / KV_STAGES) & 1) &&
+                 globaltimer_ns() - t1 < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_s = make_idesc(1, 1, 0, 0, BM, BN);   // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_o = make_idesc(1, 1, 0, 1, BM, HD);   // P (K-major) x V (MN-major)
+      const uint32_t q_addr = smem_u32(sQ), kv_addr = smem_u32(sKV), p_addr = smem_u32(sP);
+      const int nt[2] = {n0, n1};
+      bool ok = true;
+      auto wait_kv = [&](int idx) {
+        return mbar_wait_bounded(&kv_full[idx % KV_STAGES], (idx / KV_STAGES) & 1, abort_flag, p.status,
+                                 kTimeoutFullBarrier, blockIdx.x);
+      };
+      auto issue_s = [&](int t, int idx) {
+        const uint32_t qa = q_addr + t * TILE_BYTES;
+        const uint32_t ka = kv_addr + (idx % KV_STAGES) * TILE_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_base + t * BN, make_smem_desc_sw128(qa + kb * HALF_BYTES + kk * 32, 0, 1024),
+                     make_smem_desc_sw128(ka + kb * HALF_BYTES + kk * 32, 0, 1024), idesc_s,
+                     (kb | kk) ? 1u : 0u);
+        umma_commit(&s_full[t]);
+      };
+      auto issue_pv = [&](int t, int idx, bool accumulate) {
+        const uint32_t pa = p_addr + t * TILE_BYTES;
+        const uint32_t va = kv_addr + (idx % KV_STAGES) * TILE_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            // P: kv index is the contraction (64-wide halves, +32 B per 16); V: 16 kv rows = 2048 B,
+            // the two 64-wide halves of the head dimension are HALF_BYTES apart (leading offset)
+            umma_f16(tmem_base + 2 * BN + t * HD,
+                     make_smem_desc_sw128(pa + kb * HALF_BYTES + kk * 32, 0, 1024),
+                     make_smem_desc_sw128(va + (kb * 4 + kk) * 2048, HALF_BYTES, 1024), idesc_o,
+                     (accumulate || (kb | kk)) ? 1u : 0u);
+        umma_commit(&pv_done[t]);
+      };
+      ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
+      if (ok) ok = wait_kv(0);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (nt[t] > 0) issue_s(t, 0);
+        umma_commit(&kv_empty[0]);                           // K_0 is free once both S_t(K_0) retire
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        ok = wait_kv(2 * j + 1);                      // V_j
+        if (ok && j + 1 < n_kv) ok = wait_kv(2 * j + 2);  // K_{j+1}
+        if (!ok) break;
+        tc_fence_after();
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j < nt[t]) {
+            ok = mbar_wait_bounded(&p_full[t], j & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, 2 * j + 1, j > 0);
+          }
+          if (j + 1 < nt[t]) issue_s(t, 2 * j + 2);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[(2 * j + 1) % KV_STAGES]);                      // V_j
+        if (j + 1 < n_kv) umma_commit(&kv_empty[(2 * j + 2) % KV_STAGES]);    // K_{j+1}: both S_t issued above
+      }
+      if (!ok) {
+        umma_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 100000000ull) {}
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax --
+    const int t = (warp - 2) >> 2;            // query tile of this warpgroup
+    const int quarter = warp & 3;             // TMEM lane quarter this warp may access
+    const int row = quarter * 32 + lane;      // row inside the tile
+    const int n_t = t == 0 ? n0 : n1;
+    const int q_row = (2 * pair + t) * BM + row;   // sequence position of this thread's query
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + t * BN + lane_off;
+    const uint32_t o_addr = tmem_base + 2 * BN + t * HD + lane_off;
+    uint8_t* p_row = sP + t * TILE_BYTES + row * 128;
+    const int sw = row & 7;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_t && ok; ++j) {
+      ok = mbar_wait_bounded(&s_full[t], j & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+      if (!ok) break;
+      tc_fence_after();
+      const int k0 = j * BN;
+      // columns [0, limit) of this tile are visible to this row
+      int limit = p.S - k0;
+      if (p.causal) limit = min(limit, q_row - k0 + 1);
+      const bool masked = limit < BN;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        if (!masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      float alpha = 1.f;
+      bool need = false;
+      if (j == 0) {
+        m = m_new;
+      } else if (m_new > m + kRescaleThreshold) {
+        need = true;
+        alpha = fast_exp2(m - m_new);
+        m = m_new;
+        l *= alpha;
+      }
+      if (j > 0) {
+        // the previous P V product has retired: P buffer reusable, accumulator up to date
+        ok = mbar_wait_bounded(&pv_done[t], (j - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(o_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(o_addr + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      // pass 2: P = 2^(s * scale - m), row sum, bf16 into the swizzled A-operand tile
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(s_addr + c * 32, r);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+          if (masked && c * 32 + i >= limit) e = 0.f;
+          pr[i] = e;
+          l += e;
+        }
+        uint8_t* blk = p_row + (c >> 1) * HALF_BYTES;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v;
+          __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(pr[8 * q4 + 2 * e], pr[8 * q4 + 2 * e + 1]);
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ sw) << 4)) = v;
+        }
+      }
+      fence_proxy_async();     // generic-proxy writes of P -> visible to the tensor core's reads
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (ok && n_t > 0) {
+      ok = mbar_wait_bounded(&pv_done[t], (n_t - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.f / l;
+        const bool live = q_row < p.S;
+        __nv_bfloat16* dst = p.O + ((static_cast<int64_t>(batch) * p.S + q_row) * p.Hq + head) * HD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                vb[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * q4 + 2 * e]) * inv,
+                                              __uint_as_float(r[8 * q4 + 2 * e + 1]) * inv);
+              reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+            }
+          }
+        }
+        if (live)
+          p.lse[(static_cast<int64_t>(batch) * p.Hq + head) * p.S + q_row] =
+              (m + log2f(l)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
+// ============================================================ backward ========
+// One CTA owns one 128-row key/value tile of one (batch, kv head) and walks over the query heads
+// of its group and their 64-row query tiles.  Everything is computed transposed, so that the
+// softmax threads (thread = key row) write the A operands of the following products as plain
+// 128-byte rows:
+//
+//   S^T  = K Q^T            [kv 128 x q 64]   tensor memory (double buffered)
+//   dP^T = V dO^T           [kv 128 x q 64]   tensor memory (double buffered)
+//   P^T  = exp2(S^T * c - lse),  dS^T = P^T o (dP^T - D)      -> bf16, shared memory
+//   dV  += P^T dO           [kv 128 x d 128]  tensor memory, accumulated over the whole walk
+//   dK  += dS^T Q           [kv 128 x d 128]  tensor memory, accumulated over the whole walk
+//   dQ^T = K^T dS^T         [d 128 x q 64]    tensor memory (in the S^T buffer just consumed),
+//                                             added to the fp32 dQ in global memory with
+//                                             coalesced reductions (lane = head element)
+//
+//   warp 0      TMA producer: K, V once; (Q_i, dO_i) through a 3-stage ring
+//   warp 1      MMA issuer
+//   warps 2-5   softmax / dS
+//   warps 6-9   dQ reduction; both groups write dV / dK at the end
+constexpr int BQ = 64;                        // query rows per step
+constexpr int QDO_STAGES = 3;
+constexpr int QTILE_BYTES = BQ * HD * 2;      // 16 KB
+constexpr int PT_BYTES = BN * BQ * 2;         // 16 KB
+constexpr int BWD_THREADS = 320;
+constexpr int BWD_SMEM = 2 * TILE_BYTES + QDO_STAGES * 2 * QTILE_BYTES + 2 * 2 * PT_BYTES + 2 * 2 * BQ * 4 + 1024 + 256;
+
+struct BwdParams {
+  int B, S, Hq, Hkv;
+  float scale, scale_log2;
+  int causal;
+  const float* lse;    // [B, Hq, S]
+  const float* delta;  // [B, Hq, S]  rowsum(dO o O)
+  float* dQ;           // [B, S, Hq, 128] fp32, zero-initialised
+  __nv_bfloat16* dK;   // [B, S, Hkv, 128]
+  __nv_bfloat16* dV;   // [B, S, Hkv, 128]
+  int* status;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void red_add_f32(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                 const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQdO = sV + TILE_BYTES;                            // per stage: Q (16 KB) | dO (16 KB)
+  uint8_t* sPT = sQdO + QDO_STAGES * 2 * QTILE_BYTES;         // per buffer: P^T (16 KB) | dS^T (16 KB)
+  float* sStat = reinterpret_cast<float*>(sPT + 2 * 2 * PT_BYTES);   // [2][2][64]: lse*log2e, delta
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(sStat + 2 * 2 * BQ);
+  uint64_t* qdo_full = kv_full + 1;              // [QDO_STAGES]
+  uint64_t* qdo_empty = qdo_full + QDO_STAGES;   // [QDO_STAGES]
+  uint64_t* st_full = qdo_empty + QDO_STAGES;    // [2]  S^T and dP^T of a step are complete
+  uint64_t* ds_full = st_full + 2;               // [2]  P^T / dS^T written (4 warp arrivals)
+  uint64_t* pt_free = ds_full + 2;               // [2]  products reading P^T / dS^T retired
+  uint64_t* dq_full = pt_free + 2;               // [2]
+  uint64_t* dq_drained = dq_full + 2;            // [2]  (4 warp arrivals)
+  uint64_t* acc_full = dq_drained + 2;           // [1]
+  uint64_t* drain_bar = acc_full + 1;            // [1]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kv_tiles = (p.S + BN - 1) / BN;
+  const int jt = p.causal ? static_cast<int>(blockIdx.x) : num_kv_tiles - 1 - static_cast<int>(blockIdx.x);
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = jt * BN;
+  const int nq = (p.S + BQ - 1) / BQ;
+  const int i_start = p.causal ? (k0 / BQ) : 0;       // first query tile that sees this key tile
+  const int per_head = nq - i_start;
+  const int n_it = per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < QDO_STAGES; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&st_full[b], 1);
+      mbar_init(&ds_full[b], 4);
+      mbar_init(&pt_free[b], 1);
+      mbar_init(&dq_full[b], 1);
+      mbar_init(&dq_drained[b], 4);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  // tensor-memory columns
+  constexpr uint32_t COL_ST = 0;      // 2 x 64   (S^T, later dQ^T)
+  constexpr uint32_t COL_DPT = 128;   // 2 x 64
+  constexpr uint32_t COL_DV = 256;    // 128
+  constexpr uint32_t COL_DK = 384;    // 128
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        tma_load_3d(sK + h * HALF_BYTES, &tmap_k, kv_full, kv_head * HD + h * 64, k0, batch);
+        tma_load_3d(sV + h * HALF_BYTES, &tmap_v, kv_full, kv_head * HD + h * 64, k0, batch);
+      }
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int stage = it % QDO_STAGES;
+        const uint32_t phase = (it / QDO_STAGES) & 1;
+        ok = mbar_wait_bounded(&qdo_empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier,
+                               blockIdx.x);
+        if (!ok) break;
+        const int head = kv_head * group + it / per_head;
+        const int q0 = (i_start + it % per_head) * BQ;
+        uint8_t* dq = sQdO + stage * 2 * QTILE_BYTES;
+        mbar_arrive_expect_tx(&qdo_full[stage], 2 * QTILE_BYTES);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          tma_load_3d(dq + h * (QTILE_BYTES / 2), &tmap_q, &qdo_full[stage], head * HD + h * 64, q0, batch);
+          tma_load_3d(dq + QTILE_BYTES + h * (QTILE_BYTES / 2), &tmap_do, &qdo_full[stage], head * HD + h * 64,
+                      q0, batch);
+        }
+        ++issued;
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(kv_full, 0) && globaltimer_ns() - t0 < 100000000ull) {}
+        for (int b = 1; b <= min(issued, QDO_STAGES); ++b) {
+          const int it = issued - b;
+          const uint64_t t1 = globaltimer_ns();
+          while (!mbar_try_wait(&qdo_full[it % QDO_STAGES], (it / QDO_STAGES) & 1) &&
+                 globaltimer_ns() - t1 < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_st = make_idesc(1, 1, 0, 0, BN, BQ);    // K (K-major) x Q (K-major)
+      constexpr uint32_t idesc_acc = make_idesc(1, 1, 0, 1, BN, HD);   // P^T (K-major) x dO (MN-major)
+      constexpr uint32_t idesc_dq = make_idesc(1, 1, 1, 1, HD, BQ);    // K^T (MN-major) x dS^T (MN-major)
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdO),
+                     pt_addr = smem_u32(sPT);
+      bool ok = true;
+      // S^T(it) and dP^T(it) into buffer it & 1
+      auto issue_scores = [&](int it) {
+        const int b = it & 1;
+        const uint32_t qa = qdo_addr + (it % QDO_STAGES) * 2 * QTILE_BYTES;
+        const uint32_t doa = qa + QTILE_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_base + COL_ST + b * BQ, make_smem_desc_sw128(k_addr + kb * HALF_BYTES + kk * 32, 0, 1024),
+                     make_smem_desc_sw128(qa + kb * (QTILE_BYTES / 2) + kk * 32, 0, 1024), idesc_st,
+                     (kb | kk) ? 1u : 0u);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_base + COL_DPT + b * BQ, make_smem_desc_sw128(v_addr + kb * HALF_BYTES + kk * 32, 0, 1024),
+                     make_smem_desc_sw128(doa + kb * (QTILE_BYTES / 2) + kk * 32, 0, 1024), idesc_st,
+                     (kb | kk) ? 1u : 0u);
+        umma_commit(&st_full[b]);
+      };
+      auto wait_qdo = [&](int it) {
+        return mbar_wait_bounded(&qdo_full[it % QDO_STAGES], (it / QDO_STAGES) & 1, abort_flag, p.status,
+                                 kTimeoutFullBarrier, blockIdx.x);
+      };
+      ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
+      for (int it = 0; it < 2 && it < n_it && ok; ++it) {
+        ok = wait_qdo(it);
+        if (ok) {
+          tc_fence_after();
+          issue_scores(it);
+        }
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int b = it & 1;
+        const uint32_t par = (it >> 1) & 1;
+        ok = mbar_wait_bounded(&ds_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t qa = qdo_addr + (it % QDO_STAGES) * 2 * QTILE_BYTES;
+        const uint32_t doa = qa + QTILE_BYTES;
+        const uint32_t pta = pt_addr + b * 2 * PT_BYTES;
+        const uint32_t dsa = pta + PT_BYTES;
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16(tmem_base + COL_DV, make_smem_desc_sw128(pta + kk * 32, 0, 1024),
+                   make_smem_desc_sw128(doa + kk * 2048, QTILE_BYTES / 2, 1024), idesc_acc, (it | kk) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16(tmem_base + COL_DK, make_smem_desc_sw128(dsa + kk * 32, 0, 1024),
+                   make_smem_desc_sw128(qa + kk * 2048, QTILE_BYTES / 2, 1024), idesc_acc, (it | kk) ? 1u : 0u);
+        umma_commit(&qdo_empty[it % QDO_STAGES]);
+        // dQ^T = K^T dS^T  (contraction over the 128 key rows: 8 steps of 16) into the S^T buffer
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + COL_ST + b * BQ, make_smem_desc_sw128(k_addr + kk * 2048, HALF_BYTES, 1024),
+                   make_smem_desc_sw128(dsa + kk * 2048, PT_BYTES, 1024), idesc_dq, kk ? 1u : 0u);
+        umma_commit(&dq_full[b]);
+        umma_commit(&pt_free[b]);
+        if (it + 2 < n_it) {
+          ok = wait_qdo(it + 2);
+          if (ok) ok = mbar_wait_bounded(&dq_drained[b], par, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(it + 2);
+        }
+      }
+      if (ok) umma_commit(acc_full);
+      if (!ok) {
+        umma_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 100000000ull) {}
+      }
+    }
+  } else {
+    const int wg = (warp - 2) >> 2;           // 0: softmax / dS, 1: dQ reduction
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;      // TMEM lane handled by this thread
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    if (wg == 0) {
+      // ------------------------------------------------------ softmax / dS --
+      const int tid = threadIdx.x - 64;       // 0..127 inside the group
+      const int kv_row = k0 + row;
+      const bool row_live = kv_row < p.S;
+      const int sw = row & 7;
+      auto load_stat = [&](int it) -> float {
+        // threads 0..63 fetch lse (scaled to log2), 64..127 fetch delta, of step `it`
+        if (it >= n_it) return 0.f;
+        const int head = kv_head * group + it / per_head;
+        const int q = (i_start + it % per_head) * BQ + (tid & 63);
+        if (q >= p.S) return tid < 64 ? INFINITY : 0.f;
+        const int64_t off = (static_cast<int64_t>(batch) * p.Hq + head) * p.S + q;
+        return tid < 64 ? p.lse[off] * 1.4426950408889634f : p.delta[off];
+      };
+      float stat_next = load_stat(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int b = it & 1;
+        const uint32_t par = (it >> 1) & 1;
+        float* stat = sStat + b * 2 * BQ;
+        stat[tid] = stat_next;                 // buffer b was last read two steps ago
+        stat_next = load_stat(it + 1);
+        named_bar_sync(1, 128);
+        ok = mbar_wait_bounded(&st_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        if (ok) ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+        if (!ok) break;
+        tc_fence_after();
+        const int q0 = (i_start + it % per_head) * BQ;
+        // visible iff key <= query:  column c >= kv_row - q0
+        const int cmin = p.causal ? kv_row - q0 : 0;
+        uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
+        uint8_t* ds_row = pt_row + PT_BYTES;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], rp[32];
+          tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, rs);
+          tmem_ld_32x32b_x32(tmem_base + COL_DPT + b * BQ + c * 32 + lane_off, rp);
+          tmem_ld_wait();
+          float pv[32], dv[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -stat[col]));
+            if (!row_live || col < cmin) e = 0.f;
+            pv[i] = e;
+            dv[i] = e * (__uint_as_float(rp[i]) - stat[BQ + col]);
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 a, d;
+            __nv_bfloat162* ab = reinterpret_cast<__nv_bfloat162*>(&a);
+            __nv_bfloat162* db = reinterpret_cast<__nv_bfloat162*>(&d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              ab[e] = __floats2bfloat162_rn(pv[8 * q4 + 2 * e], pv[8 * q4 + 2 * e + 1]);
+              db[e] = __floats2bfloat162_rn(dv[8 * q4 + 2 * e], dv[8 * q4 + 2 * e + 1]);
+            }
+            const int chunk = c * 4 + q4;
+            *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) = a;
+            *reinterpret_cast<uint4*>(ds_row + ((chunk ^ sw) << 4)) = d;
+          }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_full[b]);
+      }
+    } else {
+      // ------------------------------------------------------ dQ reduction --
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int b = it & 1;
+        const uint32_t par = (it >> 1) & 1;
+        ok = mbar_wait_bounded(&dq_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        if (!ok) break;
+        tc_fence_after();
+        const int head = kv_head * group + it / per_head;
+        const int q0 = (i_start + it % per_head) * BQ;
+        // lane = head element d; column = query row
+        float* base = p.dQ + ((static_cast<int64_t>(batch) * p.S + q0) * p.Hq + head) * HD + row;
+        const int64_t qstride = static_cast<int64_t>(p.Hq) * HD;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int q = c * 32 + i;
+            if (q0 + q < p.S) red_add_f32(base + q * qstride, __uint_as_float(r[i]) * p.scale);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dq_drained[b]);
+      }
+    }
+    // ------------------------------------------------- dV / dK write-out --
+    if (ok && n_it > 0) {
+      ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+      if (ok) {
+        tc_fence_after();
+        const int kv_row = k0 + row;
+        const float mul = wg == 0 ? 1.f : p.scale;
+        __nv_bfloat16* dst = (wg == 0 ? p.dV : p.dK) +
+                             ((static_cast<int64_t>(batch) * p.S + kv_row) * p.Hkv + kv_head) * HD;
+        const uint32_t src = tmem_base + (wg == 0 ? COL_DV : COL_DK) + lane_off;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(src + c * 32, r);
+          tmem_ld_wait();
+          if (kv_row < p.S) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 v;
+              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                vb[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * q4 + 2 * e]) * mul,
+                                              __uint_as_float(r[8 * q4 + 2 * e + 1]) * mul);
+              reinterpret_cast<uint4*>(dst + c * 32)[q4] = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h) row of 128.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, int64_t do_batch_stride,
+                                  int64_t do_row_stride, const __nv_bfloat16* __restrict__ O,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<int64_t>(B) * S * H) return;
+  const int h = static_cast<int>(w % H);
+  const int64_t bs = w / H;
+  const int s = static_cast<int>(bs % S);
+  const int b = static_cast<int>(bs / S);
+  const uint2 a = *reinterpret_cast<const uint2*>(dO + b * do_batch_stride + s * do_row_stride + h * HD + lane * 4);
+  const uint2 o = *reinterpret_cast<const uint2*>(O + ((static_cast<int64_t>(b) * S + s) * H + h) * HD + lane * 4);
+  const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+  float acc = 0.f;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float2 x = __bfloat1622float2(ab[e]), y = __bfloat1622float2(ob[e]);
+    acc += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<int64_t>(b) * H + h) * S + s] = acc;
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n8) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(src)[2 * i], b = reinterpret_cast<const float4*>(src)[2 * i + 1];
+    uint4 v;
+    __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+    vb[0] = __floats2bfloat162_rn(a.x, a.y);
+    vb[1] = __floats2bfloat162_rn(a.z, a.w);
+    vb[2] = __floats2bfloat162_rn(b.x, b.y);
+    vb[3] = __floats2bfloat162_rn(b.z, b.w);
+    reinterpret_cast<uint4*>(dst)[i] = v;
+  }
+}
+
+}  // namespace fa
+
+// ------------------------------------------------------------------ host ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn fa_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// [B, S, cols] bf16 view with element strides (batch_stride, row_stride, 1); box = 64 x box_rows x 1.
+static int make_tmap_bsd(CUtensorMap* map, const void* ptr, int B, int S, int cols, int64_t batch_stride,
+                         int64_t row_stride, uint32_t box_rows = 128) {
+  EncodeTiledFn enc = fa_encode_fn();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+}  // namespace hpb
+
+using namespace hpb;
+
+// q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16: the head dimension contiguous, head stride 128,
+// row (token) and batch strides given in elements (so views into a packed qkv tensor work).
+// O [B, S, Hq, 128] contiguous bf16, lse [B, Hq, S] fp32.
+extern "C" int hpb_flash_attn_fwd(const void* q, long long q_batch_stride, long long q_row_stride, const void* k,
+                                  long long k_batch_stride, long long k_row_stride, const void* v,
+                                  long long v_batch_stride, long long v_row_stride, void* O, float* lse, int B,
+                                  int S, int Hq, int Hkv, float softmax_scale, int causal, int* status,
+                                  cudaStream_t stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -2;
+  if ((q_row_stride | k_row_stride | v_row_stride | q_batch_stride | k_batch_stride | v_batch_stride) & 7) return -2;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(O)) & 15)
+    return -2;
+  cudaFree(nullptr);
+  CUtensorMap tq, tk, tv;
+  int r = make_tmap_bsd(&tq, q, B, S, Hq * fa::HD, q_batch_stride, q_row_stride);
+  if (r) return r;
+  r = make_tmap_bsd(&tk, k, B, S, Hkv * fa::HD, k_batch_stride, k_row_stride);
+  if (r) return r;
+  r = make_tmap_bsd(&tv, v, B, S, Hkv * fa::HD, v_batch_stride, v_row_stride);
+  if (r) return r;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fa::flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa::FWD_SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  fa::FwdParams p;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.O = reinterpret_cast<__nv_bfloat16*>(O);
+  p.lse = lse;
+  p.status = status;
+  dim3 grid((S + 2 * fa::BM - 1) / (2 * fa::BM), Hq, B);
+  fa::flash_fwd_kernel<<<grid, fa::FWD_THREADS, fa::FWD_SMEM, stream>>>(tq, tk, tv, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Backward.  dO [B, S, Hq, 128] (strided like q), O / lse from the forward.  Outputs: dQ
+// [B, S, Hq, 128] bf16, dK / dV [B, S, Hkv, 128] bf16, all contiguous.  Workspace: dq_acc fp32
+// [B, S, Hq, 128] and delta fp32 [B, Hq, S]; dq_acc is cleared here.
+extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long long q_row_stride, const void* k,
+                                  long long k_batch_stride, long long k_row_stride, const void* v,
+                                  long long v_batch_stride, long long v_row_stride, const void* O, const float* lse,
+                                  const void* dO, long long do_batch_stride, long long do_row_stride, void* dQ,
+                                  void* dK, void* dV, float* dq_acc, float* delta, int B, int S, int Hq, int Hkv,
+                                  float softmax_scale, int causal, int* status, cudaStream_t stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -2;
+  if ((q_row_stride | k_row_stride | v_row_stride | do_row_stride | q_batch_stride | k_batch_stride |
+       v_batch_stride | do_batch_stride) & 7)
+    return -2;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dQ) | reinterpret_cast<uintptr_t>(dK) |
+       reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(O) | reinterpret_cast<uintptr_t>(dq_acc)) & 15)
+    return -2;
+  cudaFree(nullptr);
+  CUtensorMap tq, tdo, tk, tv;
+  int r = make_tmap_bsd(&tq, q, B, S, Hq * fa::HD, q_batch_stride, q_row_stride, fa::BQ);
+  if (r) return r;
+  r = make_tmap_bsd(&tdo, dO, B, S, Hq * fa::HD, do_batch_stride, do_row_stride, fa::BQ);
+  if (r) return r;
+  r = make_tmap_bsd(&tk, k, B, S, Hkv * fa::HD, k_batch_stride, k_row_stride);
+  if (r) return r;
+  r = make_tmap_bsd(&tv, v, B, S, Hkv * fa::HD, v_batch_stride, v_row_stride);
+  if (r) return r;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fa::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fa::BWD_SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  const int64_t nq = static_cast<int64_t>(B) * S * Hq * fa::HD;
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, nq * sizeof(float), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  {
+    const int64_t warps = static_cast<int64_t>(B) * S * Hq;
+    const int threads = 256;
+    const int64_t blocks = (warps * 32 + threads - 1) / threads;
+    fa::attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(dO), do_batch_stride, do_row_stride,
+        reinterpret_cast<const __nv_bfloat16*>(O), delta, B, S, Hq);
+  }
+  fa::BwdParams p;
+  p.B = B; p.S = S; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale = softmax_scale;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.lse = lse;
+  p.delta = delta;
+  p.dQ = dq_acc;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dK);
+  p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
+  p.status = status;
+  dim3 grid((S + fa::BN - 1) / fa::BN, Hkv, B);
+  fa::flash_bwd_kernel<<<grid, fa::BWD_THREADS, fa::BWD_SMEM, stream>>>(tq, tdo, tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  fa::f32_to_bf16_kernel<<<1184, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dQ), nq / 8);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -162,8 +162,12 @@ struct AdamArgs {
   float lr, b1, b2, eps, wd, bc1, bc2, grad_scale;
 };
 
+// Launched with 512 threads; the bound of 768 caps the kernel at 80 registers per thread, so
+// that a CTA (40 K registers) fits beside a persistent GEMM CTA (192 threads x 96 registers)
+// in the 64 K register file of an SM -- otherwise the 8-peer instance would need the whole
+// file and could only run in the gaps between GEMM launches.
 template <int N>  // N > 0: compile-time peer count (loads fully unrolled); N == 0: runtime `n`
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(768)
 fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict__ segs,
                       int num_segs, float* __restrict__ master, float* __restrict__ m,
                       float* __restrict__ v, __nv_bfloat16* __restrict__ param_shard, AdamArgs a,

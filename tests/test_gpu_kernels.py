@@ -268,3 +268,51 @@ def test_fp8_blockscale_gemm_and_quantisers(M, N, K):
     y = fp8.fp8_linear(x.requires_grad_(), w.requires_grad_())
     y.sum().backward()
     assert x.grad is not None and w.grad is not None
+
+
+def _attn_oracle(q, k, v, causal):
+    B, S, H, D = q.shape
+    rep = H // k.shape[2]
+    qf, kf, vf = q.float().transpose(1, 2), k.float().transpose(1, 2), v.float().transpose(1, 2)
+    kf, vf = kf.repeat_interleave(rep, 1), vf.repeat_interleave(rep, 1)
+    s = qf @ kf.transpose(-1, -2) / D ** 0.5
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    return (torch.softmax(s, -1) @ vf).transpose(1, 2), torch.logsumexp(s, -1)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,causal", [(1, 128, 1, 1, True), (1, 256, 2, 1, True), (2, 1024, 4, 2, True),
+                                              (1, 384, 2, 2, False), (1, 200, 2, 1, True), (1, 2048, 8, 2, True)])
+def test_flash_attention_forward(B, S, H, Hkv, causal):
+    from hyper_parallel_b200.ops.attention import flash_attention_forward
+    torch.manual_seed(5)
+    qkv = torch.randn(B, S, (H + 2 * Hkv) * 128, device=_dev(), dtype=torch.bfloat16)
+    q = qkv[..., :H * 128].view(B, S, H, 128)                       # strided views of a packed projection
+    k = qkv[..., H * 128:(H + Hkv) * 128].view(B, S, Hkv, 128)
+    v = qkv[..., (H + Hkv) * 128:].view(B, S, Hkv, 128)
+    q = q * 3.0                                                     # sharper softmax: exercises the rescale path
+    out, lse = flash_attention_forward(q, k, v, causal=causal)
+    native.check_status()
+    ref, ref_lse = _attn_oracle(q, k, v, causal)
+    assert _rel_err(out, ref) < 1.5e-2
+    assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,causal", [(1, 128, 1, 1, True), (1, 256, 2, 1, True), (2, 1024, 4, 2, True),
+                                              (1, 384, 2, 2, False), (1, 200, 2, 1, True)])
+def test_flash_attention_backward(B, S, H, Hkv, causal):
+    from hyper_parallel_b200.ops.attention import flash_attention_backward, flash_attention_forward
+    torch.manual_seed(6)
+    q = torch.randn(B, S, H, 128, device=_dev(), dtype=torch.bfloat16)
+    k = torch.randn(B, S, Hkv, 128, device=_dev(), dtype=torch.bfloat16)
+    v = torch.randn(B, S, Hkv, 128, device=_dev(), dtype=torch.bfloat16)
+    do = torch.randn(B, S, H, 128, device=_dev(), dtype=torch.bfloat16)
+    out, lse = flash_attention_forward(q, k, v, causal=causal)
+    dq, dk, dv = flash_attention_backward(q, k, v, out, lse, do, causal=causal)
+    native.check_status()
+    qf, kf, vf = [t.float().requires_grad_() for t in (q, k, v)]
+    ref, _ = _attn_oracle(qf, kf, vf, causal)
+    rq, rk, rv = torch.autograd.grad(ref, (qf, kf, vf), do.float())
+    assert _rel_err(dv, rv) < 2e-2
+    assert _rel_err(dk, rk) < 2e-2
+    assert _rel_err(dq, rq) < 2e-2
