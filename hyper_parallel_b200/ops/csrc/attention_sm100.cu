@@ -421,17 +421,19 @@ struct BwdParams {
   int* status;
 };
 
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void red_add_f32(float* addr, float v) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
+// fp32 tile in shared memory (dense rows) added to global memory by the TMA unit
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int x, int y, int z) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(m)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
 }
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                 const BwdParams p) {
+                 const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -448,7 +450,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* pt_free = ds_full + 2;               // [2]  products reading P^T / dS^T retired
   uint64_t* dq_full = pt_free + 2;               // [2]
   uint64_t* dq_drained = dq_full + 2;            // [2]  (4 warp arrivals)
-  uint64_t* acc_full = dq_drained + 2;           // [1]
+  uint64_t* stat_full = dq_drained + 2;          // [2]  lse / delta of a step staged (4 warp arrivals)
+  uint64_t* stage_full = stat_full + 2;          // [2]  fp32 dQ tile staged (4 warp arrivals)
+  uint64_t* acc_full = stage_full + 2;           // [1]
   uint64_t* drain_bar = acc_full + 1;            // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
@@ -475,9 +479,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int b = 0; b < 2; ++b) {
       mbar_init(&st_full[b], 1);
       mbar_init(&ds_full[b], 4);
-      mbar_init(&pt_free[b], 1);
+      mbar_init(&pt_free[b], 1);     // arrived by the dQ group once the TMA reduce has read the buffer
       mbar_init(&dq_full[b], 1);
       mbar_init(&dq_drained[b], 4);
+      mbar_init(&stat_full[b], 4);
+      mbar_init(&stage_full[b], 4);
     }
     mbar_init(acc_full, 1);
     mbar_init(drain_bar, 1);
@@ -487,6 +493,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tma_prefetch_desc(&tmap_do);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, 512);
@@ -610,7 +617,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           umma_f16(tmem_base + COL_ST + b * BQ, make_smem_desc_sw128(k_addr + kk * 2048, HALF_BYTES, 1024),
                    make_smem_desc_sw128(dsa + kk * 2048, PT_BYTES, 1024), idesc_dq, kk ? 1u : 0u);
         umma_commit(&dq_full[b]);
-        umma_commit(&pt_free[b]);
         if (it + 2 < n_it) {
           ok = wait_qdo(it + 2);
           if (ok) ok = mbar_wait_bounded(&dq_drained[b], par, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
@@ -654,8 +660,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         float* stat = sStat + b * 2 * BQ;
         stat[tid] = stat_next;                 // buffer b was last read two steps ago
         stat_next = load_stat(it + 1);
-        named_bar_sync(1, 128);
-        ok = mbar_wait_bounded(&st_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stat_full[b]);
+        ok = mbar_wait_bounded(&stat_full[b], par, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
+        if (ok) ok = mbar_wait_bounded(&st_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
         if (ok) ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
         tc_fence_after();
@@ -672,12 +680,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_ld_wait();
           float pv[32], dv[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = c * 32 + i;
-            float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -stat[col]));
-            if (!row_live || col < cmin) e = 0.f;
-            pv[i] = e;
-            dv[i] = e * (__uint_as_float(rp[i]) - stat[BQ + col]);
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 ls = *reinterpret_cast<const float4*>(stat + c * 32 + 4 * i4);
+            const float4 dl = *reinterpret_cast<const float4*>(stat + BQ + c * 32 + 4 * i4);
+            const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+            for (int e4 = 0; e4 < 4; ++e4) {
+              const int i = 4 * i4 + e4;
+              const int col = c * 32 + i;
+              float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lsv[e4]));
+              if (!row_live || col < cmin) e = 0.f;
+              pv[i] = e;
+              dv[i] = e * (__uint_as_float(rp[i]) - dlv[e4]);
+            }
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -701,6 +716,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     } else {
       // ------------------------------------------------------ dQ reduction --
+      // dQ^T (lane = head element, column = query row) is transposed through the P^T / dS^T
+      // buffer of the same step -- free once the dQ product has retired -- as a dense fp32
+      // [64 query rows x 128] tile, which one TMA reduce adds to the fp32 dQ in global memory.
+      const int tid = threadIdx.x - 192;      // 0..127 inside the group
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -709,24 +728,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         const int head = kv_head * group + it / per_head;
         const int q0 = (i_start + it % per_head) * BQ;
-        // lane = head element d; column = query row
-        float* base = p.dQ + ((static_cast<int64_t>(batch) * p.S + q0) * p.Hq + head) * HD + row;
-        const int64_t qstride = static_cast<int64_t>(p.Hq) * HD;
+        float* stage = reinterpret_cast<float*>(sPT + b * 2 * PT_BYTES) + row;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int q = c * 32 + i;
-            if (q0 + q < p.S) red_add_f32(base + q * qstride, __uint_as_float(r[i]) * p.scale);
-          }
+          for (int i = 0; i < 32; ++i) stage[(c * 32 + i) * HD] = __uint_as_float(r[i]) * p.scale;
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&dq_drained[b]);
+        if (lane == 0) mbar_arrive(&dq_drained[b]);   // the S^T buffer may be overwritten
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stage_full[b]);
+        if (tid == 0) {
+          ok = mbar_wait_bounded(&stage_full[b], par, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
+          if (!ok) break;
+          tma_reduce_add_3d(&tmap_dq, sPT + b * 2 * PT_BYTES, head * HD, q0, batch);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(&pt_free[b]);                   // the softmax group may write P^T / dS^T again
+        }
       }
+      if (tid == 0) tma_store_wait<0>();
     }
     // ------------------------------------------------- dV / dK write-out --
     if (ok && n_it > 0) {
@@ -951,7 +977,20 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
   p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
   p.status = status;
   dim3 grid((S + fa::BN - 1) / fa::BN, Hkv, B);
-  fa::flash_bwd_kernel<<<grid, fa::BWD_THREADS, fa::BWD_SMEM, stream>>>(tq, tdo, tk, tv, p);
+  CUtensorMap tdq;
+  {
+    EncodeTiledFn enc = fa_encode_fn();
+    if (enc == nullptr) return -1;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(Hq) * fa::HD, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(Hq) * fa::HD * 4, static_cast<cuuint64_t>(S) * Hq * fa::HD * 4};
+    cuuint32_t box[3] = {fa::HD, fa::BQ, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult cr = enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return static_cast<int>(cr);
+  }
+  fa::flash_bwd_kernel<<<grid, fa::BWD_THREADS, fa::BWD_SMEM, stream>>>(tq, tdo, tk, tv, tdq, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   fa::f32_to_bf16_kernel<<<1184, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dQ), nq / 8);
