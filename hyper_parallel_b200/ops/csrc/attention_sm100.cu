@@ -61,6 +61,35 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// Descriptor of the same operand `bytes` further into shared memory (the start-address field
+// holds address >> 4 and cannot overflow inside the 228 KB window).
+__device__ __forceinline__ uint64_t desc_at(uint64_t desc, uint32_t bytes) {
+  return desc + static_cast<uint64_t>(bytes >> 4);
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
+}
+// packed pair arithmetic of sm_100: one instruction for two fp32 lanes
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -98,9 +127,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   // heavy (late) query blocks first: they have the most key tiles under a causal mask
   const int num_pairs = (p.S + 2 * BM - 1) / (2 * BM);
-  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x);
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
+  const int hb = static_cast<int>(blockIdx.x) % (p.Hq * p.B);
+  const int pair = num_pairs - 1 - static_cast<int>(blockIdx.x) / (p.Hq * p.B);
+  const int head = hb % p.Hq;
+  const int batch = hb / p.Hq;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int n0 = kv_tiles_for(2 * pair, p.S, p.causal);
   const int n1 = kv_tiles_for(2 * pair + 1, p.S, p.causal);
@@ -184,31 +214,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         return mbar_wait_bounded(&kv_full[idx % KV_STAGES], (idx / KV_STAGES) & 1, abort_flag, p.status,
                                  kTimeoutFullBarrier, blockIdx.x);
       };
+      const uint64_t q_desc = make_smem_desc_sw128(q_addr, 0, 1024);
+      const uint64_t k_desc = make_smem_desc_sw128(kv_addr, 0, 1024);            // K tile, K-major
+      const uint64_t v_desc = make_smem_desc_sw128(kv_addr, HALF_BYTES, 1024);   // V tile, MN-major
+      const uint64_t p_desc = make_smem_desc_sw128(p_addr, 0, 1024);
       auto issue_s = [&](int t, int idx) {
-        const uint32_t qa = q_addr + t * TILE_BYTES;
-        const uint32_t ka = kv_addr + (idx % KV_STAGES) * TILE_BYTES;
+        const uint64_t qa = desc_at(q_desc, t * TILE_BYTES);
+        const uint64_t ka = desc_at(k_desc, (idx % KV_STAGES) * TILE_BYTES);
+        const uint32_t d = tmem_base + t * BN;
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem_base + t * BN, make_smem_desc_sw128(qa + kb * HALF_BYTES + kk * 32, 0, 1024),
-                     make_smem_desc_sw128(ka + kb * HALF_BYTES + kk * 32, 0, 1024), idesc_s,
+            umma_f16(d, desc_at(qa, kb * HALF_BYTES + kk * 32), desc_at(ka, kb * HALF_BYTES + kk * 32), idesc_s,
                      (kb | kk) ? 1u : 0u);
         umma_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, int idx, bool accumulate) {
-        const uint32_t pa = p_addr + t * TILE_BYTES;
-        const uint32_t va = kv_addr + (idx % KV_STAGES) * TILE_BYTES;
+        // P: kv index is the contraction (64-wide halves, +32 B per 16); V: 16 kv rows = 2048 B,
+        // the two 64-wide halves of the head dimension are HALF_BYTES apart (leading offset)
+        const uint64_t pa = desc_at(p_desc, t * TILE_BYTES);
+        const uint64_t va = desc_at(v_desc, (idx % KV_STAGES) * TILE_BYTES);
+        const uint32_t d = tmem_base + 2 * BN + t * HD;
+        umma_f16(d, pa, va, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            // P: kv index is the contraction (64-wide halves, +32 B per 16); V: 16 kv rows = 2048 B,
-            // the two 64-wide halves of the head dimension are HALF_BYTES apart (leading offset)
-            umma_f16(tmem_base + 2 * BN + t * HD,
-                     make_smem_desc_sw128(pa + kb * HALF_BYTES + kk * 32, 0, 1024),
-                     make_smem_desc_sw128(va + (kb * 4 + kk) * 2048, HALF_BYTES, 1024), idesc_o,
-                     (accumulate || (kb | kk)) ? 1u : 0u);
+        for (int k8 = 1; k8 < 8; ++k8)
+          umma_f16(d, desc_at(pa, (k8 >> 2) * HALF_BYTES + (k8 & 3) * 32), desc_at(va, k8 * 2048), idesc_o, 1u);
         umma_commit(&pv_done[t]);
       };
       ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
@@ -266,23 +297,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       int limit = p.S - k0;
       if (p.causal) limit = min(limit, q_row - k0 + 1);
       const bool masked = limit < BN;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        if (!masked) {
+      // the whole score row of this thread (128 fp32) in one batch of loads
+      uint32_t sr[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sr + c * 32);
+      tmem_ld_wait();
+      if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i >= limit) sr[i] = 0xff800000u;   // -inf
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+      }
+      const float m_new = fmaxf(m, fmaxf(mx0, mx1) * p.scale_log2);
       float alpha = 1.f;
       bool need = false;
       if (j == 0) {
@@ -311,32 +342,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tmem_st_wait();
         }
       }
-      // pass 2: P = 2^(s * scale - m), row sum, bf16 into the swizzled A-operand tile
-      const float neg_m = (m == -INFINITY) ? 0.f : -m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        float pr[32];
+      // P = 2^(s * scale - m) (masked scores are -inf -> 0), row sum, bf16 into the swizzled A tile
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-m, -m);
+      float2 l2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-          if (masked && c * 32 + i >= limit) e = 0.f;
-          pr[i] = e;
-          l += e;
+      for (int c8 = 0; c8 < 16; ++c8) {     // 16 chunks of 8 columns = one 16-byte store each
+        uint4 v;
+        __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = c8 * 8 + 2 * e;
+          float2 x = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2);
+          x.x = fast_exp2(x.x);
+          x.y = fast_exp2(x.y);
+          l2 = add2(l2, x);
+          vb[e] = __floats2bfloat162_rn(x.x, x.y);
         }
-        uint8_t* blk = p_row + (c >> 1) * HALF_BYTES;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 v;
-          __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(pr[8 * q4 + 2 * e], pr[8 * q4 + 2 * e + 1]);
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ sw) << 4)) = v;
-        }
+        uint8_t* blk = p_row + (c8 >> 3) * HALF_BYTES;
+        *reinterpret_cast<uint4*>(blk + (((c8 & 7) ^ sw) << 4)) = v;
       }
+      l += l2.x + l2.y;
       fence_proxy_async();     // generic-proxy writes of P -> visible to the tensor core's reads
       tc_fence_before();
       __syncwarp();
@@ -459,10 +485,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_kv_tiles = (p.S + BN - 1) / BN;
-  const int jt = p.causal ? static_cast<int>(blockIdx.x) : num_kv_tiles - 1 - static_cast<int>(blockIdx.x);
-  const int kv_head = blockIdx.y;
-  const int batch = blockIdx.z;
+  const int hb = static_cast<int>(blockIdx.x) % (p.Hkv * p.B);
+  const int jt = static_cast<int>(blockIdx.x) / (p.Hkv * p.B);   // causal: low tiles have the longest walk
+  const int kv_head = hb % p.Hkv;
+  const int batch = hb / p.Hkv;
   const int group = p.Hq / p.Hkv;
   const int k0 = jt * BN;
   const int nq = (p.S + BQ - 1) / BQ;
@@ -558,25 +584,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdO),
                      pt_addr = smem_u32(sPT);
       bool ok = true;
+      const uint64_t k_desc = make_smem_desc_sw128(k_addr, 0, 1024);              // K as K-major A
+      const uint64_t v_desc = make_smem_desc_sw128(v_addr, 0, 1024);              // V as K-major A
+      const uint64_t kt_desc = make_smem_desc_sw128(k_addr, HALF_BYTES, 1024);    // K^T as MN-major A
+      const uint64_t qk_desc = make_smem_desc_sw128(qdo_addr, 0, 1024);           // Q / dO as K-major B
+      const uint64_t qm_desc = make_smem_desc_sw128(qdo_addr, QTILE_BYTES / 2, 1024);   // Q / dO as MN-major B
+      const uint64_t ptk_desc = make_smem_desc_sw128(pt_addr, 0, 1024);           // P^T / dS^T as K-major A
+      const uint64_t ptm_desc = make_smem_desc_sw128(pt_addr, PT_BYTES, 1024);    // dS^T as MN-major B
       // S^T(it) and dP^T(it) into buffer it & 1
       auto issue_scores = [&](int it) {
         const int b = it & 1;
-        const uint32_t qa = qdo_addr + (it % QDO_STAGES) * 2 * QTILE_BYTES;
-        const uint32_t doa = qa + QTILE_BYTES;
+        const uint64_t qa = desc_at(qk_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES);
+        const uint64_t doa = desc_at(qa, QTILE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem_base + COL_ST + b * BQ, make_smem_desc_sw128(k_addr + kb * HALF_BYTES + kk * 32, 0, 1024),
-                     make_smem_desc_sw128(qa + kb * (QTILE_BYTES / 2) + kk * 32, 0, 1024), idesc_st,
-                     (kb | kk) ? 1u : 0u);
+            umma_f16(tmem_base + COL_ST + b * BQ, desc_at(k_desc, kb * HALF_BYTES + kk * 32),
+                     desc_at(qa, kb * (QTILE_BYTES / 2) + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem_base + COL_DPT + b * BQ, make_smem_desc_sw128(v_addr + kb * HALF_BYTES + kk * 32, 0, 1024),
-                     make_smem_desc_sw128(doa + kb * (QTILE_BYTES / 2) + kk * 32, 0, 1024), idesc_st,
-                     (kb | kk) ? 1u : 0u);
+            umma_f16(tmem_base + COL_DPT + b * BQ, desc_at(v_desc, kb * HALF_BYTES + kk * 32),
+                     desc_at(doa, kb * (QTILE_BYTES / 2) + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
         umma_commit(&st_full[b]);
       };
       auto wait_qdo = [&](int it) {
@@ -597,25 +628,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         ok = mbar_wait_bounded(&ds_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t qa = qdo_addr + (it % QDO_STAGES) * 2 * QTILE_BYTES;
-        const uint32_t doa = qa + QTILE_BYTES;
-        const uint32_t pta = pt_addr + b * 2 * PT_BYTES;
-        const uint32_t dsa = pta + PT_BYTES;
+        const uint64_t qa = desc_at(qm_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES);
+        const uint64_t doa = desc_at(qa, QTILE_BYTES);
+        const uint64_t pta = desc_at(ptk_desc, b * 2 * PT_BYTES);
+        const uint64_t dsa = desc_at(pta, PT_BYTES);
+        const uint64_t dsm = desc_at(ptm_desc, b * 2 * PT_BYTES + PT_BYTES);
+        const uint32_t first = it ? 1u : 0u;
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16)
+        umma_f16(tmem_base + COL_DV, pta, doa, idesc_acc, first);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem_base + COL_DV, make_smem_desc_sw128(pta + kk * 32, 0, 1024),
-                   make_smem_desc_sw128(doa + kk * 2048, QTILE_BYTES / 2, 1024), idesc_acc, (it | kk) ? 1u : 0u);
+        for (int kk = 1; kk < 4; ++kk)
+          umma_f16(tmem_base + COL_DV, desc_at(pta, kk * 32), desc_at(doa, kk * 2048), idesc_acc, 1u);
+        umma_f16(tmem_base + COL_DK, dsa, qa, idesc_acc, first);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem_base + COL_DK, make_smem_desc_sw128(dsa + kk * 32, 0, 1024),
-                   make_smem_desc_sw128(qa + kk * 2048, QTILE_BYTES / 2, 1024), idesc_acc, (it | kk) ? 1u : 0u);
+        for (int kk = 1; kk < 4; ++kk)
+          umma_f16(tmem_base + COL_DK, desc_at(dsa, kk * 32), desc_at(qa, kk * 2048), idesc_acc, 1u);
         umma_commit(&qdo_empty[it % QDO_STAGES]);
         // dQ^T = K^T dS^T  (contraction over the 128 key rows: 8 steps of 16) into the S^T buffer
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + COL_ST + b * BQ, make_smem_desc_sw128(k_addr + kk * 2048, HALF_BYTES, 1024),
-                   make_smem_desc_sw128(dsa + kk * 2048, PT_BYTES, 1024), idesc_dq, kk ? 1u : 0u);
+          umma_f16(tmem_base + COL_ST + b * BQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
+                   kk ? 1u : 0u);
         umma_commit(&dq_full[b]);
         if (it + 2 < n_it) {
           ok = wait_qdo(it + 2);
@@ -670,6 +703,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int q0 = (i_start + it % per_head) * BQ;
         // visible iff key <= query:  column c >= kv_row - q0
         const int cmin = p.causal ? kv_row - q0 : 0;
+        // warp-uniform: does any row of this warp hide any column of this step?
+        const bool masked = (k0 + quarter * 32 + 32 > p.S) || (p.causal && k0 + quarter * 32 + 31 - q0 > 0);
         uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
         uint8_t* ds_row = pt_row + PT_BYTES;
 #pragma unroll 1
@@ -689,7 +724,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               const int i = 4 * i4 + e4;
               const int col = c * 32 + i;
               float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lsv[e4]));
-              if (!row_live || col < cmin) e = 0.f;
+              if (masked && (!row_live || col < cmin)) e = 0.f;
               pv[i] = e;
               dv[i] = e * (__uint_as_float(rp[i]) - dlv[e4]);
             }
@@ -912,7 +947,7 @@ extern "C" int hpb_flash_attn_fwd(const void* q, long long q_batch_stride, long 
   p.O = reinterpret_cast<__nv_bfloat16*>(O);
   p.lse = lse;
   p.status = status;
-  dim3 grid((S + 2 * fa::BM - 1) / (2 * fa::BM), Hq, B);
+  dim3 grid(((S + 2 * fa::BM - 1) / (2 * fa::BM)) * Hq * B);
   fa::flash_fwd_kernel<<<grid, fa::FWD_THREADS, fa::FWD_SMEM, stream>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -976,7 +1011,7 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
   p.dK = reinterpret_cast<__nv_bfloat16*>(dK);
   p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
   p.status = status;
-  dim3 grid((S + fa::BN - 1) / fa::BN, Hkv, B);
+  dim3 grid(((S + fa::BN - 1) / fa::BN) * Hkv * B);
   CUtensorMap tdq;
   {
     EncodeTiledFn enc = fa_encode_fn();
