@@ -37,6 +37,12 @@ def _strides_ok(t: torch.Tensor) -> bool:
             and t.data_ptr() % 16 == 0)
 
 
+def set_forward_variant(p_in_tensor_memory: bool) -> None:
+    """Forward kernel variant: P kept in tensor memory (default) or staged through shared memory."""
+    from . import native
+    native.lib().hpb_flash_attn_set_variant(int(bool(p_in_tensor_memory)))
+
+
 def flash_attention_forward(q, k, v, causal: bool = True, scale: float = None):
     """tcgen05 flash attention forward: ``(out [B,S,H,128] bf16, lse [B,H,S] fp32)``.
 

@@ -32,9 +32,14 @@ constexpr int BN = 128;
 constexpr int HD = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KB
 constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int KV_STAGES = 3;
 constexpr int FWD_THREADS = 320;
-constexpr int FWD_SMEM = (2 + KV_STAGES + 2) * TILE_BYTES + 1024 + 256;
+// P either goes through shared memory (3-stage K/V ring + two P tiles) or stays in tensor memory
+// on top of the scores it was computed from (5-stage ring); both variants use 7 tiles of 32 KB.
+template <bool P_TMEM>
+struct FwdCfg {
+  static constexpr int KV_STAGES = P_TMEM ? 5 : 3;
+};
+constexpr int FWD_SMEM = 7 * TILE_BYTES + 1024 + 256;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -85,6 +90,13 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
       : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
   return *reinterpret_cast<float2*>(&d);
 }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -103,16 +115,32 @@ __device__ __forceinline__ int kv_tiles_for(int qt, int S, int causal) {
   return causal ? min(total, qt + 1) : total;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (row = lane, two bf16 per 32-bit column)
+// is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <bool P_TMEM>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  constexpr int KV_STAGES = FwdCfg<P_TMEM>::KV_STAGES;
   uint8_t* sQ = smem;                                  // 2 tiles
   uint8_t* sKV = smem + 2 * TILE_BYTES;                // KV_STAGES tiles
-  uint8_t* sP = sKV + KV_STAGES * TILE_BYTES;          // 2 tiles
-  uint64_t* q_full = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
+  uint8_t* sP = sKV + 3 * TILE_BYTES;                  // 2 tiles (shared-memory P variant only)
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
   uint64_t* kv_full = q_full + 1;           // [KV_STAGES]
   uint64_t* kv_empty = kv_full + KV_STAGES; // [KV_STAGES]
   uint64_t* s_full = kv_empty + KV_STAGES;  // [2]
@@ -233,13 +261,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       auto issue_pv = [&](int t, int idx, bool accumulate) {
         // P: kv index is the contraction (64-wide halves, +32 B per 16); V: 16 kv rows = 2048 B,
         // the two 64-wide halves of the head dimension are HALF_BYTES apart (leading offset)
-        const uint64_t pa = desc_at(p_desc, t * TILE_BYTES);
         const uint64_t va = desc_at(v_desc, (idx % KV_STAGES) * TILE_BYTES);
         const uint32_t d = tmem_base + 2 * BN + t * HD;
-        umma_f16(d, pa, va, idesc_o, accumulate ? 1u : 0u);
+        if constexpr (P_TMEM) {
+          // P (bf16 pairs) occupies the first 64 columns of the score tile: 16 kv = 8 columns per step
+          const uint32_t pt = tmem_base + t * BN;
+          umma_f16_ts(d, pt, va, idesc_o, accumulate ? 1u : 0u);
 #pragma unroll
-        for (int k8 = 1; k8 < 8; ++k8)
-          umma_f16(d, desc_at(pa, (k8 >> 2) * HALF_BYTES + (k8 & 3) * 32), desc_at(va, k8 * 2048), idesc_o, 1u);
+          for (int k8 = 1; k8 < 8; ++k8) umma_f16_ts(d, pt + k8 * 8, desc_at(va, k8 * 2048), idesc_o, 1u);
+        } else {
+          const uint64_t pa = desc_at(p_desc, t * TILE_BYTES);
+          umma_f16(d, pa, va, idesc_o, accumulate ? 1u : 0u);
+#pragma unroll
+          for (int k8 = 1; k8 < 8; ++k8)
+            umma_f16(d, desc_at(pa, (k8 >> 2) * HALF_BYTES + (k8 & 3) * 32), desc_at(va, k8 * 2048), idesc_o, 1u);
+        }
         umma_commit(&pv_done[t]);
       };
       ok = mbar_wait_bounded(q_full, 0, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
@@ -325,11 +361,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         l *= alpha;
       }
       if (j > 0) {
-        // the previous P V product has retired: P buffer reusable, accumulator up to date
-        ok = mbar_wait_bounded(&pv_done[t], (j - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
-        if (!ok) break;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
+        // Shared-memory P: the previous P V product must have retired before its P tile is
+        // overwritten.  Tensor-memory P lies under the scores just produced, which the tensor
+        // core wrote after that product, so only a rescale of the accumulator has to wait.
+        const bool any_need = __any_sync(0xffffffffu, need);
+        if (!P_TMEM || any_need) {
+          ok = mbar_wait_bounded(&pv_done[t], (j - 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (any_need) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
@@ -346,24 +387,40 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
       const float2 nm2 = make_float2(-m, -m);
       float2 l2 = make_float2(0.f, 0.f);
+      if constexpr (P_TMEM) {
+        // pack in place: sr[i] <- bf16 pair (2i, 2i+1); two stores of 32 columns put the row back
 #pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {     // 16 chunks of 8 columns = one 16-byte store each
-        uint4 v;
-        __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = c8 * 8 + 2 * e;
-          float2 x = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2);
+        for (int i = 0; i < 64; ++i) {
+          float2 x = fma2(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), sc2, nm2);
           x.x = fast_exp2(x.x);
           x.y = fast_exp2(x.y);
           l2 = add2(l2, x);
-          vb[e] = __floats2bfloat162_rn(x.x, x.y);
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(x.x, x.y);
+          sr[i] = *reinterpret_cast<const uint32_t*>(&b2);
         }
-        uint8_t* blk = p_row + (c8 >> 3) * HALF_BYTES;
-        *reinterpret_cast<uint4*>(blk + (((c8 & 7) ^ sw) << 4)) = v;
+        tmem_st_32x32b_x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(sr));
+        tmem_st_32x32b_x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(sr + 32));
+        tmem_st_wait();
+      } else {
+#pragma unroll
+        for (int c8 = 0; c8 < 16; ++c8) {     // 16 chunks of 8 columns = one 16-byte store each
+          uint4 v;
+          __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = c8 * 8 + 2 * e;
+            float2 x = fma2(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), sc2, nm2);
+            x.x = fast_exp2(x.x);
+            x.y = fast_exp2(x.y);
+            l2 = add2(l2, x);
+            vb[e] = __floats2bfloat162_rn(x.x, x.y);
+          }
+          uint8_t* blk = p_row + (c8 >> 3) * HALF_BYTES;
+          *reinterpret_cast<uint4*>(blk + (((c8 & 7) ^ sw) << 4)) = v;
+        }
       }
       l += l2.x + l2.y;
-      fence_proxy_async();     // generic-proxy writes of P -> visible to the tensor core's reads
+      if constexpr (!P_TMEM) fence_proxy_async();   // generic-proxy writes of P -> visible to the tensor core
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
@@ -909,6 +966,10 @@ static int make_tmap_bsd(CUtensorMap* map, const void* ptr, int B, int S, int co
 
 using namespace hpb;
 
+// Forward variant: 1 = P stays in tensor memory (default), 0 = P goes through shared memory.
+static int g_fwd_p_in_tmem = 1;
+extern "C" void hpb_flash_attn_set_variant(int p_in_tmem) { g_fwd_p_in_tmem = p_in_tmem; }
+
 // q [B, S, Hq, 128], k / v [B, S, Hkv, 128] bf16: the head dimension contiguous, head stride 128,
 // row (token) and batch strides given in elements (so views into a packed qkv tensor work).
 // O [B, S, Hq, 128] contiguous bf16, lse [B, Hq, S] fp32.
@@ -935,8 +996,11 @@ extern "C" int hpb_flash_attn_fwd(const void* q, long long q_batch_stride, long 
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fa::flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fa::flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          fa::FWD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fa::flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               fa::FWD_SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
@@ -948,7 +1012,10 @@ extern "C" int hpb_flash_attn_fwd(const void* q, long long q_batch_stride, long 
   p.lse = lse;
   p.status = status;
   dim3 grid(((S + 2 * fa::BM - 1) / (2 * fa::BM)) * Hq * B);
-  fa::flash_fwd_kernel<<<grid, fa::FWD_THREADS, fa::FWD_SMEM, stream>>>(tq, tk, tv, p);
+  if (g_fwd_p_in_tmem)
+    fa::flash_fwd_kernel<true><<<grid, fa::FWD_THREADS, fa::FWD_SMEM, stream>>>(tq, tk, tv, p);
+  else
+    fa::flash_fwd_kernel<false><<<grid, fa::FWD_THREADS, fa::FWD_SMEM, stream>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -283,8 +283,10 @@ def _attn_oracle(q, k, v, causal):
 
 @pytest.mark.parametrize("B,S,H,Hkv,causal", [(1, 128, 1, 1, True), (1, 256, 2, 1, True), (2, 1024, 4, 2, True),
                                               (1, 384, 2, 2, False), (1, 200, 2, 1, True), (1, 2048, 8, 2, True)])
-def test_flash_attention_forward(B, S, H, Hkv, causal):
-    from hyper_parallel_b200.ops.attention import flash_attention_forward
+@pytest.mark.parametrize("p_tmem", [True, False])
+def test_flash_attention_forward(B, S, H, Hkv, causal, p_tmem):
+    from hyper_parallel_b200.ops.attention import flash_attention_forward, set_forward_variant
+    set_forward_variant(p_tmem)
     torch.manual_seed(5)
     qkv = torch.randn(B, S, (H + 2 * Hkv) * 128, device=_dev(), dtype=torch.bfloat16)
     q = qkv[..., :H * 128].view(B, S, H, 128)                       # strided views of a packed projection
@@ -296,6 +298,7 @@ def test_flash_attention_forward(B, S, H, Hkv, causal):
     ref, ref_lse = _attn_oracle(q, k, v, causal)
     assert _rel_err(out, ref) < 1.5e-2
     assert torch.allclose(lse, ref_lse, atol=2e-2, rtol=1e-3)
+    set_forward_variant(True)
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,causal", [(1, 128, 1, 1, True), (1, 256, 2, 1, True), (2, 1024, 4, 2, True),
