@@ -16,8 +16,9 @@
 // GEMM -> reduce-scatter.  Output tiles are produced destination by destination (peers first, own
 // rows last); the epilogue stores a tile whose rows belong to rank r straight into r's receive slot
 // `recv[src = me]` in symmetric memory (peer stores), and the CTA that completes the last tile of a
-// destination publishes a flag there.  When the main loop is done the CTAs wait (bounded) for the
-// flags of all sources and add the n partial slabs in fp32 into the bf16 output shard.
+// destination publishes a flag there.  The tiles of a rank's own rows come last: their epilogue
+// waits (bounded) for the flags of all sources, adds the received partial slabs to the fp32
+// accumulator and writes the bf16 output shard.
 //
 // Cross-rank ordering uses signal pads with monotonically increasing epochs (st.release.sys /
 // ld.acquire.sys); every wait is bounded and reports through the status word.
@@ -31,7 +32,8 @@ constexpr int A_TILE = BLOCK_M * BLOCK_K * 2, B_TILE = BLOCK_N * BLOCK_K * 2, ST
 constexpr int THREADS = 256;            // producer, MMA, 4 epilogue warps, 2 communication warps
 constexpr int COMM_THREADS = 64;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int XPOSE_BYTES = 32 * 128;    // per epilogue warp: 32 rows x 64 bf16, for 128-byte peer stores
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + 4 * XPOSE_BYTES;
 constexpr int kMaxPeers = 8;
 constexpr int kSlots = 16;              // flags per signal slot
 
@@ -401,85 +403,131 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else if (warp < 6) {
+    // ---------------------------------------------------------------- epilogue --
+    // Tiles for a peer: bf16 rows are transposed through a per-warp shared-memory tile so that
+    // every store instruction writes four full 128-byte lines of the peer's receive slab (row-
+    // owned 16-byte stores would cross NVLink as partial sectors).  One system fence and one
+    // counter update per (warp, destination), not per tile.  Tiles of this rank's own rows come
+    // last: by then the peers' partial slabs have arrived, and the epilogue adds them to the
+    // accumulator and writes the final output -- there is no separate reduction pass.
     const int q = warp & 3;
     int local_tile = 0;
     bool ok = true;
-    const bool vec_ok = (p.N & 7) == 0;
+    uint8_t* xp = s.base + STAGES * STAGE_BYTES + 256 + q * XPOSE_BYTES;
+    int cur_dest = -1;
+    unsigned cur_cnt = 0;
+    bool have_peers = false;
+    auto publish = [&]() {
+      if (cur_dest >= 0 && cur_dest != p.rank && cur_cnt > 0) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const unsigned done = atomicAdd(p.dest_count + cur_dest, cur_cnt) + cur_cnt;
+          if (done == static_cast<unsigned>(tiles_per_dest) * 4u) {
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<unsigned*>(p.pads.ptr[cur_dest]) + 2 * kSlots + p.rank, p.epoch);
+          }
+        }
+      }
+      cur_cnt = 0;
+    };
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
       int dest, m_local, n0;
       decode(t, dest, m_local, n0);
+      if (dest != cur_dest) {
+        publish();
+        cur_dest = dest;
+      }
       const int buf = local_tile & 1;
       ok = mbar_wait_bounded(&s.tmem_full[buf], (local_tile >> 1) & 1, s.abort_flag, p.status, kTimeoutTmemFull,
                              blockIdx.x);
       if (!ok) break;
       tc_fence_after();
-      const int row = m_local + q * 32 + lane;                 // row inside the destination's slab
-      // slab `src = me` of the destination's receive area (a peer pointer unless dest == me)
-      __nv_bfloat16* slab = reinterpret_cast<__nv_bfloat16*>(p.recv.ptr[dest]) +
-                            static_cast<long long>(p.rank) * p.Ms * p.N;
       const uint32_t taddr = tmem_base + buf * BLOCK_N + (static_cast<uint32_t>(q * 32) << 16);
+      const int row0 = m_local + q * 32;                       // first row of this warp inside the slab
+      if (dest != p.rank) {
+        __nv_bfloat16* slab = reinterpret_cast<__nv_bfloat16*>(p.recv.ptr[dest]) +
+                              static_cast<long long>(p.rank) * p.Ms * p.N;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col = n0 + c * 32;
-        if (row < p.Ms && col < p.N)
-          store_row32(slab + static_cast<long long>(row) * p.N + col, r, p.N - col, vec_ok);
+        for (int c = 0; c < BLOCK_N / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(r));
+          tmem_ld_32x32b_x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              vb[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+            *reinterpret_cast<uint4*>(xp + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          __syncwarp();
+          const int col = n0 + c * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(xp + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+            if (row0 + rr < p.Ms && col < p.N)
+              *reinterpret_cast<uint4*>(slab + static_cast<long long>(row0 + rr) * p.N + col) = v;
+          }
+          __syncwarp();
+        }
+      } else {
+        if (!have_peers) {
+          // all partial slabs for my rows must have landed (flags raised by the peers' epilogues)
+          bool got = true;
+          if (lane < p.n && lane != p.rank)
+            got = wait_flag_sys(reinterpret_cast<const unsigned*>(p.pads.ptr[p.rank]) + 2 * kSlots + lane, p.epoch,
+                                p.limit_ns, s.abort_flag, p.status, 0x200 | lane);
+          ok = __all_sync(0xffffffffu, got);
+          if (!ok) break;
+          have_peers = true;
+        }
+        const int row = row0 + lane;
+        const long long slab_elems = static_cast<long long>(p.Ms) * p.N;
+        const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(p.recv.ptr[p.rank]);
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (row < p.Ms && col < p.N) {
+            const long long off = static_cast<long long>(row) * p.N + col;
+            const int nv = min(4, (p.N - col) / 8);
+            for (int j = 0; j < nv; ++j) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+              for (int src = 0; src < p.n; ++src) {
+                if (src == p.rank) continue;
+                const uint4 v = *reinterpret_cast<const uint4*>(mine + src * slab_elems + off + 8 * j);
+                const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 x = __bfloat1622float2(vb[e]);
+                  f[2 * e] += x.x;
+                  f[2 * e + 1] += x.y;
+                }
+              }
+              uint4 o;
+              __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+              *reinterpret_cast<uint4*>(out + off + 8 * j) = o;
+            }
+          }
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.tmem_empty[buf]);
-      // publish: the warp that completes the last quarter of the last tile of `dest` raises the flag
-      __threadfence_system();
-      __syncwarp();
-      if (lane == 0) {
-        const unsigned done = atomicAdd(p.dest_count + dest, 1u) + 1;
-        if (done == static_cast<unsigned>(tiles_per_dest) * 4u) {
-          __threadfence_system();
-          st_release_sys(reinterpret_cast<unsigned*>(p.pads.ptr[dest]) + 2 * kSlots + p.rank, p.epoch);
-        }
-      }
+      ++cur_cnt;
     }
-  }
-  // ------------------------------------------------ reduction of the n received slabs --
-  __syncthreads();
-  {
-    __shared__ int s_ok;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (threadIdx.x < p.n) {
-      if (!wait_flag_sys(reinterpret_cast<const unsigned*>(p.pads.ptr[p.rank]) + 2 * kSlots + threadIdx.x, p.epoch,
-                         p.limit_ns, s.abort_flag, p.status, 0x200 | threadIdx.x))
-        s_ok = 0;
-    }
-    __syncthreads();
-    if (s_ok && !*s.abort_flag) {
-      const long long vecs = static_cast<long long>(p.Ms) * p.N / 8;
-      const uint4* base = reinterpret_cast<const uint4*>(p.recv.ptr[p.rank]);
-      uint4* out = reinterpret_cast<uint4*>(p.out);
-      for (long long i = blockIdx.x * static_cast<long long>(THREADS) + threadIdx.x; i < vecs;
-           i += static_cast<long long>(gridDim.x) * THREADS) {
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-        for (int r = 0; r < p.n; ++r) {
-          const uint4 v = base[static_cast<long long>(r) * vecs + i];
-          const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(vb[e]);
-            acc[2 * e] += f.x;
-            acc[2 * e + 1] += f.y;
-          }
-        }
-        uint4 o;
-        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-        out[i] = o;
-      }
-    }
+    if (ok) publish();
   }
   tc_fence_before();
   __syncthreads();
