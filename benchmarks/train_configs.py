@@ -1,0 +1,263 @@
+"""Training benchmarks of the hybrid-parallel configurations other than the headline one.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29544 benchmarks/train_configs.py --config {tp_hsdp,moe_ep,pp} [options]
+
+* ``tp_hsdp``  Llama-2-13B, tensor parallel (+ sequence-parallel activations) ``--tp`` wide, HSDP
+  (level3, full shard) over the remaining ranks; ``HPB_FUSED_TP=0`` selects NCCL + GEMM instead of
+  the fused all-gather->GEMM / GEMM->reduce-scatter kernels.
+* ``moe_ep``   DeepSeek-V3 (``--layers``, ``--experts``) with expert parallelism over all ranks.
+* ``pp``       Llama-3-8B split into ``--pp`` pipeline stages (x ``--vpp`` chunks per rank),
+  schedule ``--schedule {gpipe,1f1b,vpp}``, ``--micro`` micro-batches.
+
+Timing rules are those of ``bench.py``: warm-up, CUDA events around exactly ``--steps`` steps,
+barrier + synchronize on both sides, max over ranks; the step includes the optimizer.  Rank 0
+prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=["tp_hsdp", "moe_ep", "pp"])
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=1, help="sequences per data-parallel replica (per rank for moe_ep)")
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--tp", type=int, default=None)
+    ap.add_argument("--pp", type=int, default=None)
+    ap.add_argument("--vpp", type=int, default=2)
+    ap.add_argument("--micro", type=int, default=8)
+    ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"])
+    ap.add_argument("--experts", type=int, default=None)
+    return ap.parse_args()
+
+
+def timed_steps(step, args, dev):
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.utils.clocks import ClockSampler
+    for i in range(args.warmup):
+        step(i)
+    native.check_status()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        e0.record()
+        for i in range(args.steps):
+            out = step(args.warmup + i)
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+    native.check_status()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item(), out, clocks.summary()
+
+
+def run_tp_hsdp(args, rank, world, dev):
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200 import Layout
+    from hyper_parallel_b200.models.llama import LlamaConfig
+    from hyper_parallel_b200.models.llama_tp import TPLlama
+    from hyper_parallel_b200.optim import FusedAdamW
+    tp = args.tp or min(4, world)
+    dp = world // tp
+    cfg = LlamaConfig.llama2_13b()
+    if args.layers:
+        cfg.num_layers = args.layers
+    layout = Layout((dp, tp), ("dp", "tp"))
+    model = TPLlama(cfg, layout, device=dev)
+    model.init_weights()
+    kw = dict(shard_size=dp, threshold=0, optimizer_level="level3", comm_fusion=dp > 1, comm_async=dp > 1)
+    for layer in model.layers:
+        hp.hsdp(layer, **kw)
+    hp.hsdp(model, **kw)
+    opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    dp_rank = rank // tp
+    g = torch.Generator().manual_seed(dp_rank)
+    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1), generator=g).to(dev)
+
+    def step(i):
+        model.zero_grads()
+        loss = model(toks[i, :, :-1], toks[i, :, 1:])
+        loss.backward()
+        hp.hsdp_sync_stream()
+        opt.step()
+        return loss
+
+    ms, loss, clocks = timed_steps(step, args, dev)
+    tokens = dp * args.batch * args.seq_len
+    return {"config": {"model": "llama2_13b", "layers": cfg.num_layers, "parallelism": f"tp{tp}(+sp) x hsdp{dp} level3",
+                       "global_batch": dp * args.batch, "seq_len": args.seq_len,
+                       "fused_tp": os.environ.get("HPB_FUSED_TP", "1") != "0"},
+            "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(loss.detach()), "clocks": clocks,
+            "mfu_flops_per_token": cfg.flops_per_token(args.seq_len)}
+
+
+def run_moe_ep(args, rank, world, dev):
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200.models.deepseek_v3 import DeepSeekV3, DeepSeekV3Config
+    from hyper_parallel_b200.optim import FusedAdamW
+    cfg = DeepSeekV3Config()
+    if args.layers:
+        cfg.num_layers = args.layers
+    if args.experts:
+        cfg.n_routed_experts = args.experts
+    model = DeepSeekV3(cfg, ep_group=dist.group.WORLD if world > 1 else None, device=dev)
+    model.init_weights()
+    opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    # non-expert parameters are replicated over the expert-parallel ranks: plain data parallelism
+    from hyper_parallel_b200.models.deepseek_v3 import MoE
+    experts = {id(p) for m in model.modules() if isinstance(m, MoE) for p in (m.w_gate_up, m.w_down)}
+    shared = [p for p in model.parameters() if id(p) not in experts]
+    g = torch.Generator().manual_seed(rank)
+    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1), generator=g).to(dev)
+
+    def step(i):
+        opt.zero_grad(set_to_none=True)
+        loss = model(toks[i, :, :-1], toks[i, :, 1:])
+        loss.backward()
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in shared if p.grad is not None])
+            dist.all_reduce(flat)
+            flat.div_(world)
+            o = 0
+            for p in shared:
+                if p.grad is not None:
+                    p.grad.copy_(flat[o:o + p.numel()].view_as(p))
+                    o += p.numel()
+        opt.step()
+        return loss
+
+    ms, loss, clocks = timed_steps(step, args, dev)
+    tokens = world * args.batch * args.seq_len
+    return {"config": {"model": "deepseek_v3", "layers": cfg.num_layers, "experts": cfg.n_routed_experts,
+                       "parallelism": f"ep{world} (+dp{world} on shared weights)", "global_batch": world * args.batch,
+                       "seq_len": args.seq_len},
+            "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(loss.detach()), "clocks": clocks,
+            "mfu_flops_per_token": cfg.flops_per_token(args.seq_len)}
+
+
+def run_pp(args, rank, world, dev):
+    from torch import nn
+    from hyper_parallel_b200 import PipelineStage
+    from hyper_parallel_b200 import ops
+    from hyper_parallel_b200.core.pipeline_parallel import Schedule1F1B, ScheduleGPipe, ScheduleInterleaved1F1B
+    from hyper_parallel_b200.models.llama import Llama, LlamaBlock, LlamaConfig
+    from hyper_parallel_b200.optim import FusedAdamW
+    import torch.nn.functional as F
+    pp = args.pp or world
+    assert pp == world, "this benchmark runs pure pipeline parallelism (one rank per stage)"
+    cfg = LlamaConfig.llama3_8b()
+    if args.layers:
+        cfg.num_layers = args.layers
+    chunks = args.vpp if args.schedule == "vpp" else 1
+    n_virtual = pp * chunks
+    per = cfg.num_layers // n_virtual
+    S, B = args.seq_len, args.batch
+
+    class Chunk(nn.Module):
+        """Layers [lo, hi) of the model; the first chunk embeds, the last computes the loss."""
+
+        def __init__(self, lo, hi, first, last):
+            super().__init__()
+            self.first, self.last = first, last
+            self.layers = nn.ModuleList(LlamaBlock(cfg, i, device=dev) for i in range(lo, hi))
+            if first:
+                self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, device=dev, dtype=torch.bfloat16))
+                nn.init.normal_(self.embed, 0.0, 0.02)
+            if last:
+                self.final_norm = nn.Parameter(torch.ones(cfg.hidden_size, device=dev, dtype=torch.bfloat16))
+                self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, device=dev, dtype=torch.bfloat16))
+                nn.init.normal_(self.lm_head, 0.0, 0.02)
+            for l in self.layers:
+                l.reset_parameters()
+            self.targets = None
+
+        def forward(self, x):
+            if self.first:
+                mb = x.shape[0]
+                h, resid = F.embedding(x[:, :-1].reshape(-1), self.embed), None
+                self._tgt = x[:, 1:]
+            else:
+                mb = x.shape[0]
+                h, resid = x.reshape(-1, cfg.hidden_size), None
+            for l in self.layers:
+                h, resid = l(h, resid, mb, S)
+            h = h if resid is None else h + resid
+            if not self.last:
+                return h.view(mb, S, cfg.hidden_size)
+            xn = ops.rmsnorm(h, self.final_norm, cfg.norm_eps)
+            logits = ops.linear(xn, self.lm_head)
+            tgt = self.targets.pop(0)
+            return ops.fused_cross_entropy(logits, tgt.reshape(-1), float(tgt.numel() * args.micro), unit_grad=True)
+
+    idx = [rank + c * pp for c in range(chunks)]
+    mods = [Chunk(i * per, (i + 1) * per, i == 0, i == n_virtual - 1) for i in idx]
+    stages = [PipelineStage(m, i, n_virtual, device=dev) for m, i in zip(mods, idx)]
+    if args.schedule == "vpp":
+        sched = ScheduleInterleaved1F1B(stages, args.micro)
+    else:
+        sched = (ScheduleGPipe if args.schedule == "gpipe" else Schedule1F1B)(stages[0], args.micro)
+    params = [p for m in mods for p in m.parameters()]
+    opt = FusedAdamW(params, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, B * args.micro, S + 1), generator=g).to(dev)
+    last_mod = mods[-1] if mods[-1].last else None
+
+    def step(i):
+        opt.zero_grad(set_to_none=True)
+        if last_mod is not None:
+            last_mod.targets = list(toks[i, :, 1:].chunk(args.micro))
+        out = sched.run(toks[i]) if rank == 0 else sched.run()
+        opt.step()
+        return torch.stack([o.detach() for o in out]).sum() if out is not None else torch.zeros((), device=dev)
+
+    ms, loss, clocks = timed_steps(step, args, dev)
+    lt = loss.clone()
+    dist.all_reduce(lt, op=dist.ReduceOp.MAX)
+    tokens = B * args.micro * S
+    return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} {args.schedule}"
+                       + (f" x{chunks} chunks" if chunks > 1 else ""), "micro_batches": args.micro,
+                       "global_batch": B * args.micro, "seq_len": S},
+            "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(lt.detach()), "clocks": clocks,
+            "mfu_flops_per_token": cfg.flops_per_token(S)}
+
+
+def main():
+    args = parse()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    res = {"tp_hsdp": run_tp_hsdp, "moe_ep": run_moe_ep, "pp": run_pp}[args.config](args, rank, world, dev)
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))).get("bf16_tflops_sustained", 1400.0)
+    except OSError:
+        peak = 1400.0
+    fpt = res.pop("mfu_flops_per_token")
+    res["mfu_of_measured_sustained_bf16"] = fpt * res["value"] / world / (peak * 1e12)
+    res.update({"metric": "train tokens/sec (device-timed, max over ranks)", "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "data": "synthetic"})
+    if rank == 0:
+        print(json.dumps(res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
