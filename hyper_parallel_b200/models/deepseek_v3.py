@@ -184,8 +184,14 @@ class MoE(nn.Module):
         c = self.cfg
         topk_idx, topk_w = moe_ops.route(x, self.gate, self.gate_bias, c.top_k, c.n_group, c.topk_group,
                                          c.routed_scaling_factor)
-        y = moe_ops.expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down, c.n_routed_experts,
-                                        self.ep_group)
+        from ..parallel import ep_fused
+        if ep_fused.usable(x, topk_idx, self.w_gate_up, c.n_routed_experts, self.ep_group):
+            # dispatch / combine kernels over NVLink peer memory around the grouped expert GEMMs
+            y = ep_fused.fused_expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down,
+                                                   c.n_routed_experts, self.ep_group)
+        else:
+            y = moe_ops.expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down, c.n_routed_experts,
+                                            self.ep_group)
         if self.shared is not None:
             y = y + self.shared(x)
         return y

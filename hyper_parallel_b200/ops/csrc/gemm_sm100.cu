@@ -96,7 +96,9 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p) {
     tile_coords(t, num_m, num_n, m_blk, n_blk);
     ti.group = p.mode == 1 ? p.block_group[m_blk] : 0;
     ti.k_row0 = 0;
-    ti.num_k = (p.K + BLOCK_K - 1) / BLOCK_K;
+    // a negative group marks an unused row block of an over-allocated (capacity-sized) operand:
+    // no loads, no products, and the epilogue leaves the output rows alone
+    ti.num_k = ti.group < 0 ? 0 : (p.K + BLOCK_K - 1) / BLOCK_K;
   }
   ti.m0 = m_blk * BLOCK_M;
   ti.n0 = n_blk * BLOCK_N;
@@ -274,7 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
         const int col = col0 + c * 32;
-        if (row_local < p.M && col < p.N) {
+        if (row_local < p.M && col < p.N && ti.group >= 0) {
           if constexpr (OUT_F32) {
             float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col;
             if (col + 32 <= p.N && (p.ldc & 3) == 0) {

@@ -145,3 +145,50 @@ def test_fused_ag_gemm_and_gemm_rs_match_reference(tmp_path):
     from dist_utils import _free_port
     mp.spawn(_tp_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert torch.load(tmp_path / "tp.pt")["ok"]
+
+
+def _ep_worker(rank, world, port, tmp):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from hyper_parallel_b200.ops import moe, native
+    from hyper_parallel_b200.parallel import ep_fused
+    T, H, Fh, E, k = 260, 256, 128, 8, 3
+    El = E // world
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    wgu = (torch.randn(El, 2 * Fh, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    wd = (torch.randn(El, H, Fh, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:k] for _ in range(T)])
+    wts = torch.rand(T, k, device=dev, generator=g)
+    ok = True
+    for it in range(2):                                   # twice: the workspace is reused
+        dy = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+        res = []
+        for fused in (True, False):
+            xa, wa, ga, da = [t.clone().requires_grad_() for t in (x, wts, wgu, wd)]
+            f = ep_fused.fused_expert_parallel_ffn if fused else moe.expert_parallel_ffn
+            y = f(xa, idx, wa, ga, da, E, dist.group.WORLD)
+            y.backward(dy)
+            res.append([y] + [t.grad for t in (xa, wa, ga, da)])
+        for a, b in zip(*res):
+            ok &= ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item() < 2e-2
+    torch.cuda.synchronize()
+    native.check_status()
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"ok": bool(t.item())}, os.path.join(tmp, "ep.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_expert_parallel_dispatch_combine_matches_nccl_path(tmp_path):
+    _need(2)
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    mp.spawn(_ep_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert torch.load(tmp_path / "ep.pt")["ok"]
