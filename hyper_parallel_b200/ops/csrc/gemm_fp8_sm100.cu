@@ -23,7 +23,7 @@ constexpr int BM = 128, BN = 128, BK = 128;       // BK in elements = bytes
 constexpr int UMMA_K = 32;
 constexpr int STAGES = 6;
 constexpr int A_TILE = BM * BK, B_TILE = BN * BK, STAGE_BYTES = A_TILE + B_TILE;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;      // producer, MMA, 2 x 4 promotion warps (each group owns 64 columns)
 constexpr int NBUF = 4;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
@@ -63,7 +63,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(&part_full[b], 1);
-      mbar_init(&part_empty[b], 4);
+      mbar_init(&part_empty[b], 8);
     }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -132,54 +132,92 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
     }
   } else {
+    // promotion: every 128-deep partial product is scaled by (activation scale of the row) x
+    // (weight scale of the block) and added to the fp32 accumulator in registers.  Two groups of
+    // four warps split the 128 columns, so two warps share each scheduler and hide each other's
+    // tensor-memory load latency; the scales of the next block are fetched one block ahead.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HN = BN / 2;
     const int kblocks = (p.K + BK - 1) / BK;
     long it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const int m0 = (t % num_m) * BM, n_blk = t / num_m, n0 = n_blk * BN;
+      const int m0 = (t % num_m) * BM, n_blk = t / num_m, n0 = n_blk * BN + half * HN;
       const int row = m0 + q * 32 + lane;
       const int srow = row < p.M ? row : p.M - 1;
-      float acc[BN];
+      float2 acc[HN / 2];
 #pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-      for (int kb = 0; kb < num_k; ++kb, ++it) {
-        const int pb = static_cast<int>(it % NBUF);
-        const uint32_t pphase = static_cast<uint32_t>((it / NBUF) & 1);
-        const float scale = p.sa[static_cast<long long>(kb) * p.M + srow] *
-                            p.sb[static_cast<long long>(n_blk) * kblocks + kb];
-        ok = mbar_wait_bounded(&part_full[pb], pphase, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t taddr = tmem_base + pb * BN + (static_cast<uint32_t>(q * 32) << 16);
+      for (int j = 0; j < HN / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+      const float* sa_row = p.sa + srow;
+      const float* sb_row = p.sb + static_cast<long long>(n_blk) * kblocks;
+      // scales are fetched four blocks ahead (an L2 round trip is longer than one block) and
+      // multiplied only when they are used, so that the loads never stall the promotion
+      constexpr int PF = 4;
+      float sa_v[PF], sb_v[PF];
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
+      for (int u = 0; u < PF; ++u) {
+        const int kq = u < num_k ? u : num_k - 1;
+        sa_v[u] = sa_row[static_cast<long long>(kq) * p.M];
+        sb_v[u] = sb_row[kq];
+      }
+      for (int kb0 = 0; kb0 < num_k && ok; kb0 += PF) {
+#pragma unroll
+        for (int u = 0; u < PF; ++u) {
+          const int kb = kb0 + u;
+          if (kb >= num_k) break;
+          const int pb = static_cast<int>(it % NBUF);
+          const uint32_t pphase = static_cast<uint32_t>((it / NBUF) & 1);
+          ++it;
+          const float scale = sa_v[u] * sb_v[u];
+          {
+            const int kq = kb + PF < num_k ? kb + PF : num_k - 1;
+            sa_v[u] = sa_row[static_cast<long long>(kq) * p.M];
+            sb_v[u] = sb_row[kq];
+          }
+          ok = mbar_wait_bounded(&part_full[pb], pphase, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t taddr = tmem_base + pb * BN + half * HN + (static_cast<uint32_t>(q * 32) << 16);
+          uint32_t r[HN];
+          tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
+          tmem_ld_32x32b_x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(r + 32));
           tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&part_empty[pb]);      // the values are in registers
+          const float2 s2 = make_float2(scale, scale);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), scale, acc[c * 32 + j]);
+          for (int j = 0; j < HN / 2; ++j) {
+            unsigned long long d;
+            const float2 x = make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            asm("fma.rn.f32x2 %0, %1, %2, %3;"
+                : "=l"(d)
+                : "l"(*reinterpret_cast<const unsigned long long*>(&x)),
+                  "l"(*reinterpret_cast<const unsigned long long*>(&s2)),
+                  "l"(*reinterpret_cast<const unsigned long long*>(&acc[j])));
+            acc[j] = *reinterpret_cast<float2*>(&d);
+          }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&part_empty[pb]);
       }
       if (!ok) break;
       if (row < p.M) {
         __nv_bfloat16* dst = p.C + static_cast<long long>(row) * p.ldc + n0;
-        if (n0 + BN <= p.N && (p.ldc & 7) == 0) {
+        if (n0 + HN <= p.N && (p.ldc & 7) == 0) {
 #pragma unroll
-          for (int j = 0; j < BN / 8; ++j) {
+          for (int j = 0; j < HN / 8; ++j) {
             uint4 v;
             __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(acc[8 * j + 2 * e], acc[8 * j + 2 * e + 1]);
+            for (int e = 0; e < 4; ++e) vb[e] = __floats2bfloat162_rn(acc[4 * j + e].x, acc[4 * j + e].y);
             reinterpret_cast<uint4*>(dst)[j] = v;
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < BN; ++j)          // static indices keep `acc` in registers
-            if (n0 + j < p.N) dst[j] = __float2bfloat16(acc[j]);
+          for (int j = 0; j < HN / 2; ++j) {         // static indices keep `acc` in registers
+            if (n0 + 2 * j < p.N) dst[2 * j] = __float2bfloat16(acc[j].x);
+            if (n0 + 2 * j + 1 < p.N) dst[2 * j + 1] = __float2bfloat16(acc[j].y);
+          }
         }
       }
     }
