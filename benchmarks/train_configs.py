@@ -7,7 +7,8 @@
   (level3, full shard) over the remaining ranks; ``HPB_FUSED_TP=0`` selects NCCL + GEMM instead of
   the fused all-gather->GEMM / GEMM->reduce-scatter kernels.
 * ``moe_ep``   DeepSeek-V3 (``--layers``, ``--experts``) with expert parallelism over all ranks.
-* ``pp``       Llama-3-8B split into ``--pp`` pipeline stages (x ``--vpp`` chunks per rank),
+* ``pp``       Llama-3-8B split into ``--pp`` pipeline stages (x ``--vpp`` chunks per rank), each stage
+  ``--tp`` wide tensor parallel,
   schedule ``--schedule {gpipe,1f1b,vpp}``, ``--micro`` micro-batches.
 
 Timing rules are those of ``bench.py``: warm-up, CUDA events around exactly ``--steps`` steps,
@@ -159,8 +160,9 @@ def run_pp(args, rank, world, dev):
     from hyper_parallel_b200.models.llama import Llama, LlamaBlock, LlamaConfig
     from hyper_parallel_b200.optim import FusedAdamW
     import torch.nn.functional as F
-    pp = args.pp or world
-    assert pp == world, "this benchmark runs pure pipeline parallelism (one rank per stage)"
+    tp = args.tp or 1
+    pp = args.pp or world // tp
+    assert pp * tp == world, "pipeline stages x tensor-parallel width must equal the world size"
     cfg = LlamaConfig.llama3_8b()
     if args.layers:
         cfg.num_layers = args.layers
@@ -168,6 +170,7 @@ def run_pp(args, rank, world, dev):
     n_virtual = pp * chunks
     per = cfg.num_layers // n_virtual
     S, B = args.seq_len, args.batch
+    stage_rank = rank // tp                      # ranks [s * tp, (s + 1) * tp) form pipeline stage s
 
     class Chunk(nn.Module):
         """Layers [lo, hi) of the model; the first chunk embeds, the last computes the loss."""
@@ -188,12 +191,10 @@ def run_pp(args, rank, world, dev):
             self.targets = None
 
         def forward(self, x):
+            mb = x.shape[0]
             if self.first:
-                mb = x.shape[0]
                 h, resid = F.embedding(x[:, :-1].reshape(-1), self.embed), None
-                self._tgt = x[:, 1:]
             else:
-                mb = x.shape[0]
                 h, resid = x.reshape(-1, cfg.hidden_size), None
             for l in self.layers:
                 h, resid = l(h, resid, mb, S)
@@ -205,7 +206,31 @@ def run_pp(args, rank, world, dev):
             tgt = self.targets.pop(0)
             return ops.fused_cross_entropy(logits, tgt.reshape(-1), float(tgt.numel() * args.micro), unit_grad=True)
 
-    idx = [rank + c * pp for c in range(chunks)]
+    class TPChunk(nn.Module):
+        """The same slice of the model, tensor parallel (+ sequence-parallel activations) inside the stage."""
+
+        def __init__(self, lo, hi, first, last):
+            super().__init__()
+            from hyper_parallel_b200 import Layout
+            from hyper_parallel_b200.models.llama_tp import TPLlama
+            self.first, self.last = first, last
+            self.m = TPLlama(cfg, Layout((1, tp), ("dp", "tp"), list(range(stage_rank * tp, stage_rank * tp + tp))), device=dev, first_layer=lo, num_layers=hi - lo,
+                             with_embed=first, with_head=last)
+            self.m.init_weights()
+            self.targets = None
+
+        def forward(self, *x):
+            kw = {}
+            if self.last:
+                tgt = self.targets.pop(0)
+                kw = dict(targets=tgt, loss_denominator=float(tgt.numel() * args.micro))
+            if self.first:
+                return self.m(x[0][:, :-1].contiguous(), **kw)
+            return self.m((x[0], x[1]), batch=B, seq_len=S, **kw)
+
+    if tp > 1:
+        Chunk = TPChunk  # noqa: F811
+    idx = [stage_rank + c * pp for c in range(chunks)]
     mods = [Chunk(i * per, (i + 1) * per, i == 0, i == n_virtual - 1) for i in idx]
     stages = [PipelineStage(m, i, n_virtual, device=dev) for m, i in zip(mods, idx)]
     if args.schedule == "vpp":
@@ -222,7 +247,7 @@ def run_pp(args, rank, world, dev):
         opt.zero_grad(set_to_none=True)
         if last_mod is not None:
             last_mod.targets = list(toks[i, :, 1:].chunk(args.micro))
-        out = sched.run(toks[i]) if rank == 0 else sched.run()
+        out = sched.run(toks[i]) if stage_rank == 0 else sched.run()
         opt.step()
         return torch.stack([o.detach() for o in out]).sum() if out is not None else torch.zeros((), device=dev)
 
@@ -230,7 +255,7 @@ def run_pp(args, rank, world, dev):
     lt = loss.clone()
     dist.all_reduce(lt, op=dist.ReduceOp.MAX)
     tokens = B * args.micro * S
-    return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} {args.schedule}"
+    return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} x tp{tp} {args.schedule}"
                        + (f" x{chunks} chunks" if chunks > 1 else ""), "micro_batches": args.micro,
                        "global_batch": B * args.micro, "seq_len": S},
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(lt.detach()), "clocks": clocks,

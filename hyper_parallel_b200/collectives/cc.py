@@ -93,22 +93,24 @@ def get_backend(group=None) -> str:
     return dist.get_backend(group)
 
 
-def group_for_ranks(ranks: Sequence[int], timeout=None, pg_options=None, group_desc=None):
+def group_for_ranks(ranks: Sequence[int], timeout=None, pg_options=None, group_desc=None, tag=None):
     """Return (creating once) the process group whose members are ``ranks`` in this order.
 
     Returns ``None`` when torch.distributed is not initialised or the group has a
-    single member (every collective over it is the identity).
+    single member (every collective over it is the identity).  ``tag`` asks for a separate
+    group (its own communicator and stream) over the same ranks, e.g. one per traffic direction.
     """
-    key = tuple(int(r) for r in ranks)
-    if not is_initialized() or len(key) <= 1:
+    ranks_key = tuple(int(r) for r in ranks)
+    key = ranks_key if tag is None else ranks_key + (str(tag),)
+    if not is_initialized() or len(ranks_key) <= 1:
         return None
     grp = _GROUP_CACHE.get(key)
     if grp is not None:
         return grp
-    if key == tuple(range(dist.get_world_size())):
+    if tag is None and ranks_key == tuple(range(dist.get_world_size())):
         grp = dist.group.WORLD
     else:
-        if dist.get_rank() not in key:
+        if dist.get_rank() not in ranks_key:
             return None
         kwargs = {}
         if timeout is not None:
@@ -117,9 +119,34 @@ def group_for_ranks(ranks: Sequence[int], timeout=None, pg_options=None, group_d
             kwargs["pg_options"] = pg_options
         if group_desc is not None:
             kwargs["group_desc"] = group_desc
-        grp = dist.new_group(list(key), use_local_synchronization=True, **kwargs)
+        grp = dist.new_group(list(ranks_key), use_local_synchronization=True, **kwargs)
     _GROUP_CACHE[key] = grp
     return grp
+
+
+def world_collective_groups(specs: Sequence[Tuple[Sequence[int], str]]) -> Dict[Tuple[Tuple[int, ...], str], object]:
+    """Create (once) one group per ``(ranks, tag)`` of ``specs``; EVERY rank of the world must call
+    this with the same list.  Returns the groups this rank is a member of.
+
+    Unlike :func:`group_for_ranks` this does not rely on member-only creation, whose group names
+    depend on how many groups each member has created before (torch/distributed/distributed_c10d.py,
+    ``_hash_ranks_to_str``) and therefore break when members have different histories -- as the
+    two ends of a pipeline do.
+    """
+    mine: Dict[Tuple[Tuple[int, ...], str], object] = {}
+    if not is_initialized():
+        return mine
+    me = dist.get_rank()
+    for ranks, tag in specs:
+        rk = tuple(int(r) for r in ranks)
+        key = rk + (str(tag),)
+        grp = _GROUP_CACHE.get(key)
+        if grp is None:
+            grp = dist.new_group(list(rk))
+            _GROUP_CACHE[key] = grp
+        if me in rk:
+            mine[(rk, str(tag))] = grp
+    return mine
 
 
 def split_group(parent_pg=None, split_ranks: Optional[Sequence[Sequence[int]]] = None, timeout=None,

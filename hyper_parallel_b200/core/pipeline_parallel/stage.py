@@ -19,6 +19,8 @@ while micro-batch ``i`` computes (``overlap_p2p``).
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
@@ -91,6 +93,26 @@ class PipelineStage:
                              f"{(self.real_stage_index + 1) * self.device_num_per_stage}))")
         self.pp_ranks = [self.rank + self.device_num_per_stage * (i - self.real_stage_index)
                          for i in range(self.real_stage_num)]
+        # One process group (communicator + stream) per ordered neighbour pair and traffic
+        # direction: activations and gradients then do not queue behind each other, which a single
+        # communicator would force.  The groups of all pipeline rings are created by all ranks of
+        # the world in the same order (every rank builds its stage with the same configuration).
+        self._p2p_groups = {}
+        if self.real_stage_num > 1 and os.environ.get("HPB_PP_SPLIT_GROUPS", "1") != "0":
+            links = [(i, i + 1) for i in range(self.real_stage_num - 1)]
+            if virtual_chunk_num > 1:
+                links.append((self.real_stage_num - 1, 0))
+            specs, meaning = [], {}
+            for ring in range(self.device_num_per_stage):
+                ring_ranks = [ring + self.device_num_per_stage * i for i in range(self.real_stage_num)]
+                for a, b in links:
+                    for src, dst, kind in ((a, b, "f"), (b, a, "b")):
+                        rs, rd = ring_ranks[src], ring_ranks[dst]
+                        spec = (tuple(sorted((rs, rd))), f"pp-{rs}-{rd}-{kind}")
+                        specs.append(spec)
+                        meaning[spec] = (rs, rd, kind)
+            for spec, grp in cc.world_collective_groups(specs).items():
+                self._p2p_groups[meaning[spec]] = grp
         self._shared_groups = []
         for info in self.shared_parameters:
             ranks = sorted({self.peer_rank(s) for s in info.shared_stage})
@@ -136,24 +158,26 @@ class PipelineStage:
         return DTensor._wrap(buf, _build_layout(mesh, placements, buf.dim()))
 
     def _send(self, tensors: Sequence[torch.Tensor], dst_rank: int, key: Tuple[str, int]) -> None:
+        grp = self._p2p_groups.get((self.rank, dst_rank, key[0]))
         need_meta = self.dyn_shape or key not in self._sent_meta
         if need_meta:
-            dist.send_object_list([[self._describe(t) for t in tensors]], dst=dst_rank)
+            dist.send_object_list([[self._describe(t) for t in tensors]], dst=dst_rank, group=grp)
             self._sent_meta.add(key)
         for t in tensors:
             local = t.to_local() if isinstance(t, DTensor) else t
-            self._pending_sends.append((dist.isend(local.detach().contiguous(), dst=dst_rank), local))
+            self._pending_sends.append((dist.isend(local.detach().contiguous(), dst=dst_rank, group=grp), local))
 
     def _post_recv(self, src_rank: int, key: Tuple[str, int]) -> _Pending:
+        grp = self._p2p_groups.get((src_rank, self.rank, key[0]))
         metas = None if self.dyn_shape else self.meta_cache.get(key)
         if metas is None:
             box = [None]
-            dist.recv_object_list(box, src=src_rank)
+            dist.recv_object_list(box, src=src_rank, group=grp)
             metas = box[0]
             self.meta_cache[key] = metas
         dev = self._dev()
         bufs = [torch.empty(m[0], dtype=m[1], device=dev) for m in metas]
-        works = [dist.irecv(b, src=src_rank) for b in bufs]
+        works = [dist.irecv(b, src=src_rank, group=grp) for b in bufs]
         return _Pending(works, bufs, metas)
 
     def wait_sends(self) -> None:
