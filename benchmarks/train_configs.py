@@ -230,6 +230,10 @@ def run_pp(args, rank, world, dev):
 
     if tp > 1:
         Chunk = TPChunk  # noqa: F811
+        # The fused tensor-parallel kernels rendezvous with their peer inside the kernel while they
+        # occupy every SM; a pipeline send that the peer's progress depends on may then not get
+        # scheduled.  Inside pipeline stages tensor parallelism therefore uses NCCL + GEMM.
+        os.environ["HPB_FUSED_TP"] = "0"
     idx = [stage_rank + c * pp for c in range(chunks)]
     mods = [Chunk(i * per, (i + 1) * per, i == 0, i == n_virtual - 1) for i in idx]
     stages = [PipelineStage(m, i, n_virtual, device=dev) for m, i in zip(mods, idx)]
