@@ -3,9 +3,9 @@
 ``causal_attention(q[B,S,H,D], k[B,S,Hkv,D], v[B,S,Hkv,D]) -> [B,S,H,D]`` with
 grouped-query support.  The backend is chosen by ``HPB_ATTN``:
 
-* ``hpb``: this library's tcgen05 flash-attention kernels (``attention_sm100.cu``; head
-  dimension 128);
-* ``cudnn`` (default on CUDA): the fused cuDNN flash-attention graph through
+* ``hpb`` (default on CUDA for bf16 with head dimension 128): this library's tcgen05
+  flash-attention kernels (``attention_sm100.cu``);
+* ``cudnn`` (other shapes): the fused cuDNN flash-attention graph through
   ``torch.nn.functional.scaled_dot_product_attention``;
 * ``flash``: the generic flash backend of the same call;
 * ``math``: plain softmax(QK^T)V in fp32 (the CPU path and the test oracle).
@@ -72,8 +72,17 @@ def flash_attention_forward(q, k, v, causal: bool = True, scale: float = None):
     return out, lse
 
 
+def _default_backend(q: torch.Tensor) -> str:
+    if not q.is_cuda:
+        return "math"
+    from . import native
+    if q.shape[-1] == 128 and q.dtype == torch.bfloat16 and native.available():
+        return "hpb"
+    return "cudnn"
+
+
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
-    backend = os.environ.get("HPB_ATTN", "cudnn" if q.is_cuda else "math")
+    backend = os.environ.get("HPB_ATTN") or _default_backend(q)
     if backend == "math" or not q.is_cuda:
         return _math_attention(q, k, v)
     if backend == "hpb" and q.shape[-1] == 128 and q.dtype == torch.bfloat16:

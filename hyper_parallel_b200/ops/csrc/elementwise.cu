@@ -198,46 +198,86 @@ __global__ void colsum_kernel(const float* __restrict__ partial, void* __restric
 
 // -------------------------------------------------------------- SwiGLU ----
 // gu is [T, 2F] with gate in columns [0,F) and up in [F,2F);  out[T,F] = silu(gate)*up
-__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t T,
-                                  int F) {
+// Rows are walked by CTA pairs of (row, column chunk) without any division; every thread keeps two
+// independent 16-byte gate/up pairs in flight.
+__device__ __forceinline__ float fast_sigmoid(float g) { return __fdividef(1.f, 1.f + __expf(-g)); }
+
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t T, int F) {
   const int fv = F >> 3;
-  const int64_t total = T * fv;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t t = i / fv;
-    const int c = static_cast<int>(i - t * fv);
+  for (int64_t t = blockIdx.y; t < T; t += gridDim.y) {
     const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * F);
-    float g[8], u[8], o[8];
-    unpack8(row[c], g);
-    unpack8(row[fv + c], u);
+    uint4* orow = reinterpret_cast<uint4*>(out + t * F);
+    for (int c = blockIdx.x * 512 + threadIdx.x; c < fv; c += gridDim.x * 512) {
+      const int c2 = c + 256;
+      const bool two = c2 < fv;
+      const uint4 g0 = row[c], u0 = row[fv + c];
+      uint4 g1 = g0, u1 = u0;
+      if (two) {
+        g1 = row[c2];
+        u1 = row[fv + c2];
+      }
+      float g[8], u[8], o[8];
+      unpack8(g0, g);
+      unpack8(u0, u);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
-    reinterpret_cast<uint4*>(out + t * F)[c] = pack8(o);
+      for (int e = 0; e < 8; ++e) o[e] = g[e] * fast_sigmoid(g[e]) * u[e];
+      orow[c] = pack8(o);
+      if (two) {
+        unpack8(g1, g);
+        unpack8(u1, u);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = g[e] * fast_sigmoid(g[e]) * u[e];
+        orow[c2] = pack8(o);
+      }
+    }
   }
 }
 // dgu[T,2F]: dgate = dout*up*(sig + g*sig*(1-sig)), dup = dout*silu(g)
-__global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dout,
-                                  bf16* __restrict__ dgu, int64_t T, int F) {
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dout, bf16* __restrict__ dgu, int64_t T,
+                  int F) {
   const int fv = F >> 3;
-  const int64_t total = T * fv;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t t = i / fv;
-    const int c = static_cast<int>(i - t * fv);
+  for (int64_t t = blockIdx.y; t < T; t += gridDim.y) {
     const uint4* row = reinterpret_cast<const uint4*>(gu + t * 2 * F);
-    float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(row[c], g);
-    unpack8(row[fv + c], u);
-    unpack8(reinterpret_cast<const uint4*>(dout + t * F)[c], d);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float s = 1.f / (1.f + __expf(-g[e]));
-      dg[e] = d[e] * u[e] * s * (1.f + g[e] * (1.f - s));
-      du[e] = d[e] * g[e] * s;
-    }
+    const uint4* drow = reinterpret_cast<const uint4*>(dout + t * F);
     uint4* orow = reinterpret_cast<uint4*>(dgu + t * 2 * F);
-    orow[c] = pack8(dg);
-    orow[fv + c] = pack8(du);
+    for (int c = blockIdx.x * 512 + threadIdx.x; c < fv; c += gridDim.x * 512) {
+      const int c2 = c + 256;
+      const bool two = c2 < fv;
+      const uint4 g0 = row[c], u0 = row[fv + c], d0 = drow[c];
+      uint4 g1 = g0, u1 = u0, d1 = d0;
+      if (two) {
+        g1 = row[c2];
+        u1 = row[fv + c2];
+        d1 = drow[c2];
+      }
+      float g[8], u[8], d[8], dg[8], du[8];
+      unpack8(g0, g);
+      unpack8(u0, u);
+      unpack8(d0, d);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float sg = fast_sigmoid(g[e]);
+        dg[e] = d[e] * u[e] * sg * (1.f + g[e] * (1.f - sg));
+        du[e] = d[e] * g[e] * sg;
+      }
+      orow[c] = pack8(dg);
+      orow[fv + c] = pack8(du);
+      if (two) {
+        unpack8(g1, g);
+        unpack8(u1, u);
+        unpack8(d1, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float sg = fast_sigmoid(g[e]);
+          dg[e] = d[e] * u[e] * sg * (1.f + g[e] * (1.f - sg));
+          du[e] = d[e] * g[e] * sg;
+        }
+        orow[c2] = pack8(dg);
+        orow[fv + c2] = pack8(du);
+      }
+    }
   }
 }
 
@@ -487,14 +527,27 @@ extern "C" int hpb_swiglu_fwd(const void* gu, void* out, int64_t T, int F, int n
                               cudaStream_t s) {
   if (F % 8) return -2;
   if (T == 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256, num_sms), 256, 0, s>>>((const bf16*)gu, (bf16*)out, T, F);
+  {
+    const int gx = (F / 8 + 511) / 512;
+    int64_t gy = (static_cast<int64_t>(num_sms) * 8 + gx - 1) / gx;
+    if (gy > T) gy = T;
+    if (gy > 65535) gy = 65535;
+    swiglu_fwd_kernel<<<dim3(gx, static_cast<unsigned>(gy)), 256, 0, s>>>((const bf16*)gu, (bf16*)out, T, F);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int hpb_swiglu_bwd(const void* gu, const void* dout, void* dgu, int64_t T, int F,
                               int num_sms, cudaStream_t s) {
   if (F % 8) return -2;
   if (T == 0) return 0;
-  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256, num_sms), 256, 0, s>>>((const bf16*)gu, (const bf16*)dout, (bf16*)dgu, T, F);
+  {
+    const int gx = (F / 8 + 511) / 512;
+    int64_t gy = (static_cast<int64_t>(num_sms) * 8 + gx - 1) / gx;
+    if (gy > T) gy = T;
+    if (gy > 65535) gy = 65535;
+    swiglu_bwd_kernel<<<dim3(gx, static_cast<unsigned>(gy)), 256, 0, s>>>((const bf16*)gu, (const bf16*)dout,
+                                                                       (bf16*)dgu, T, F);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
