@@ -481,15 +481,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 //                                             added to the fp32 dQ in global memory with
 //                                             coalesced reductions (lane = head element)
 //
-//   warp 0      TMA producer: K, V once; (Q_i, dO_i) through a 3-stage ring
-//   warp 1      MMA issuer
-//   warps 2-5   softmax / dS
-//   warps 6-9   dQ reduction; both groups write dV / dK at the end
+//   warp 0       TMA producer: K, V once; (Q_i, dO_i) through a 3-stage ring
+//   warp 1       MMA issuer
+//   warps 2-9    softmax / dS: two groups of four warps, each owning 32 of the 64 query columns;
+//                they also write dV / dK at the end
+//   warps 10-13  dQ read-out and TMA reduce
 constexpr int BQ = 64;                        // query rows per step
 constexpr int QDO_STAGES = 3;
 constexpr int QTILE_BYTES = BQ * HD * 2;      // 16 KB
 constexpr int PT_BYTES = BN * BQ * 2;         // 16 KB
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 448;
 constexpr int BWD_SMEM = 2 * TILE_BYTES + QDO_STAGES * 2 * QTILE_BYTES + 2 * 2 * PT_BYTES + 2 * 2 * BQ * 4 + 1024 + 256;
 
 struct BwdParams {
@@ -561,7 +562,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&st_full[b], 1);
-      mbar_init(&ds_full[b], 4);
+      mbar_init(&ds_full[b], 8);
       mbar_init(&pt_free[b], 1);     // arrived by the dQ group once the TMA reduce has read the buffer
       mbar_init(&dq_full[b], 1);
       mbar_init(&dq_drained[b], 4);
@@ -648,23 +649,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint64_t qm_desc = make_smem_desc_sw128(qdo_addr, QTILE_BYTES / 2, 1024);   // Q / dO as MN-major B
       const uint64_t ptk_desc = make_smem_desc_sw128(pt_addr, 0, 1024);           // P^T / dS^T as K-major A
       const uint64_t ptm_desc = make_smem_desc_sw128(pt_addr, PT_BYTES, 1024);    // dS^T as MN-major B
-      // S^T(it) and dP^T(it) into buffer it & 1
-      auto issue_scores = [&](int it) {
+      // S^T(it) and dP^T(it) into buffer it & 1 (st_full follows the S^T product, issued last)
+      auto issue_dpt = [&](int it) {
         const int b = it & 1;
-        const uint64_t qa = desc_at(qk_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES);
-        const uint64_t doa = desc_at(qa, QTILE_BYTES);
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem_base + COL_ST + b * BQ, desc_at(k_desc, kb * HALF_BYTES + kk * 32),
-                     desc_at(qa, kb * (QTILE_BYTES / 2) + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
+        const uint64_t doa = desc_at(qk_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES + QTILE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16(tmem_base + COL_DPT + b * BQ, desc_at(v_desc, kb * HALF_BYTES + kk * 32),
                      desc_at(doa, kb * (QTILE_BYTES / 2) + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
+      };
+      auto issue_st = [&](int it) {
+        const int b = it & 1;
+        const uint64_t qa = desc_at(qk_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16(tmem_base + COL_ST + b * BQ, desc_at(k_desc, kb * HALF_BYTES + kk * 32),
+                     desc_at(qa, kb * (QTILE_BYTES / 2) + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
         umma_commit(&st_full[b]);
       };
       auto wait_qdo = [&](int it) {
@@ -676,9 +680,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         ok = wait_qdo(it);
         if (ok) {
           tc_fence_after();
-          issue_scores(it);
+          issue_dpt(it);
+          issue_st(it);
         }
       }
+      // Per step, once the softmax warps have written P^T / dS^T: dQ^T first (its read-out and
+      // the reduce that follows are the longest dependency of the walk), then dV / dK, then the
+      // scores of step it + 2 -- dP^T right away, S^T once the dQ^T tile that shares its buffer
+      // has been read out.
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -691,6 +700,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint64_t dsa = desc_at(pta, PT_BYTES);
         const uint64_t dsm = desc_at(ptm_desc, b * 2 * PT_BYTES + PT_BYTES);
         const uint32_t first = it ? 1u : 0u;
+        // dQ^T = K^T dS^T  (contraction over the 128 key rows: 8 steps of 16) into the S^T buffer
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + COL_ST + b * BQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
+                   kk ? 1u : 0u);
+        umma_commit(&dq_full[b]);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16)
         umma_f16(tmem_base + COL_DV, pta, doa, idesc_acc, first);
 #pragma unroll
@@ -701,18 +716,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int kk = 1; kk < 4; ++kk)
           umma_f16(tmem_base + COL_DK, desc_at(dsa, kk * 32), desc_at(qa, kk * 2048), idesc_acc, 1u);
         umma_commit(&qdo_empty[it % QDO_STAGES]);
-        // dQ^T = K^T dS^T  (contraction over the 128 key rows: 8 steps of 16) into the S^T buffer
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + COL_ST + b * BQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
-                   kk ? 1u : 0u);
-        umma_commit(&dq_full[b]);
         if (it + 2 < n_it) {
           ok = wait_qdo(it + 2);
-          if (ok) ok = mbar_wait_bounded(&dq_drained[b], par, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
           if (!ok) break;
           tc_fence_after();
-          issue_scores(it + 2);
+          issue_dpt(it + 2);
+          ok = mbar_wait_bounded(&dq_drained[b], par, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+          if (!ok) break;
+          tc_fence_after();
+          issue_st(it + 2);
         }
       }
       if (ok) umma_commit(acc_full);
@@ -723,20 +735,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     }
   } else {
-    const int wg = (warp - 2) >> 2;           // 0: softmax / dS, 1: dQ reduction
+    const int wg = (warp - 2) >> 2;           // 0, 1: softmax / dS of query columns [32 wg, 32 wg + 32); 2: dQ
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;      // TMEM lane handled by this thread
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    if (wg == 0) {
+    if (wg < 2) {
       // ------------------------------------------------------ softmax / dS --
-      const int tid = threadIdx.x - 64;       // 0..127 inside the group
+      const int tid = threadIdx.x - 64;       // 0..255 over both softmax groups; 0..127 stage the statistics
       const int kv_row = k0 + row;
       const bool row_live = kv_row < p.S;
       const int sw = row & 7;
       auto load_stat = [&](int it) -> float {
         // threads 0..63 fetch lse (scaled to log2), 64..127 fetch delta, of step `it`
-        if (it >= n_it) return 0.f;
+        if (it >= n_it || tid >= 128) return 0.f;
         const int head = kv_head * group + it / per_head;
         const int q = (i_start + it % per_head) * BQ + (tid & 63);
         if (q >= p.S) return tid < 64 ? INFINITY : 0.f;
@@ -748,13 +760,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
         float* stat = sStat + b * 2 * BQ;
-        stat[tid] = stat_next;                 // buffer b was last read two steps ago
+        // P^T / dS^T buffer b is free again (the dQ tile staged in it has been read); this also
+        // means that all eight softmax warps have finished step it - 2, so the statistics buffer
+        // b can be rewritten
+        ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+        if (!ok) break;
+        if (tid < 128) stat[tid] = stat_next;
         stat_next = load_stat(it + 1);
         __syncwarp();
-        if (lane == 0) mbar_arrive(&stat_full[b]);
+        if (lane == 0 && wg == 0) mbar_arrive(&stat_full[b]);
         ok = mbar_wait_bounded(&stat_full[b], par, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
         if (ok) ok = mbar_wait_bounded(&st_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
-        if (ok) ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
         tc_fence_after();
         const int q0 = (i_start + it % per_head) * BQ;
@@ -764,41 +780,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const bool masked = (k0 + quarter * 32 + 32 > p.S) || (p.causal && k0 + quarter * 32 + 31 - q0 > 0);
         uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
         uint8_t* ds_row = pt_row + PT_BYTES;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        {
+          const int c = wg;                    // this group's 32 query columns
           uint32_t rs[32], rp[32];
           tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, rs);
           tmem_ld_32x32b_x32(tmem_base + COL_DPT + b * BQ + c * 32 + lane_off, rp);
           tmem_ld_wait();
-          float pv[32], dv[32];
+          uint32_t pk[16], dk[16];
+          const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 ls = *reinterpret_cast<const float4*>(stat + c * 32 + 4 * i4);
-            const float4 dl = *reinterpret_cast<const float4*>(stat + BQ + c * 32 + 4 * i4);
-            const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
-#pragma unroll
-            for (int e4 = 0; e4 < 4; ++e4) {
-              const int i = 4 * i4 + e4;
-              const int col = c * 32 + i;
-              float e = fast_exp2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lsv[e4]));
-              if (masked && (!row_live || col < cmin)) e = 0.f;
-              pv[i] = e;
-              dv[i] = e * (__uint_as_float(rp[i]) - dlv[e4]);
+          for (int i2 = 0; i2 < 16; ++i2) {
+            const float2 ls = *reinterpret_cast<const float2*>(stat + c * 32 + 2 * i2);
+            const float2 dl = *reinterpret_cast<const float2*>(stat + BQ + c * 32 + 2 * i2);
+            float2 e = fma2(make_float2(__uint_as_float(rs[2 * i2]), __uint_as_float(rs[2 * i2 + 1])), sc2,
+                            make_float2(-ls.x, -ls.y));
+            e.x = fast_exp2(e.x);
+            e.y = fast_exp2(e.y);
+            if (masked) {
+              const int col = c * 32 + 2 * i2;
+              if (!row_live || col < cmin) e.x = 0.f;
+              if (!row_live || col + 1 < cmin) e.y = 0.f;
             }
+            const float2 d = mul2(e, add2(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])),
+                                          make_float2(-dl.x, -dl.y)));
+            const __nv_bfloat162 eb = __floats2bfloat162_rn(e.x, e.y), db = __floats2bfloat162_rn(d.x, d.y);
+            pk[i2] = *reinterpret_cast<const uint32_t*>(&eb);
+            dk[i2] = *reinterpret_cast<const uint32_t*>(&db);
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 a, d;
-            __nv_bfloat162* ab = reinterpret_cast<__nv_bfloat162*>(&a);
-            __nv_bfloat162* db = reinterpret_cast<__nv_bfloat162*>(&d);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              ab[e] = __floats2bfloat162_rn(pv[8 * q4 + 2 * e], pv[8 * q4 + 2 * e + 1]);
-              db[e] = __floats2bfloat162_rn(dv[8 * q4 + 2 * e], dv[8 * q4 + 2 * e + 1]);
-            }
             const int chunk = c * 4 + q4;
-            *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) = a;
-            *reinterpret_cast<uint4*>(ds_row + ((chunk ^ sw) << 4)) = d;
+            *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) =
+                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+            *reinterpret_cast<uint4*>(ds_row + ((chunk ^ sw) << 4)) =
+                make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
           }
         }
         fence_proxy_async();
@@ -811,7 +826,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // dQ^T (lane = head element, column = query row) is transposed through the P^T / dS^T
       // buffer of the same step -- free once the dQ product has retired -- as a dense fp32
       // [64 query rows x 128] tile, which one TMA reduce adds to the fp32 dQ in global memory.
-      const int tid = threadIdx.x - 192;      // 0..127 inside the group
+      const int tid = threadIdx.x - 320;      // 0..127 inside the group
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -821,17 +836,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int head = kv_head * group + it / per_head;
         const int q0 = (i_start + it % per_head) * BQ;
         float* stage = reinterpret_cast<float*>(sPT + b * 2 * PT_BYTES) + row;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) stage[(c * 32 + i) * HD] = __uint_as_float(r[i]) * p.scale;
-        }
+        uint32_t r[64];
+        tmem_ld32(tmem_base + COL_ST + b * BQ + lane_off, r);
+        tmem_ld32(tmem_base + COL_ST + b * BQ + 32 + lane_off, r + 32);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&dq_drained[b]);   // the S^T buffer may be overwritten
+        // the staging tile lies over P^T / dS^T of this step: the dV / dK products, issued after
+        // the dQ^T product, must have retired as well (their commit frees the Q / dO stage)
+        ok = mbar_wait_bounded(&qdo_empty[it % QDO_STAGES], (it / QDO_STAGES) & 1, abort_flag, p.status,
+                               kTimeoutEmptyBarrier, blockIdx.x);
+        if (!ok) break;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) stage[i * HD] = __uint_as_float(r[i]) * p.scale;
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(&stage_full[b]);
@@ -847,7 +865,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (tid == 0) tma_store_wait<0>();
     }
     // ------------------------------------------------- dV / dK write-out --
-    if (ok && n_it > 0) {
+    if (ok && n_it > 0 && wg < 2) {
       ok = mbar_wait_bounded(acc_full, 0, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
       if (ok) {
         tc_fence_after();
