@@ -1,0 +1,104 @@
+"""HSDP matrix on 4 gloo ranks against a single-process SGD run (the reference's
+tests/torch/hsdp/hsdp.py cases): pure DP, levels 1-3, fully / partially sharded, with and without
+gradient accumulation, synchronous / asynchronous hooks, bucket fusion, prefetch."""
+import pytest
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from dist_utils import run_distributed
+
+HID, LAYERS, BATCH, STEPS, LR = 32, 3, 16, 3, 0.05
+
+
+def _net():
+    torch.manual_seed(5)
+    return nn.Sequential(*[nn.Sequential(nn.Linear(HID, HID), nn.Tanh()) for _ in range(LAYERS)])
+
+
+def _data():
+    g = torch.Generator().manual_seed(1)
+    return torch.randn(STEPS, BATCH, HID, generator=g), torch.randn(STEPS, BATCH, HID, generator=g)
+
+
+def _reference(acc):
+    net = _net()
+    xs, ys = _data()
+    opt = torch.optim.SGD(net.parameters(), lr=LR)
+    losses = []
+    for s in range(STEPS):
+        opt.zero_grad()
+        tot = 0.0
+        for xm, ym in zip(xs[s].chunk(acc), ys[s].chunk(acc)):
+            loss = F.mse_loss(net(xm), ym) / acc
+            loss.backward()
+            tot += loss.item()
+        opt.step()
+        losses.append(tot)
+    return losses, [p.detach().clone() for p in net.parameters()]
+
+
+def _worker(rank, world, level, shard_size, acc, mode):
+    import torch.distributed as dist
+    import hyper_parallel_b200 as hp
+    ref_losses, ref_params = _reference(acc)
+    net = _net()
+    # gradients are summed over the ranks (as in the reference); grad_scale turns the sum into the mean
+    kw = dict(shard_size=shard_size, threshold=0, optimizer_level=level, enable_grad_accumulation=acc > 1,
+              grad_scale=1.0 / world,
+              comm_async=mode in ("async", "fusion_async"), comm_fusion=mode in ("fusion", "fusion_async"))
+    if mode == "per_layer_prefetch":
+        for layer in net:
+            hp.hsdp(layer, **kw)
+        hp.hsdp(net, **kw)
+        for i, layer in enumerate(net):
+            if i + 1 < LAYERS:
+                layer.set_forward_prefetch_cells([net[i + 1]])
+            if i > 0:
+                layer.set_backward_prefetch_cells([net[i - 1]])
+    else:
+        hp.hsdp(net, **kw)
+    xs, ys = _data()
+    opt = torch.optim.SGD(net.parameters(), lr=LR)
+    losses = []
+    for s in range(STEPS):
+        net.zero_grads()
+        x, y = xs[s].chunk(world)[rank], ys[s].chunk(world)[rank]
+        tot = torch.zeros(())
+        chunks = list(zip(x.chunk(acc), y.chunk(acc)))
+        for i, (xm, ym) in enumerate(chunks):
+            net.set_requires_grad_sync(i == len(chunks) - 1)
+            # every rank holds 1/world of the batch: the global mean is the mean of the rank means
+            loss = F.mse_loss(net(xm), ym) / acc
+            loss.backward()
+            tot += loss.detach()
+        hp.hsdp_sync_stream()
+        opt.step()
+        dist.all_reduce(tot)
+        losses.append((tot / world).item())
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-5, (level, shard_size, acc, mode, losses, ref_losses)
+    # parameters: gather the shards over the shard group and compare
+    for p, ref in zip(net.parameters(), ref_params):
+        hpar = getattr(p, "_hsdp_param", None)
+        local = p.detach().contiguous()
+        if hpar is not None and hpar.shard_size > 1:
+            grp = hpar.sharded_group_info.group
+            parts = [torch.empty_like(local) for _ in range(hpar.shard_size)]
+            dist.all_gather(parts, local, group=grp)
+            local = torch.cat(parts, 0)
+        assert local.shape == ref.shape and torch.allclose(local, ref, atol=1e-5), (level, shard_size, acc, mode)
+
+
+CASES = [("level1", 1, 1, "sync"),                       # pure data parallel
+         ("level1", 4, 1, "sync"), ("level2", 4, 1, "sync"), ("level3", 4, 1, "sync"),      # fully sharded
+         ("level1", 2, 1, "sync"), ("level2", 2, 1, "sync"), ("level3", 2, 1, "sync"),      # shard 2 x replicate 2
+         ("level1", 4, 2, "sync"), ("level2", 2, 2, "sync"), ("level3", 4, 2, "sync"),      # gradient accumulation
+         ("level2", 4, 1, "async"), ("level3", 2, 1, "async"),
+         ("level2", 4, 1, "fusion"), ("level3", 2, 2, "fusion_async"),
+         ("level3", 4, 1, "per_layer_prefetch")]
+
+
+@pytest.mark.parametrize("level,shard_size,acc,mode", CASES)
+def test_hsdp_matches_single_process(level, shard_size, acc, mode):
+    run_distributed(_worker, 4, level, shard_size, acc, mode)
