@@ -535,8 +535,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint64_t* dq_full = pt_free + 2;               // [2]
   uint64_t* dq_drained = dq_full + 2;            // [2]  (4 warp arrivals)
   uint64_t* stat_full = dq_drained + 2;          // [2]  lse / delta of a step staged (4 warp arrivals)
-  uint64_t* stage_full = stat_full + 2;          // [2]  fp32 dQ tile staged (4 warp arrivals)
-  uint64_t* acc_full = stage_full + 2;           // [1]
+  uint64_t* acc_full = stat_full + 2;            // [1]
   uint64_t* drain_bar = acc_full + 1;            // [1]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
@@ -563,11 +562,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int b = 0; b < 2; ++b) {
       mbar_init(&st_full[b], 1);
       mbar_init(&ds_full[b], 8);
-      mbar_init(&pt_free[b], 1);     // arrived by the dQ group once the TMA reduce has read the buffer
+      mbar_init(&pt_free[b], 4);     // one arrival per dQ warp once its TMA reduce has read the buffer
       mbar_init(&dq_full[b], 1);
       mbar_init(&dq_drained[b], 4);
       mbar_init(&stat_full[b], 4);
-      mbar_init(&stage_full[b], 4);
     }
     mbar_init(acc_full, 1);
     mbar_init(drain_bar, 1);
@@ -826,7 +824,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // dQ^T (lane = head element, column = query row) is transposed through the P^T / dS^T
       // buffer of the same step -- free once the dQ product has retired -- as a dense fp32
       // [64 query rows x 128] tile, which one TMA reduce adds to the fp32 dQ in global memory.
-      const int tid = threadIdx.x - 320;      // 0..127 inside the group
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -835,7 +832,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         const int head = kv_head * group + it / per_head;
         const int q0 = (i_start + it % per_head) * BQ;
-        float* stage = reinterpret_cast<float*>(sPT + b * 2 * PT_BYTES) + row;
+        // every warp stages and reduces its own 32 head elements: a dense [64 query rows x 32]
+        // fp32 tile of 8 KB, added to global memory by one TMA reduce per warp
+        float* stage = reinterpret_cast<float*>(sPT + b * 2 * PT_BYTES + quarter * (BQ * 32 * 4)) + lane;
         uint32_t r[64];
         tmem_ld32(tmem_base + COL_ST + b * BQ + lane_off, r);
         tmem_ld32(tmem_base + COL_ST + b * BQ + 32 + lane_off, r + 32);
@@ -849,20 +848,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                                kTimeoutEmptyBarrier, blockIdx.x);
         if (!ok) break;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) stage[i * HD] = __uint_as_float(r[i]) * p.scale;
+        for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&stage_full[b]);
-        if (tid == 0) {
-          ok = mbar_wait_bounded(&stage_full[b], par, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
-          if (!ok) break;
-          tma_reduce_add_3d(&tmap_dq, sPT + b * 2 * PT_BYTES, head * HD, q0, batch);
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmap_dq, sPT + b * 2 * PT_BYTES + quarter * (BQ * 32 * 4), head * HD + quarter * 32, q0,
+                            batch);
           tma_store_commit();
           tma_store_wait_read<0>();
-          mbar_arrive(&pt_free[b]);                   // the softmax group may write P^T / dS^T again
+          mbar_arrive(&pt_free[b]);                   // 4 arrivals: the softmax groups may write P^T / dS^T again
         }
       }
-      if (tid == 0) tma_store_wait<0>();
+      if (lane == 0) tma_store_wait<0>();
     }
     // ------------------------------------------------- dV / dK write-out --
     if (ok && n_it > 0 && wg < 2) {
@@ -1103,7 +1100,7 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
     if (enc == nullptr) return -1;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(Hq) * fa::HD, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(B)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(Hq) * fa::HD * 4, static_cast<cuuint64_t>(S) * Hq * fa::HD * 4};
-    cuuint32_t box[3] = {fa::HD, fa::BQ, 1};
+    cuuint32_t box[3] = {32, fa::BQ, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult cr = enc(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
