@@ -20,6 +20,10 @@ from .core.pipeline_parallel import (BatchDimSpec, MetaStep, MetaStepType, Pipel
                                      ScheduleGPipe, ScheduleInterleaved1F1B, SharedParameterInfo,
                                      validate_pipeline_execution)
 
+from .core import function_override as _function_override
+
+_function_override.install()
+
 __all__ = [
     "get_platform", "hsdp", "hsdp_sync_stream", "HSDPCell", "Layout", "DTensor", "DeviceMesh",
     "init_device_mesh", "init_parameters", "shard_module", "shard", "custom_shard",

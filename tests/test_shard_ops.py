@@ -160,3 +160,24 @@ def _battery_worker(rank, world):
 
 def test_distributed_ops_match_single_device_on_four_ranks():
     run_distributed(_battery_worker, 4)
+
+
+def _hook_worker(rank, world):
+    import hyper_parallel_b200 as hp
+    from torch import nn
+    lay = hp.Layout((2,), ("dp",))
+    lin = nn.Linear(4, 4, bias=False)
+    lin.weight = nn.Parameter(hp.distribute_tensor(lin.weight.detach(), lay("None", "None")))
+    seen = []
+    lin.register_full_backward_pre_hook(lambda m, go: seen.append("pre"))
+    lin.register_full_backward_hook(lambda m, gi, go: seen.append(("post", tuple(go[0].shape))))
+    x = hp.DTensor.from_local(torch.randn(3, 4, requires_grad=True), lay("dp", "None"))
+    y = lin(x)
+    assert isinstance(y, hp.DTensor)
+    y.to_local().sum().backward()
+    assert seen == ["pre", ("post", (3, 4))], seen
+    assert x.to_local().grad is not None and lin.weight.to_local().grad is not None
+
+
+def test_module_full_backward_hooks_work_with_dtensor_arguments():
+    run_distributed(_hook_worker, 2)
