@@ -1,0 +1,143 @@
+"""custom_shard, parallelize_value_and_grad, custom distributed-op registration through the
+environment, DeviceMesh.from_group / flatten, and tied parameters across pipeline stages."""
+import os
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from dist_utils import run_distributed
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _custom_shard_worker(rank, world):
+    import hyper_parallel_b200 as hp
+    lay = hp.Layout((2, 2), ("dp", "mp"))
+    g = torch.Generator().manual_seed(2)
+    X = torch.randn(8, 6, generator=g)
+    x = hp.distribute_tensor(X.clone(), lay("dp", "mp"))
+
+    def local_fn(t, k):                      # runs on the local shard
+        assert not isinstance(t, hp.DTensor) and t.shape == (4, 6)
+        return t * k, int(t.shape[0])
+
+    fn = hp.custom_shard(local_fn, lay.mesh, out_placements=(lay("dp", "None"), None),
+                         in_placements=(lay("dp", "None"), None))
+    y, n = fn(x, 3.0)                        # x is redistributed from ("dp","mp") to ("dp","None")
+    assert isinstance(y, hp.DTensor) and n == 4
+    assert torch.allclose(y.full_tensor(), X * 3.0)
+    # parallelize_value_and_grad: a loss replicated on every rank is seeded with 1 / repeat_num
+    W = torch.randn(6, 6, generator=g)
+    w = hp.distribute_tensor(W.clone(), lay("None", "None"))
+    w.requires_grad_(True)
+    xr = hp.distribute_tensor(X.clone(), lay("None", "None"))
+
+    def loss_fn():
+        return (torch.matmul(xr, w) ** 2).mean()
+
+    loss, grads = hp.parallelize_value_and_grad(loss_fn, [w])()
+    Wr = W.clone().requires_grad_(True)
+    ((X @ Wr) ** 2).mean().backward()
+    total = grads[0].clone()
+    torch.distributed.all_reduce(total)      # what a data-parallel reduction would produce
+    assert torch.allclose(total, Wr.grad, atol=1e-5)
+
+
+def test_custom_shard_and_value_and_grad():
+    run_distributed(_custom_shard_worker, 4)
+
+
+def _custom_op_worker(rank, world):
+    os.environ["HYPER_PARALLEL_OPS_YAML_DIR"] = os.path.join(HERE, "custom_ops")
+    os.environ["HYPER_PARALLEL_OPS_PYTHON_PATH"] = os.path.join(HERE, "custom_ops")
+    import importlib
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200.core.shard import _op_dispatch
+    importlib.reload(_op_dispatch)           # picks the environment up, as a fresh process would
+    from hyper_parallel_b200.core.shard.ops.parallel_ops import get_distributed_op
+    rule = get_distributed_op("stack_rows")
+    assert rule is not None and type(rule).__name__ == "StackDistributedOp"
+    lay = hp.Layout((2,), ("dp",))
+    out = rule.infer_layout((lay("dp", "None"), lay("dp", "None")), ())
+    assert tuple(out.alias_tensor_map) == ("None", "dp", "None")
+    # the built-in catalogue is still there
+    assert get_distributed_op("matmul") is not None
+
+
+def test_custom_distributed_op_registration_through_the_environment():
+    run_distributed(_custom_op_worker, 2)
+
+
+def _mesh_worker(rank, world):
+    import torch.distributed as dist
+    import hyper_parallel_b200 as hp
+    mesh = hp.init_device_mesh("cpu", (2, 2), mesh_dim_names=("dp", "tp"))
+    flat = mesh.flatten("all")
+    assert flat.size() == 4 and flat.ndim == 1 and flat.get_local_rank() == rank
+    assert mesh.flatten("all") is flat                                   # cached on the root
+    t = torch.ones(1) * rank
+    dist.all_reduce(t, group=flat.get_group())
+    assert t.item() == 6
+    sub = mesh["tp"]
+    assert sub.size() == 2 and set(sub.rank_list) == {rank - rank % 2, rank - rank % 2 + 1}
+    dm = hp.DeviceMesh.from_group(sub.get_group(), "cpu", mesh_dim_names=("tp",))
+    assert dm.size() == 2 and dm.get_local_rank() == rank % 2
+    t = torch.ones(1)
+    dist.all_reduce(t, group=dm.get_group())
+    assert t.item() == 2
+    assert isinstance(mesh.to_hash(), int) and tuple(mesh.get_coordinate()) == (rank // 2, rank % 2)
+
+
+def test_device_mesh_flatten_from_group_submesh():
+    run_distributed(_mesh_worker, 4)
+
+
+class _First(nn.Module):
+    def __init__(self, emb):
+        super().__init__()
+        self.emb = emb
+        self.lin = nn.Linear(8, 8)
+
+    def forward(self, tok):
+        return torch.tanh(self.lin(F.embedding(tok, self.emb)))
+
+
+class _Last(nn.Module):
+    def __init__(self, emb):
+        super().__init__()
+        self.emb = emb                       # tied: output projection uses the embedding matrix
+
+    def forward(self, h):
+        return (h @ self.emb.t()).pow(2).mean() / 2
+
+
+def _tied_worker(rank, world):
+    from hyper_parallel_b200 import PipelineStage, SharedParameterInfo
+    from hyper_parallel_b200.core.pipeline_parallel import Schedule1F1B
+    torch.manual_seed(3)
+    emb_ref = nn.Parameter(torch.randn(12, 8))
+    first_ref = _First(emb_ref)
+    last_ref = _Last(emb_ref)
+    tok = torch.randint(0, 12, (4, 5), generator=torch.Generator().manual_seed(4))
+    for tm in tok.chunk(2):
+        last_ref(first_ref(tm)).backward()
+    # two stages, each with its own copy of the embedding; stage 1's copy starts different and is
+    # overwritten by the broadcast from stage 0; gradients are summed after the schedule
+    torch.manual_seed(3)
+    emb0 = nn.Parameter(torch.randn(12, 8))
+    first = _First(emb0)
+    if rank == 0:
+        mod, emb = first, emb0
+    else:
+        emb = nn.Parameter(torch.zeros(12, 8))
+        mod = _Last(emb)
+    stage = PipelineStage(mod, rank, 2, device="cpu", shared_parameters=[SharedParameterInfo(emb, [0, 1])])
+    sched = Schedule1F1B(stage, 2)
+    sched.run(tok) if rank == 0 else sched.run()
+    assert torch.allclose(emb.detach(), emb_ref.detach())               # broadcast at init
+    assert torch.allclose(emb.grad, emb_ref.grad, atol=1e-6)            # all-reduced after the schedule
+
+
+def test_pipeline_tied_parameters_are_broadcast_and_their_grads_summed():
+    run_distributed(_tied_worker, 2)
