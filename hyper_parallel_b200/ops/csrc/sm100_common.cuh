@@ -77,16 +77,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One probe of an mbarrier phase.  The suspend-time hint lets the hardware park the thread until
+// the phase completes (or the hint, 20 us, runs out) instead of returning at once: a polling warp
+// then takes no issue slots from the warps that share its scheduler.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
       : "memory");
   return ok != 0;
 }
@@ -101,7 +104,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   uint32_t it = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 0x3ff) == 0) {
+    if ((++it & 0x3f) == 0) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
         *abort_flag = 1;
