@@ -69,7 +69,9 @@ __device__ __forceinline__ void tmem_st_wait() {
 // Descriptor of the same operand `bytes` further into shared memory (the start-address field
 // holds address >> 4 and cannot overflow inside the 228 KB window).
 __device__ __forceinline__ uint64_t desc_at(uint64_t desc, uint32_t bytes) {
-  return desc + static_cast<uint64_t>(bytes >> 4);
+  // one 32-bit add: the address field sits in the low word and cannot carry out of it
+  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+  return (desc & 0xffffffff00000000ull) | lo;
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
