@@ -124,13 +124,17 @@ class LlamaBlock(nn.Module):
         qkv = ops.linear(x, self.wqkv)                      # [T, (nh + 2 nkv) hd]
         if qkv.is_cuda:
             qkv = _RopeQK.apply(qkv, nh, nkv, hd, seq_len, cfg.rope_theta)
-            q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+            # attention reads q / k / v as views of the packed projection output and returns one
+            # packed gradient: no split / concatenation copies
+            a = attn_ops.causal_attention_packed(qkv.view(batch, seq_len, -1), nh, nkv)
+            q = None
         else:
             q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
             q = ops.apply_rope(q.reshape(-1, nh, hd), seq_len, cfg.rope_theta).reshape(-1, nh * hd)
             k = ops.apply_rope(k.reshape(-1, nkv, hd), seq_len, cfg.rope_theta).reshape(-1, nkv * hd)
-        a = attn_ops.causal_attention(q.view(batch, seq_len, nh, hd), k.view(batch, seq_len, nkv, hd),
-                                      v.view(batch, seq_len, nkv, hd))
+        if q is not None:
+            a = attn_ops.causal_attention(q.view(batch, seq_len, nh, hd), k.view(batch, seq_len, nkv, hd),
+                                          v.view(batch, seq_len, nkv, hd))
         o = ops.linear(a.reshape(batch * seq_len, nh * hd), self.wo)
         x, resid = ops.add_rmsnorm(o, resid, self.ffn_norm, cfg.norm_eps)
         gu = ops.linear(x, self.w_gate_up)

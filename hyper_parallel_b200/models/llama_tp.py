@@ -100,13 +100,15 @@ class TPLlamaBlock(nn.Module):
         qkv = tp_ops.column_parallel_linear(x, _local(self.wqkv), self.group)        # [T, (nh + 2 nkv) hd]
         if qkv.is_cuda:
             qkv = _RopeQK.apply(qkv, nh, nkv, hd, seq_len, cfg.rope_theta)
-            q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+            a = attn_ops.causal_attention_packed(qkv.view(batch, seq_len, -1), nh, nkv)
+            q = None
         else:
             q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
             q = ops.apply_rope(q.reshape(-1, nh, hd), seq_len, cfg.rope_theta).reshape(-1, nh * hd)
             k = ops.apply_rope(k.reshape(-1, nkv, hd), seq_len, cfg.rope_theta).reshape(-1, nkv * hd)
-        a = attn_ops.causal_attention(q.view(batch, seq_len, nh, hd), k.view(batch, seq_len, nkv, hd),
-                                      v.view(batch, seq_len, nkv, hd))
+        if q is not None:
+            a = attn_ops.causal_attention(q.view(batch, seq_len, nh, hd), k.view(batch, seq_len, nkv, hd),
+                                          v.view(batch, seq_len, nkv, hd))
         o = tp_ops.row_parallel_linear(a.reshape(batch * seq_len, nh * hd), _local(self.wo), self.group)
         x, resid = ops.add_rmsnorm(o, resid, ffn_norm, cfg.norm_eps)
         gu = tp_ops.column_parallel_linear(x, _local(self.w_gate_up), self.group)

@@ -98,8 +98,13 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
     return o.transpose(1, 2)
 
 
-def flash_attention_backward(q, k, v, out, lse, do, causal: bool = True, scale: float = None):
-    """tcgen05 flash attention backward: ``(dq, dk, dv)`` bf16, contiguous ``[B,S,H,128]``."""
+def flash_attention_backward(q, k, v, out, lse, do, causal: bool = True, scale: float = None, packed: bool = False):
+    """tcgen05 flash attention backward: ``(dq, dk, dv)`` bf16 ``[B,S,H,128]``.
+
+    With ``packed=True`` the three gradients are the column ranges ``[dq | dk | dv]`` of ONE
+    ``[B, S, (H + 2 Hkv) * 128]`` tensor (returned as a fourth value), which is the gradient of a
+    fused qkv projection output without any concatenation copy.
+    """
     import ctypes
     from . import native
     B, S, H, D = q.shape
@@ -110,23 +115,77 @@ def flash_attention_backward(q, k, v, out, lse, do, causal: bool = True, scale: 
     if not getattr(lib, "_hpb_fa_bwd_bound", False):
         vp, ci, cll, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
         lib.hpb_flash_attn_bwd.argtypes = [vp, cll, cll, vp, cll, cll, vp, cll, cll, vp, vp, vp, cll, cll, vp, vp, vp,
-                                           vp, vp, ci, ci, ci, ci, cf, ci, vp, vp]
+                                           cll, cll, vp, vp, ci, ci, ci, ci, cf, ci, vp, vp]
         lib.hpb_flash_attn_bwd.restype = ci
         lib._hpb_fa_bwd_bound = True
     dev = q.device
-    dq = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=dev)
-    dk = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
-    dv = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
+    if packed:
+        W = (H + 2 * Hkv) * D
+        dqkv = torch.empty((B, S, W), dtype=torch.bfloat16, device=dev)
+        dq = dqkv[..., :H * D].view(B, S, H, D)
+        dk = dqkv[..., H * D:(H + Hkv) * D].view(B, S, Hkv, D)
+        dv = dqkv[..., (H + Hkv) * D:].view(B, S, Hkv, D)
+        dq_stride = dkv_stride = W
+    else:
+        dqkv = None
+        dq = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=dev)
+        dk = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
+        dv = torch.empty((B, S, Hkv, D), dtype=torch.bfloat16, device=dev)
+        dq_stride, dkv_stride = H * D, Hkv * D
     dq_acc = torch.empty((B, S, H, D), dtype=torch.float32, device=dev)
     delta = torch.empty((B, H, S), dtype=torch.float32, device=dev)
     rc = lib.hpb_flash_attn_bwd(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1),
                                 v.data_ptr(), v.stride(0), v.stride(1), out.data_ptr(), lse.data_ptr(),
                                 do.data_ptr(), do.stride(0), do.stride(1), dq.data_ptr(), dk.data_ptr(),
-                                dv.data_ptr(), dq_acc.data_ptr(), delta.data_ptr(), B, S, H, Hkv,
-                                float(scale if scale is not None else 1.0 / math.sqrt(D)), int(causal),
+                                dv.data_ptr(), dq_stride, dkv_stride, dq_acc.data_ptr(), delta.data_ptr(), B, S, H,
+                                Hkv, float(scale if scale is not None else 1.0 / math.sqrt(D)), int(causal),
                                 native.status_word(dev).data_ptr(), native.stream(dev))
     native.check(rc, "hpb_flash_attn_bwd")
+    if packed:
+        return dq, dk, dv, dqkv
     return dq, dk, dv
+
+
+class _FlashAttentionPacked(torch.autograd.Function):
+    """Attention on a fused projection output ``qkv[B, S, (H + 2 Hkv) * 128]``: q / k / v are read as
+    strided views and the backward writes one packed gradient, so no split / concat copy exists."""
+
+    @staticmethod
+    def forward(ctx, qkv, H, Hkv):
+        B, S, W = qkv.shape
+        D = W // (H + 2 * Hkv)
+        q = qkv[..., :H * D].view(B, S, H, D)
+        k = qkv[..., H * D:(H + Hkv) * D].view(B, S, Hkv, D)
+        v = qkv[..., (H + Hkv) * D:].view(B, S, Hkv, D)
+        out, lse = flash_attention_forward(q, k, v, causal=True)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.heads = (H, Hkv, D)
+        return out
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, out, lse = ctx.saved_tensors
+        H, Hkv, D = ctx.heads
+        B, S, W = qkv.shape
+        q = qkv[..., :H * D].view(B, S, H, D)
+        k = qkv[..., H * D:(H + Hkv) * D].view(B, S, Hkv, D)
+        v = qkv[..., (H + Hkv) * D:].view(B, S, Hkv, D)
+        dqkv = flash_attention_backward(q, k, v, out, lse, do, causal=True, packed=True)[3]
+        return dqkv, None, None
+
+
+def causal_attention_packed(qkv: torch.Tensor, num_heads: int, num_kv_heads: int) -> torch.Tensor:
+    """``qkv[B, S, (H + 2 Hkv) * D]`` (q heads, then k heads, then v heads) -> ``[B, S, H, D]``."""
+    B, S, W = qkv.shape
+    D = W // (num_heads + 2 * num_kv_heads)
+    backend = os.environ.get("HPB_ATTN") or _default_backend(qkv.view(B, S, -1, D))
+    if backend == "hpb" and D == 128 and qkv.dtype == torch.bfloat16 and qkv.is_cuda and qkv.stride(2) == 1 \
+            and qkv.stride(1) % 8 == 0 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 \
+            and os.environ.get("HPB_ATTN_BWD", "hpb") == "hpb":
+        return _FlashAttentionPacked.apply(qkv, num_heads, num_kv_heads)
+    q, k, v = qkv.split([num_heads * D, num_kv_heads * D, num_kv_heads * D], dim=-1)
+    return causal_attention(q.reshape(B, S, num_heads, D) if not q.is_contiguous() else q.view(B, S, num_heads, D),
+                            k.reshape(B, S, num_kv_heads, D), v.reshape(B, S, num_kv_heads, D))
 
 
 class _FlashAttention(torch.autograd.Function):

@@ -502,8 +502,9 @@ struct BwdParams {
   const float* lse;    // [B, Hq, S]
   const float* delta;  // [B, Hq, S]  rowsum(dO o O)
   float* dQ;           // [B, S, Hq, 128] fp32, zero-initialised
-  __nv_bfloat16* dK;   // [B, S, Hkv, 128]
-  __nv_bfloat16* dV;   // [B, S, Hkv, 128]
+  __nv_bfloat16* dK;   // [B, S, Hkv, 128], token stride dkv_row_stride elements
+  __nv_bfloat16* dV;   // likewise
+  long long dkv_row_stride;
   int* status;
 };
 
@@ -871,7 +872,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int kv_row = k0 + row;
         const float mul = wg == 0 ? 1.f : p.scale;
         __nv_bfloat16* dst = (wg == 0 ? p.dV : p.dK) +
-                             ((static_cast<int64_t>(batch) * p.S + kv_row) * p.Hkv + kv_head) * HD;
+                             (static_cast<int64_t>(batch) * p.S + kv_row) * p.dkv_row_stride + kv_head * HD;
         const uint32_t src = tmem_base + (wg == 0 ? COL_DV : COL_DK) + lane_off;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -929,17 +930,23 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, int64_t 
   if (lane == 0) delta[(static_cast<int64_t>(b) * H + h) * S + s] = acc;
 }
 
-__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n8) {
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float4 a = reinterpret_cast<const float4*>(src)[2 * i], b = reinterpret_cast<const float4*>(src)[2 * i + 1];
-    uint4 v;
-    __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-    vb[0] = __floats2bfloat162_rn(a.x, a.y);
-    vb[1] = __floats2bfloat162_rn(a.z, a.w);
-    vb[2] = __floats2bfloat162_rn(b.x, b.y);
-    vb[3] = __floats2bfloat162_rn(b.z, b.w);
-    reinterpret_cast<uint4*>(dst)[i] = v;
+// dst[row, 0:cols] (token stride dst_stride) = bf16(src[row, 0:cols]); cols a multiple of 8.
+__global__ void f32_to_bf16_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                        int64_t rows, int cols, int64_t dst_stride) {
+  const int vec_per_row = cols >> 3;
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    const float4* s4 = reinterpret_cast<const float4*>(src + row * cols);
+    uint4* d4 = reinterpret_cast<uint4*>(dst + row * dst_stride);
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < vec_per_row; c += gridDim.x * blockDim.x) {
+      const float4 a = s4[2 * c], b = s4[2 * c + 1];
+      uint4 v;
+      __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+      vb[0] = __floats2bfloat162_rn(a.x, a.y);
+      vb[1] = __floats2bfloat162_rn(a.z, a.w);
+      vb[2] = __floats2bfloat162_rn(b.x, b.y);
+      vb[3] = __floats2bfloat162_rn(b.z, b.w);
+      d4[c] = v;
+    }
   }
 }
 
@@ -1037,14 +1044,16 @@ extern "C" int hpb_flash_attn_fwd(const void* q, long long q_batch_stride, long 
 }
 
 // Backward.  dO [B, S, Hq, 128] (strided like q), O / lse from the forward.  Outputs: dQ
-// [B, S, Hq, 128] bf16, dK / dV [B, S, Hkv, 128] bf16, all contiguous.  Workspace: dq_acc fp32
+// [B, S, Hq, 128] bf16, dK / dV [B, S, Hkv, 128] bf16 with token strides dq_row_stride / dkv_row_stride
+// elements (so that they may be the three column ranges of one packed gradient).  Workspace: dq_acc fp32
 // [B, S, Hq, 128] and delta fp32 [B, Hq, S]; dq_acc is cleared here.
 extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long long q_row_stride, const void* k,
                                   long long k_batch_stride, long long k_row_stride, const void* v,
                                   long long v_batch_stride, long long v_row_stride, const void* O, const float* lse,
                                   const void* dO, long long do_batch_stride, long long do_row_stride, void* dQ,
-                                  void* dK, void* dV, float* dq_acc, float* delta, int B, int S, int Hq, int Hkv,
-                                  float softmax_scale, int causal, int* status, cudaStream_t stream) {
+                                  void* dK, void* dV, long long dq_row_stride, long long dkv_row_stride,
+                                  float* dq_acc, float* delta, int B, int S, int Hq, int Hkv, float softmax_scale,
+                                  int causal, int* status, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return 0;
   if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -2;
   if ((q_row_stride | k_row_stride | v_row_stride | do_row_stride | q_batch_stride | k_batch_stride |
@@ -1054,6 +1063,7 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
        reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dQ) | reinterpret_cast<uintptr_t>(dK) |
        reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(O) | reinterpret_cast<uintptr_t>(dq_acc)) & 15)
     return -2;
+  if ((dq_row_stride | dkv_row_stride) & 7) return -2;
   cudaFree(nullptr);
   CUtensorMap tq, tdo, tk, tv;
   int r = make_tmap_bsd(&tq, q, B, S, Hq * fa::HD, q_batch_stride, q_row_stride, fa::BQ);
@@ -1094,6 +1104,7 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
   p.dQ = dq_acc;
   p.dK = reinterpret_cast<__nv_bfloat16*>(dK);
   p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
+  p.dkv_row_stride = dkv_row_stride;
   p.status = status;
   dim3 grid(((S + fa::BN - 1) / fa::BN) * Hkv * B);
   CUtensorMap tdq;
@@ -1112,6 +1123,12 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
   fa::flash_bwd_kernel<<<grid, fa::BWD_THREADS, fa::BWD_SMEM, stream>>>(tq, tdo, tk, tv, tdq, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  fa::f32_to_bf16_kernel<<<1184, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dQ), nq / 8);
+  {
+    const int cols = Hq * fa::HD;
+    const int64_t rows = static_cast<int64_t>(B) * S;
+    dim3 cgrid((cols / 8 + 255) / 256, static_cast<unsigned>(rows < 4096 ? rows : 4096));
+    fa::f32_to_bf16_rows_kernel<<<cgrid, 256, 0, stream>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dQ), rows, cols,
+                                                          dq_row_stride);
+  }
   return static_cast<int>(cudaGetLastError());
 }
