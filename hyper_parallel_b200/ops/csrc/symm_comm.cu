@@ -48,15 +48,7 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 
 // ------------------------------------------------------------- all-gather ----
 // full[full_off + r*n + j] = peer_r.shard[shard_off + j]   for every segment, rank r, j < n
-//
-// Every thread keeps one 16-byte load per rank in flight (the own shard included), so that the
-// local copy (HBM) and the n-1 peer copies (NVLink) proceed at the same time instead of one
-// rank after the other; with few ranks a second vector per rank is added to cover the NVLink
-// latency.
-// (The bound of 768 caps the registers at 80 per thread: a 512-thread CTA then fits beside a
-// persistent GEMM CTA in the register file of an SM.)
-template <int N>  // N > 0: compile-time rank count (loads fully unrolled); N == 0: runtime `n`
-__global__ void __launch_bounds__(768)
+__global__ void __launch_bounds__(512)
 p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict__ segs,
                      int num_segs, __nv_bfloat16* __restrict__ full, int rank, int n, uint32_t epoch,
                      uint64_t limit_ns, int* status, unsigned int* done_counter) {
@@ -65,56 +57,29 @@ p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict
     if (blockIdx.x == 0) signal_peers(pads, rank, n, 0, epoch);   // my shard is final
     if (!wait_peers(pads, rank, n, 0, epoch, limit_ns, status)) return;
   }
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (int s = 0; s < num_segs; ++s) {
     const Segment sg = segs[s];
     const long long nv = sg.n >> 3;  // 16-byte vectors (n and offsets are multiples of 8)
-    if constexpr (N > 0) {
-      constexpr int U = N <= 2 ? 4 : (N <= 4 ? 2 : 1);   // vectors per rank in flight
-      const uint4* src[N];
-      uint4* dst[N];
-#pragma unroll
-      for (int rr = 0; rr < N; ++rr) {
-        const int r = (rank + rr) % N;
-        src[rr] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(shards.ptr[r]) + sg.shard_off);
-        dst[rr] = reinterpret_cast<uint4*>(full + sg.full_off + static_cast<long long>(r) * sg.n);
-      }
+    for (int rr = 0; rr < n; ++rr) {
+      const int r = (rank + rr) % n;  // start with my own shard, then spread over the peers
+      const uint4* src = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const __nv_bfloat16*>(shards.ptr[r]) + sg.shard_off);
+      uint4* dst = reinterpret_cast<uint4*>(full + sg.full_off + static_cast<long long>(r) * sg.n);
+      const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
       long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-      for (; i + (U - 1) * stride < nv; i += U * stride) {
-        uint4 v[U][N];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int rr = N - 1; rr >= 0; --rr) v[u][rr] = src[rr][i + u * stride];   // peers first, own shard last
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int rr = N - 1; rr >= 0; --rr) dst[rr][i + u * stride] = v[u][rr];
+      // four independent 16-byte loads in flight per thread: NVLink latency is ~2 us, so the
+      // bytes in flight, not the CTA count, set the achieved bandwidth
+      for (; i + 3 * stride < nv; i += 4 * stride) {
+        const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
+        dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
       }
-      for (; i < nv; i += stride) {
-#pragma unroll
-        for (int rr = 0; rr < N; ++rr) dst[rr][i] = src[rr][i];
-      }
-    } else {
-      for (int rr = 0; rr < n; ++rr) {
-        const int r = (rank + rr) % n;
-        const uint4* src = reinterpret_cast<const uint4*>(
-            reinterpret_cast<const __nv_bfloat16*>(shards.ptr[r]) + sg.shard_off);
-        uint4* dst = reinterpret_cast<uint4*>(full + sg.full_off + static_cast<long long>(r) * sg.n);
-        long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-        for (; i + 3 * stride < nv; i += 4 * stride) {
-          const uint4 v0 = src[i], v1 = src[i + stride], v2 = src[i + 2 * stride], v3 = src[i + 3 * stride];
-          dst[i] = v0; dst[i + stride] = v1; dst[i + 2 * stride] = v2; dst[i + 3 * stride] = v3;
-        }
-        for (; i < nv; i += stride) dst[i] = src[i];
-      }
-    }
-    // tail elements
-    if (blockIdx.x == 0)
-      for (int r = 0; r < n; ++r)
+      for (; i < nv; i += stride) dst[i] = src[i];
+      // tail elements
+      if (blockIdx.x == 0)
         for (long long i = (nv << 3) + threadIdx.x; i < sg.n; i += blockDim.x)
           (full + sg.full_off + static_cast<long long>(r) * sg.n)[i] =
               (reinterpret_cast<const __nv_bfloat16*>(shards.ptr[r]) + sg.shard_off)[i];
+    }
   }
   if (sync) {
     // "done reading your shard": the last CTA to finish tells the peers and waits for theirs,
@@ -139,11 +104,10 @@ struct AdamArgs {
   float lr, b1, b2, eps, wd, bc1, bc2, grad_scale;
 };
 
-// Launched as twice the requested number of CTAs of 256 threads (two resident per SM: twice the
-// independent load batches in flight).  The bound of 768 caps the kernel at 80 registers per
-// thread, so that two CTAs (40 K registers) fit beside a persistent GEMM CTA (192 threads x 96
-// registers) in the 64 K register file of an SM -- otherwise the 8-peer instance would need the
-// whole file and could only run in the gaps between GEMM launches.
+// Launched with 512 threads; the bound of 768 caps the kernel at 80 registers per thread, so
+// that a CTA (40 K registers) fits beside a persistent GEMM CTA (192 threads x 96 registers)
+// in the 64 K register file of an SM -- otherwise the 8-peer instance would need the whole
+// file and could only run in the gaps between GEMM launches.
 template <int N>  // N > 0: compile-time peer count (loads fully unrolled); N == 0: runtime `n`
 __global__ void __launch_bounds__(768)
 fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict__ segs,
@@ -309,20 +273,11 @@ extern "C" int hpb_p2p_allgather(void* const* shard_ptrs, void* const* pads, con
                                  unsigned long long limit_ns, int* status, unsigned* done_counter,
                                  int num_ctas, cudaStream_t s) {
   if (n > kMaxPeers) return -2;
-#define HPB_AG(NN)                                                                                \
-  prefer_shared(p2p_allgather_kernel<NN>);                                                        \
-  p2p_allgather_kernel<NN><<<num_ctas, 512, 0, s>>>(make_table(shard_ptrs, n), make_table(pads, n), \
-                                                    reinterpret_cast<const Segment*>(segs), num_segs, \
-                                                    reinterpret_cast<__nv_bfloat16*>(full), rank, n, \
-                                                    epoch, limit_ns, status, done_counter)
-  switch (n) {
-    case 1: HPB_AG(1); break;
-    case 2: HPB_AG(2); break;
-    case 4: HPB_AG(4); break;
-    case 8: HPB_AG(8); break;
-    default: HPB_AG(0); break;
-  }
-#undef HPB_AG
+  prefer_shared(p2p_allgather_kernel);
+  p2p_allgather_kernel<<<num_ctas, 512, 0, s>>>(make_table(shard_ptrs, n), make_table(pads, n),
+                                                reinterpret_cast<const Segment*>(segs), num_segs,
+                                                reinterpret_cast<__nv_bfloat16*>(full), rank, n,
+                                                epoch, limit_ns, status, done_counter);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -336,7 +291,7 @@ extern "C" int hpb_fused_rs_adamw(void* const* grad_ptrs, void* const* pads, con
   AdamArgs a{lr, b1, b2, eps, wd, 1.f - powf(b1, (float)step), 1.f - powf(b2, (float)step), grad_scale};
 #define HPB_RS(NN)                                                                              \
   prefer_shared(fused_rs_adamw_kernel<NN>);                                                     \
-  fused_rs_adamw_kernel<NN><<<2 * num_ctas, 256, 0, s>>>(                                           \
+  fused_rs_adamw_kernel<NN><<<num_ctas, 512, 0, s>>>(                                           \
       make_table(grad_ptrs, n), make_table(pads, n), reinterpret_cast<const Segment*>(segs),    \
       num_segs, master, m, v, reinterpret_cast<__nv_bfloat16*>(param_shard), a, rank, n, epoch, \
       limit_ns, status, done_counter)
