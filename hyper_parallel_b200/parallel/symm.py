@@ -1,7 +1,8 @@
 """Symmetric memory over NVLink / NVSwitch: one buffer per rank, mapped into every peer.
 
-The reference has no counterpart (its communication is ``torch.distributed`` only, SURVEY
-§2.11); this is the layer the fused compute+collective kernels are built on.
+The reference has no counterpart (its communication is ``torch.distributed`` only,
+hyper_parallel/platform/torch/platform.py:176-424); this is the layer the fused compute+collective
+kernels are built on.
 
 ``SymmetricMemory(group, nbytes)`` allocates ``nbytes`` on every rank of ``group`` plus a
 signal pad, exchanges CUDA IPC handles through the process group and maps all peers.  It
