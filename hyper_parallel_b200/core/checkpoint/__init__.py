@@ -1,4 +1,4 @@
-from .api import load, save  # noqa: F401
+from .api import AsyncSaveHandle, async_save, load, save  # noqa: F401
 from .filesystem_storage import FileSystemReader, FileSystemWriter  # noqa: F401
 from .layout import combine_layout, get_current_layout, get_global_layout, load_layout, save_layout  # noqa: F401
 from .loader import load_checkpoint  # noqa: F401

@@ -83,3 +83,76 @@ def load(state_dict: Dict[str, Any], *, checkpoint_id=None, storage_reader: Opti
     if dist_on and use_collectives:
         import torch.distributed as dist
         dist.barrier()
+
+
+class AsyncSaveHandle:
+    """Result of :func:`async_save`; ``wait()`` returns the metadata (and re-raises a write error)."""
+
+    def __init__(self, thread, box):
+        self._thread, self._box = thread, box
+
+    def done(self) -> bool:
+        return not self._thread.is_alive()
+
+    def wait(self) -> Metadata:
+        self._thread.join()
+        if "error" in self._box:
+            raise self._box["error"]
+        return self._box["metadata"]
+
+
+def async_save(state_dict: Dict[str, Any], *, checkpoint_id=None, storage_writer: Optional[StorageWriter] = None,
+               planner: Optional[SavePlanner] = None) -> AsyncSaveHandle:
+    """Checkpoint without stalling the training loop (the reference only saves synchronously).
+
+    Every tensor is first copied to host memory (pinned for CUDA tensors, on a side stream that the
+    call waits for, so the caller may overwrite the parameters as soon as this returns); the files
+    are then written by a background thread.  The thread must not issue collectives next to the
+    training loop's, so each rank plans and writes on its own (``.rank{r}_metadata``, the layout of
+    ``save(use_collectives=False)``), which ``load`` reads on any number of ranks.
+    """
+    import threading
+
+    import torch
+
+    from ..dtensor import DTensor
+
+    def stage(t):
+        local = t.to_local() if isinstance(t, DTensor) else t
+        if local.is_cuda:
+            host = torch.empty(local.shape, dtype=local.dtype, device="cpu", pin_memory=True)
+            host.copy_(local.detach(), non_blocking=True)
+        else:
+            host = local.detach().clone()
+        return DTensor._wrap(host, t.layout) if isinstance(t, DTensor) else host
+
+    side = None
+    if torch.cuda.is_available() and any(
+            (v.to_local() if isinstance(v, DTensor) else v).is_cuda for v in state_dict.values()
+            if isinstance(v, torch.Tensor)):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+    staged: Dict[str, Any] = {}
+    ctx = torch.cuda.stream(side) if side is not None else None
+    if ctx is not None:
+        ctx.__enter__()
+    try:
+        for k, v in state_dict.items():
+            staged[k] = stage(v) if isinstance(v, torch.Tensor) else v
+    finally:
+        if ctx is not None:
+            ctx.__exit__(None, None, None)
+    if side is not None:
+        side.synchronize()
+    box: Dict[str, Any] = {}
+
+    def work():
+        try:
+            box["metadata"] = save(staged, checkpoint_id=checkpoint_id, storage_writer=storage_writer,
+                                   planner=planner, use_collectives=False)
+        except BaseException as e:  # noqa: BLE001 - re-raised by wait()
+            box["error"] = e
+
+    th = threading.Thread(target=work, name="hpb-async-save", daemon=True)
+    th.start()
+    return AsyncSaveHandle(th, box)

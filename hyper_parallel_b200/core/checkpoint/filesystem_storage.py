@@ -116,7 +116,43 @@ class FileSystemReader(StorageReader):
                 if not isinstance(md, Metadata):
                     raise ValueError(f"{p} does not contain checkpoint metadata")
                 return md
+        merged = self._merge_rank_metadata()
+        if merged is not None:
+            return merged
         raise FileNotFoundError(f"no metadata file in {self.path} (looked for {[os.path.basename(c) for c in cand]})")
+
+    def _merge_rank_metadata(self) -> Optional[Metadata]:
+        """Union of all ``.rank{r}_metadata`` files: a checkpoint written rank by rank (without
+        collectives) then loads on any number of ranks and layout, like a coordinated one."""
+        import dataclasses
+        import re
+        files = sorted(f for f in os.listdir(self.path) if re.fullmatch(r"\.rank\d+_metadata", f))
+        if not files:
+            return None
+        state: Dict[str, object] = {}
+        storage: Dict[MetadataIndex, object] = {}
+        for fn in files:
+            with open(os.path.join(self.path, fn), "rb") as f:
+                md = ReferenceCompatUnpickler(f).load()
+            for fqn, entry in md.state_dict_metadata.items():
+                have = state.get(fqn)
+                if have is None or not hasattr(entry, "chunks"):
+                    state[fqn] = entry
+                else:
+                    chunks = list(have.chunks) + [c for c in entry.chunks if c not in have.chunks]
+                    state[fqn] = dataclasses.replace(have, chunks=chunks)
+            for idx, info in (md.storage_data or {}).items():
+                storage.setdefault(idx, info)
+        # chunk indices are positions in the merged chunk lists
+        fixed: Dict[MetadataIndex, object] = {}
+        for idx, info in storage.items():
+            entry = state.get(idx.fqn)
+            if hasattr(entry, "chunks") and idx.offset is not None:
+                pos = next((i for i, c in enumerate(entry.chunks) if tuple(c.offsets) == tuple(idx.offset)), idx.index)
+                fixed[MetadataIndex(idx.fqn, idx.offset, pos)] = info
+            else:
+                fixed[idx] = info
+        return Metadata(state_dict_metadata=state, storage_data=fixed)
 
     def configure_reader(self, metadata: Metadata, is_coordinator: bool, rank: int = 0) -> None:
         self.metadata = metadata

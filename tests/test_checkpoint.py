@@ -127,3 +127,29 @@ def test_layout_json_and_single_file_helpers(tmp_path):
     assert torch.equal(ckpt.load_checkpoint(str(tmp_path / "one.pt"))["x"], torch.ones(2))
     with pytest.raises(ValueError):
         ckpt.save_checkpoint({}, str(tmp_path / "bad.txt"))
+
+
+def _async_save_worker(rank, world, ckpt):
+    from hyper_parallel_b200 import Layout, distribute_tensor
+    from hyper_parallel_b200.core import checkpoint as dcp
+    lay = Layout((world,), ("dp",))
+    full = torch.arange(48, dtype=torch.float32).reshape(8, 6)
+    sd = {"w": distribute_tensor(full.clone(), lay("dp", "None")), "b": torch.full((3,), 7.0), "step": 5}
+    handle = dcp.async_save(sd, checkpoint_id=ckpt)
+    sd["w"].to_local().zero_()                       # the caller may overwrite right away
+    md = handle.wait()
+    assert handle.done() and "w" in md.state_dict_metadata
+    import torch.distributed as dist
+    dist.barrier()
+    # same layout
+    out = {"w": distribute_tensor(torch.zeros(8, 6), lay("dp", "None")), "b": torch.zeros(3), "step": 0}
+    dcp.load(out, checkpoint_id=ckpt)
+    assert torch.equal(out["w"].full_tensor(), full) and torch.equal(out["b"], torch.full((3,), 7.0)) and out["step"] == 5
+    # another layout: the rank-local metadata files are merged
+    out2 = {"w": distribute_tensor(torch.zeros(8, 6), lay("None", "dp"))}
+    dcp.load(out2, checkpoint_id=ckpt)
+    assert torch.equal(out2["w"].full_tensor(), full)
+
+
+def test_async_save_then_load_with_another_layout(tmp_path):
+    run_distributed(_async_save_worker, 2, str(tmp_path / "async"))
