@@ -153,3 +153,60 @@ def _async_save_worker(rank, world, ckpt):
 
 def test_async_save_then_load_with_another_layout(tmp_path):
     run_distributed(_async_save_worker, 2, str(tmp_path / "async"))
+
+
+class _Mlp(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = torch.nn.Linear(8, 16, bias=False)
+        self.b = torch.nn.Linear(16, 8, bias=False)
+
+    def forward(self, x):
+        return self.b(torch.tanh(self.a(x)))
+
+
+def _train_steps(net, opt, n, start=0):
+    import hyper_parallel_b200 as hp
+    g = torch.Generator().manual_seed(100)
+    xs = torch.randn(8, 4, 8, generator=g)
+    for i in range(start, start + n):
+        net.zero_grads()
+        net(xs[i]).pow(2).mean().backward()
+        hp.hsdp_sync_stream()
+        opt.step()
+
+
+def _hsdp_resume_worker(rank, world, ckpt, phase):
+    import hyper_parallel_b200 as hp
+    from hyper_parallel_b200.core import checkpoint as dcp
+    from hyper_parallel_b200.core.hsdp import get_sharded_state_dict, restore_optimizer_step
+    from hyper_parallel_b200.optim import FusedAdamW
+    torch.manual_seed(9)
+    net = _Mlp()
+    hp.hsdp(net, shard_size=world, threshold=0, optimizer_level="level3", grad_scale=1.0 / world)
+    opt = FusedAdamW(net.parameters(), lr=1e-2, master_weights=False)
+    if phase == "save":
+        _train_steps(net, opt, 3)
+        sd = get_sharded_state_dict(net, opt)
+        dcp.save(sd, checkpoint_id=ckpt)
+        _train_steps(net, opt, 2, start=3)            # the uninterrupted run
+        full = {k: (v.full_tensor() if isinstance(v, hp.DTensor) else v) for k, v in get_sharded_state_dict(net).items()}
+        if rank == 0:
+            torch.save(full, ckpt + "_final.pt")
+    else:
+        opt.init_state()
+        sd = get_sharded_state_dict(net, opt)
+        dcp.load(sd, checkpoint_id=ckpt)
+        restore_optimizer_step(opt, sd)
+        assert opt._step_count == 3
+        _train_steps(net, opt, 2, start=3)
+        want = torch.load(ckpt + "_final.pt")
+        for k, v in get_sharded_state_dict(net).items():
+            got = v.full_tensor() if isinstance(v, hp.DTensor) else v
+            assert torch.allclose(got, want[k], atol=1e-6), k
+
+
+def test_hsdp_model_and_optimizer_resume_on_another_rank_count(tmp_path):
+    ckpt = str(tmp_path / "hsdp_ckpt")
+    run_distributed(_hsdp_resume_worker, 4, ckpt, "save")
+    run_distributed(_hsdp_resume_worker, 2, ckpt, "resume")     # resumes sharded 2 ways instead of 4
