@@ -81,6 +81,16 @@ class HSDPModule:
                 raise ValueError(f"{type(m).__name__} is not a fully_shard module")
         self._fsdp_state.bwd_prefetch = list(modules)
 
+    def zero_grads(self) -> None:
+        """Drop the accumulated (sharded) gradients of every wrapped module below this one.  The
+        reference refuses this call on torch and points at ``optimizer.zero_grad()``
+        (hyper_parallel/core/fully_shard/api.py:91-99); here it does the same job."""
+        for p in self.parameters():
+            p.grad = None
+            fp = getattr(p, "_fsdp_param", None)
+            if fp is not None and getattr(fp, "sharded_param", None) is not None:
+                fp.sharded_param.grad = None
+
     def set_reduce_op_type(self, reduce_op_type: str) -> None:
         if reduce_op_type not in ("avg", "sum"):
             raise ValueError(f"reduce_op_type must be 'avg' or 'sum', got {reduce_op_type!r}")
@@ -175,18 +185,44 @@ def fully_shard(module: nn.Module, *, mesh: Optional[DeviceMesh] = None,
 
 
 def get_model_state_dict(model: nn.Module, *, options: Optional[StateDictOptions] = None) -> Dict[str, Any]:
-    """Sharded (DTensor) or full state dict of a ``fully_shard`` model, optionally moved to CPU."""
+    """State dict of a ``fully_shard`` model (hyper_parallel/core/fully_shard/api.py:443-490).
+
+    ==================  =============  ==========================================
+    ``full_state_dict``  ``cpu_offload``  result
+    ==================  =============  ==========================================
+    False               False          DTensors (this rank's shards, no copy)
+    False               True           DTensors whose local shard is on the host
+    True                False          full tensors on every rank
+    True                True           full tensors on the host, rank 0 only
+    ==================  =============  ==========================================
+
+    ``ignore_frozen_params`` drops parameters with ``requires_grad=False``.  Every rank must call
+    this function when ``full_state_dict`` is set: the gathers are collective.
+    """
     options = options or StateDictOptions()
+    full = bool(getattr(options, "full_state_dict", False))
+    to_cpu = bool(getattr(options, "cpu_offload", False))
+    if getattr(options, "broadcast_from_rank0", False) and not full:
+        raise ValueError("full_state_dict must be True when broadcast_from_rank0 is True.")
+    skip_frozen = bool(getattr(options, "ignore_frozen_params", False))
+    keep = not (full and to_cpu) or cc.get_rank() == 0
     out: Dict[str, Any] = {}
-    for name, p in list(model.named_parameters()) + list(model.named_buffers()):
+    entries = [(n, p, True) for n, p in model.named_parameters()] + \
+              [(n, b, False) for n, b in model.named_buffers()]
+    persistent = set(model.state_dict().keys())
+    for name, p, is_param in entries:
+        if name not in persistent or (is_param and skip_frozen and not p.requires_grad):
+            continue
         fp = getattr(p, "_fsdp_param", None)
         if fp is None:
             v = p.detach()
-        elif options.full_state_dict:
+        elif full:
             v = fp.full_tensor().detach()
         else:
             v = fp.sharded_param.detach()
-        if options.cpu_offload:
+        if not keep:
+            continue
+        if to_cpu:
             v = v.cpu() if not isinstance(v, DTensor) else DTensor._wrap(v.to_local().cpu(), v.layout)
         out[name] = v
     return out

@@ -73,5 +73,12 @@ class HSDPMeshInfo(DataParallelMeshInfo):
 
 @dataclass
 class StateDictOptions:
+    """Same fields (and defaults) as ``torch.distributed.checkpoint.state_dict.StateDictOptions``, which
+    the reference takes directly (hyper_parallel/core/fully_shard/api.py:443-490); an instance of the
+    torch class is accepted wherever this one is."""
     full_state_dict: bool = False
     cpu_offload: bool = False
+    ignore_frozen_params: bool = False
+    keep_submodule_prefixes: bool = True
+    strict: bool = True
+    broadcast_from_rank0: bool = False

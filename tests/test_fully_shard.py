@@ -75,7 +75,7 @@ def _worker(rank, world, mode):
     tol = 5e-2 if mode == "mp" else 1e-5
     for a, b in zip(losses, ref_losses):
         assert abs(a - b) < tol * max(1.0, abs(b)), (mode, losses, ref_losses)
-    full = get_model_state_dict(net, options=StateDictOptions(full_state_dict=True, cpu_offload=True))
+    full = get_model_state_dict(net, options=StateDictOptions(full_state_dict=True))
     for k, v in ref_sd.items():
         assert torch.allclose(full[k].float(), v, atol=tol), (mode, k)
     sharded = get_model_state_dict(net)
