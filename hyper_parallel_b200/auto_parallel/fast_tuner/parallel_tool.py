@@ -19,7 +19,7 @@ from .config import ModelSpec, Strategy, TunerConfig, load_model_spec
 from .cost_model import Hardware, estimate_step_time
 from .memory_model import filter_oom, write_candidate_csv
 from .pipeline_balance import LayerProfile, balance_pipeline
-from .profiling import (ProfileInfo, launch_profile, parse_layer_records, select_profile_candidates,
+from .profiling import (launch_profile, parse_layer_records, select_profile_candidates,
                         write_profile_config)
 from .space import (Config, build_initial_spaces, dp_of, ep_of, expert_filter_configs, mbs_of, op_of, pp_of,
                     sp_of, tp_of, vp_of)

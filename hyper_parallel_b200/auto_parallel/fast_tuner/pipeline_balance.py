@@ -13,7 +13,7 @@ that makes each stage fit its memory limit at the least extra time.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 from .pp_simulator import compute_order, simulate
 

@@ -15,9 +15,9 @@ import sys
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
-from .config import ModelSpec, TunerConfig
+from .config import ModelSpec
 from .pipeline_balance import LayerProfile
-from .space import Config, cp_of, dp_of, ep_of, mbs_of, op_of, pp_of, sp_of, tp_of, vp_of
+from .space import Config, cp_of, ep_of, tp_of
 
 
 @dataclass

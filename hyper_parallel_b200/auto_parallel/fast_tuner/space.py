@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import itertools
 import math
-from typing import Callable, List, Sequence
+from typing import Callable, List
 
 from .config import ModelSpec, Strategy
 

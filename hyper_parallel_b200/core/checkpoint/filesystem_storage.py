@@ -21,7 +21,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .metadata import Metadata, MetadataIndex
-from .planner import LoadItemType, LoadPlan, LoadPlanner, SavePlan, SavePlanner, WriteItemType
+from .planner import LoadPlan, LoadPlanner, SavePlan, SavePlanner, WriteItemType
 from .storage import StorageInfo, StorageReader, StorageWriter, WriteResult, _metadata_file_name
 from ._compat import ReferenceCompatUnpickler, reference_module_names
 

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 from abc import ABC, abstractmethod
 from dataclasses import dataclass
-from typing import Any, List, Optional
+from typing import List, Optional
 
 from .metadata import Metadata, MetadataIndex
 from .planner import LoadPlan, LoadPlanner, SavePlan, SavePlanner

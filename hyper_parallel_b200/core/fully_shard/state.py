@@ -9,7 +9,7 @@ overlaps the backward of layer *i-1*) or by the end-of-backward callback.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List
 
 import torch
 from torch import nn

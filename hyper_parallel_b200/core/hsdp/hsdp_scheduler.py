@@ -16,7 +16,7 @@ and hyper_parallel/platform/torch/hsdp/scheduler.py:51-106 of the reference:
 from __future__ import annotations
 
 import enum
-from typing import List, Optional
+from typing import List
 
 import torch
 from torch.autograd import Variable

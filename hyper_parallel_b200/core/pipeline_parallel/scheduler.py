@@ -22,13 +22,12 @@ from __future__ import annotations
 
 import logging
 from enum import Enum, auto
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..dtensor import DTensor
 from .stage import PipelineStage
-from .utils import BatchDimSpec, MicroBatch
+from .utils import MicroBatch
 
 logger = logging.getLogger(__name__)
 

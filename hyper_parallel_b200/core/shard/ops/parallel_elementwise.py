@@ -10,10 +10,8 @@ non-partial operand by the number of partial ranks so that the later sum is righ
 """
 from __future__ import annotations
 
-import numbers
 from typing import List, Optional
 
-import torch
 
 from ._common import make, split_shapes
 from .parallel_ops import DistributedOp

@@ -20,7 +20,6 @@ from __future__ import annotations
 
 from typing import Dict, List, Tuple
 
-import torch
 
 from ..collectives import cc
 from .layout import Layout

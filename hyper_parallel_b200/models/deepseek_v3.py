@@ -18,7 +18,6 @@ on CPU the same functions run their PyTorch formulation, which is the oracle.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Optional
 

@@ -10,7 +10,6 @@ is what the CPU tests (and the oracle) run.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Optional
 

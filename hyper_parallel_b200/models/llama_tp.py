@@ -18,7 +18,6 @@ import torch.nn.functional as F
 from torch import nn
 
 from .. import ops
-from ..core.device_mesh import DeviceMesh
 from ..core.dtensor import DTensor
 from ..core.layout import Layout
 from ..ops import attention as attn_ops

@@ -11,7 +11,7 @@ all-to-all of ``redistribute`` (hyper_parallel/core/tensor_redistribution.py:84-
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,7 @@ advances the step counter.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, Optional
+from typing import Dict, Iterable
 
 import torch
 

@@ -23,7 +23,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 
