@@ -259,10 +259,18 @@ def run_pp(args, rank, world, dev):
     lt = loss.clone()
     dist.all_reduce(lt, op=dist.ReduceOp.MAX)
     tokens = B * args.micro * S
+    stats = torch.cuda.memory_stats(dev)
+    mem = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2**30, torch.cuda.max_memory_reserved(dev) / 2**30,
+                        float(stats.get("num_alloc_retries", 0)), float(stats.get("num_device_alloc", 0))],
+                       device=dev, dtype=torch.float64)
+    dist.all_reduce(mem, op=dist.ReduceOp.MAX)
     return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} x tp{tp} {args.schedule}"
                        + (f" x{chunks} chunks" if chunks > 1 else ""), "micro_batches": args.micro,
                        "global_batch": B * args.micro, "seq_len": S},
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(lt.detach()), "clocks": clocks,
+            "memory_max_over_ranks": {"peak_allocated_gib": round(float(mem[0]), 2),
+                                      "peak_reserved_gib": round(float(mem[1]), 2),
+                                      "alloc_retries": int(mem[2]), "device_allocs": int(mem[3])},
             "mfu_flops_per_token": cfg.flops_per_token(S)}
 
 
