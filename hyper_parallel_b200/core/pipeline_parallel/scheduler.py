@@ -254,30 +254,9 @@ class PipelineScheduleRuntime:
         for st in self.stages:
             st.fwd_cache.clear()
             st.input_grads.clear()
-        posted_early = set()
-        for pos, step in enumerate(prog):
+        for step in prog:
             stage = self.stage_by_index[step.stage_index]
             m = step.micro_index
-            if step.type in (T.FWD, T.BWD) and self.overlap_p2p:
-                # Post the receives that follow this compute step before its kernels are enqueued: the
-                # communicator's stream waits for whatever the compute stream holds when the receive
-                # is posted, so a receive posted afterwards cannot start until this step has finished,
-                # and the peer's matching send spins on its SMs for that long.
-                for nxt in range(pos + 1, len(prog)):
-                    ahead = prog[nxt]
-                    if ahead.type in (T.FWD, T.BWD):
-                        break
-                    if ahead.type not in (T.FWD_RECV, T.BWD_RECV):
-                        continue
-                    peer_stage = self.stage_by_index[ahead.stage_index]
-                    fwd = ahead.type == T.FWD_RECV
-                    if not peer_stage.can_post_recv_early(fwd):
-                        break
-                    pend = peer_stage.post_forward_recv() if fwd else peer_stage.post_backward_recv()
-                    (recv_f if fwd else recv_b)[(ahead.stage_index, ahead.micro_index)] = pend
-                    posted_early.add(nxt)
-            if pos in posted_early:
-                continue
             if step.type == T.FWD_RECV:
                 p = stage.post_forward_recv()
                 if not self.overlap_p2p:

@@ -180,17 +180,6 @@ class PipelineStage:
         works = [dist.irecv(b, src=src_rank, group=grp) for b in bufs]
         return _Pending(works, bufs, metas)
 
-    def can_post_recv_early(self, forward: bool) -> bool:
-        """Whether the next receive of that direction may be posted ahead of its place in the program:
-        the shapes are known (no blocking metadata exchange, which could wait on a peer that waits
-        on us) and the receive has a communicator of its own (posting it earlier cannot reorder it
-        against a send)."""
-        if self.dyn_shape:
-            return False
-        src = self.src_stage if forward else self.dst_stage
-        key = ("f" if forward else "b", src)
-        return key in self.meta_cache and (self.peer_rank(src), self.rank, key[0]) in self._p2p_groups
-
     def wait_sends(self) -> None:
         for w, _keep in self._pending_sends:
             w.wait()
