@@ -34,7 +34,7 @@ class AsyncSaveOnCpu(torch.autograd.graph.saved_tensors_hooks):
 
         def unpack(obj):
             if isinstance(obj, Storage):
-                return obj.swap_tensor.get()
+                return obj.swap_tensor.take()
             return obj
 
         super().__init__(pack, unpack)

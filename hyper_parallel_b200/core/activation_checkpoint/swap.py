@@ -110,19 +110,32 @@ class SwapTensor:
         self._device_tensor = dev
         self.state = SwapState.H2D
 
-    def wait_load(self) -> torch.Tensor:
+    def wait_load(self, keep_host: bool = False) -> torch.Tensor:
         if self.state in (SwapState.HOST, SwapState.D2H):
             self.launch_load()
         if self.state == SwapState.H2D:
             if self._event is not None:
-                torch.cuda.current_stream(self.device).wait_event(self._event)
+                cur = torch.cuda.current_stream(self.device)
+                cur.wait_event(self._event)
+                self._device_tensor.record_stream(cur)      # allocated on the copy stream, read on this one
                 self._event = None
-            self._host_tensor = None
+            if not keep_host:
+                self._host_tensor = None
             self.state = SwapState.DEVICE
         return self._device_tensor
 
     def get(self) -> torch.Tensor:
         return self.wait_load()
+
+    def take(self) -> torch.Tensor:
+        """The device tensor for one use by autograd.  When a host copy exists this object lets go of
+        the device copy afterwards, so the memory returns to the allocator as soon as the backward
+        node that asked for it is done; a later request loads from the host copy again."""
+        t = self.wait_load(keep_host=True)
+        if self._host_tensor is not None and self.is_cuda:
+            self._device_tensor = None
+            self.state = SwapState.HOST
+        return t
 
 
 class SwapGroup:
@@ -149,7 +162,7 @@ class SwapGroup:
 
     def wait_load(self) -> None:
         for t in self.tensors:
-            t.wait_load()
+            t.wait_load(keep_host=True)
 
     def clear(self) -> None:
         self.tensors = []
