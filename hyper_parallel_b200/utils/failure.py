@@ -33,11 +33,18 @@ class Heartbeat:
         self.world = dist.get_world_size() if world_size is None else world_size
         self.prefix = prefix
         self.count = 0
+        self.store_lost = False
         self._seen: Dict[int, tuple] = {}
 
     def beat(self) -> None:
+        """Publish this rank's counter.  If the store cannot be reached (the rank that hosts it has
+        gone) the error is kept in ``store_lost`` instead of being raised: ``dead_ranks`` then sees no
+        counter move and reports the others, the store's host among them, after its timeout."""
         self.count += 1
-        self.store.set(f"{self.prefix}/{self.rank}", str(self.count))
+        try:
+            self.store.set(f"{self.prefix}/{self.rank}", str(self.count))
+        except Exception:  # noqa: BLE001 - DistNetworkError / RuntimeError, depending on the store
+            self.store_lost = True
 
     def _read(self, r: int) -> int:
         try:

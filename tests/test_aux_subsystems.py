@@ -55,6 +55,7 @@ def _hb_worker(rank, world, port, q):
             dist.all_reduce(t)                 # the job makes progress while everybody is alive
         time.sleep(0.1)
     q.put((f"dead{rank}", dead))
+    time.sleep(1.5)                            # rank 0 hosts the store: let the others finish reading it
     os._exit(0)                                # no collective teardown with a missing rank
 
 
