@@ -113,34 +113,80 @@ def main():
                     "peaks": src})
     native.check_status(dev)
 
-    # ---- HSDP: P2P all-gather and fused reduce-scatter + AdamW (one Llama-3-8B layer: 218 M params) ----
+    # ---- HSDP: weight all-gather fused into the consumer GEMM, P2P all-gather, fused reduce-scatter + AdamW
+    # (one Llama-3-8B layer: 218 M params) ----
+    import ctypes
     from hyper_parallel_b200.parallel import fused_hsdp as fh
-    from hyper_parallel_b200.parallel.symm import DEFAULT_WAIT_NS, SymmetricMemory
+    from hyper_parallel_b200.parallel.symm import DEFAULT_WAIT_NS, SLOT_SHARD_VERSION, SymmetricMemory
     lib = fh._bind(native.lib())
+    stream = native.stream(dev)
+    status = native.status_word(dev)
+    T = 8192
+    for name, (rows, cols, w_mn) in {"gate_up fwd": (28672, 4096, False), "qkv fwd": (6144, 4096, False),
+                                      "down fwd": (4096, 14336, False), "gate_up dgrad": (28672, 4096, True),
+                                      "down dgrad": (4096, 14336, True)}.items():
+        shard_rows = rows // n
+        sm = SymmetricMemory(group, shard_rows * cols * 2, dev)
+        w_shard = sm.tensor(torch.bfloat16, shard_rows * cols, 0).view(shard_rows, cols)
+        w_shard.normal_(0, 0.02)
+        staging = torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
+        cnt = torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=dev)
+        K, N = (rows, cols) if w_mn else (cols, rows)
+        a = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
+        y = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+        seq = [0]
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def fused():
+            seq[0] += 1
+            native.check(lib.hpb_gemm2_agw(a.data_ptr(), a.stride(0), sm.ptrs, staging.data_ptr(), int(w_mn), rows,
+                                           cols, y.data_ptr(), y.stride(0), T, n, rank, cnt.data_ptr(),
+                                           cnt.data_ptr() + 4 * (cnt.numel() - 1), seq[0], sm.pad_ptrs[rank],
+                                           SLOT_SHARD_VERSION, 0, DEFAULT_WAIT_NS, status.data_ptr(),
+                                           native.sm_count(dev), stream), "hpb_gemm2_agw")
+
+        def unfused():
+            dist.all_gather_into_tensor(staging.view(-1), w_shard.view(-1))
+            Fn.gemm(a, staging, b_mn=w_mn, out=y)
+
+        t_f = timed(fused)
+        t_u = timed(unfused)
+        t_g = timed(lambda: Fn.gemm(a, staging, b_mn=w_mn, out=y))
+        flops = 2.0 * T * N * K
+        roof = max(flops / (peak_tf * 1e12), (n - 1) * shard_rows * cols * 2 / (LINK_GBS * 1e9)) * 1e3
+        out.append({"path": f"hsdp_allgather_gemm[{name}]", "n_gpus": n, "M": T, "N": N, "K": K, "fused_ms": t_f,
+                    "nccl_plus_gemm_ms": t_u, "gemm_alone_ms": t_g, "roofline_ms": roof,
+                    "fraction_of_roofline": roof / t_f, "peaks": src})
+        native.check_status(dev)
+        del staging, a, y
+        sm.close()
+
     numel = 218_112_000 // (8 * n) * (8 * n)
     shard = numel // n
-    symm = SymmetricMemory(group, shard * 2 + 256 + numel * 2, dev)
+    symm = SymmetricMemory(group, shard * 2 + 256 + numel * 2, dev, multicast=True)
     goff = (shard * 2 + 255) // 256 * 256
     full = torch.empty(numel, dtype=torch.bfloat16, device=dev)
-    segs = torch.tensor([[0, 0, shard]], dtype=torch.int64, device=dev)
-    status = native.status_word(dev)
+    segs = torch.tensor([[0, 0, shard, 0]], dtype=torch.int64, device=dev)
     sptr, gptr = symm.ptr_table(0), symm.ptr_table(goff)
     symm.tensor(torch.bfloat16, numel, goff).normal_()
     master = torch.zeros(shard, dtype=torch.float32, device=dev)
     m1, m2 = torch.zeros_like(master), torch.zeros_like(master)
-    stream = native.stream(dev)
+    hyper = (ctypes.c_float * 5)(1e-4, 0.9, 0.95, 1e-8, 0.1)
+    ver = [0]
 
     def ag():
         native.check(lib.hpb_p2p_allgather(sptr, symm.pad_ptrs, segs.data_ptr(), 1, full.data_ptr(), rank, n,
                                            symm.next_epoch(), DEFAULT_WAIT_NS, status.data_ptr(),
                                            symm.done_counter.data_ptr(), fh._NUM_COMM_CTAS, stream), "ag")
 
-    def rs():
-        native.check(lib.hpb_fused_rs_adamw(gptr, symm.pad_ptrs, segs.data_ptr(), 1, master.data_ptr(),
-                                            m1.data_ptr(), m2.data_ptr(), symm.tensor(torch.bfloat16, shard, 0).data_ptr(),
-                                            1e-4, 0.9, 0.95, 1e-8, 0.1, 1, 1.0, rank, n, symm.next_epoch(),
-                                            DEFAULT_WAIT_NS, status.data_ptr(), symm.done_counter.data_ptr() + 8,
-                                            fh._NUM_RS_CTAS, stream), "rs")
+    def rs(mc):
+        ver[0] += 1
+        native.check(lib.hpb_fused_rs_adamw(gptr, mc, symm.pad_ptrs, segs.data_ptr(), 1, master.data_ptr(),
+                                            m1.data_ptr(), m2.data_ptr(),
+                                            symm.tensor(torch.bfloat16, shard, 0).data_ptr(), hyper, 1, 1, 1.0, rank,
+                                            n, symm.next_epoch(), ver[0], DEFAULT_WAIT_NS, status.data_ptr(),
+                                            symm.done_counter.data_ptr() + 8, fh._NUM_RS_CTAS, stream), "rs")
 
     shard_t = torch.empty(shard, dtype=torch.bfloat16, device=dev)
     grad_full = torch.randn(numel, dtype=torch.bfloat16, device=dev)
@@ -160,13 +206,23 @@ def main():
     roof = max((n - 1) * shard * 2 / (LINK_GBS * 1e9), numel * 2 / (hbm_gbs * 1e9)) * 1e3
     out.append({"path": "hsdp_p2p_allgather", "n_gpus": n, "params": numel, "fused_ms": t, "nccl_ms": timed(ag_nccl),
                 "roofline_ms": roof, "fraction_of_roofline": roof / t, "peaks": src})
-    t = timed(rs)
-    # bytes: (n-1) peer shards of bf16 gradients over NVLink; local: own gradient shard 2 B, master/m/v read +
-    # write 24 B, bf16 parameter write 2 B per owned element
+    # bytes: (n-1) peer shards of bf16 gradients over NVLink (egress; with the in-switch reduction the
+    # ingress is one shard); local: own gradient shard 2 B, master/m/v read + write 24 B, bf16
+    # parameter write 2 B per owned element
     roof = max((n - 1) * shard * 2 / (LINK_GBS * 1e9), shard * 28 / (hbm_gbs * 1e9)) * 1e3
-    out.append({"path": "hsdp_fused_rs_adamw", "n_gpus": n, "params": numel, "fused_ms": t,
-                "nccl_rs_plus_adamw_ms": timed(rs_nccl), "roofline_ms": roof, "fraction_of_roofline": roof / t,
+    t_nccl = timed(rs_nccl)
+    t = timed(lambda: rs(None))
+    out.append({"path": "hsdp_fused_rs_adamw[peer loads]", "n_gpus": n, "params": numel, "fused_ms": t,
+                "nccl_rs_plus_adamw_ms": t_nccl, "roofline_ms": roof, "fraction_of_roofline": roof / t,
                 "peaks": src})
+    if symm.mc_base is not None:
+        t = timed(lambda: rs(symm.mc_base + goff))
+        out.append({"path": "hsdp_fused_rs_adamw[multimem.ld_reduce]", "n_gpus": n, "params": numel, "fused_ms": t,
+                    "nccl_rs_plus_adamw_ms": t_nccl, "roofline_ms": roof, "fraction_of_roofline": roof / t,
+                    "peaks": src})
+    else:
+        out.append({"path": "hsdp_fused_rs_adamw[multimem.ld_reduce]", "n_gpus": n,
+                    "unavailable": f"no multicast mapping (transport {symm.transport})"})
     native.check_status(dev)
     if rank == 0:
         for o in out:

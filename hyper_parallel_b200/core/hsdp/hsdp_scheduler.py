@@ -80,6 +80,11 @@ def _root_backward_callback() -> None:
     global _ROOT_CALLBACK_QUEUED
     _ROOT_CALLBACK_QUEUED = False
     for sch in _ALL_SCHEDULERS:
+        # buckets that are only partly filled (a parameter got no gradient in this pass) are
+        # completed with zeros and reduced now; afterwards no bucket keeps stale entries
+        _PENDING.extend(sch.hsdp_state.flush_partial_buckets())
+        sch.hsdp_state.reset_buckets()
+    for sch in _ALL_SCHEDULERS:
         if sch.state in (FwdBwdState.PRE_BACKWARD, FwdBwdState.BACKWARD) or not sch.hsdp_state.is_sharded:
             sch.hsdp_state.shard()
         sch.state = FwdBwdState.PRE_FORWARD

@@ -178,14 +178,20 @@ class HSDPState:
         from ...parallel import fused_hsdp
         level3 = self.config.shard_level == OptimizerLevel.SHARD_OPT_GRAD_PARAM
         for plist in groups.values():
-            if plist[0].shard.device.type == "cuda" and fused_hsdp.can_use(plist):
-                buf = fused_hsdp.SymmParamBuffer(plist, level3)      # NVLink P2P gather + fused RS/AdamW
-                self.symm_buffers.append(buf)
-                self.param_buffers.append(buf)
-                self._in_buffer.update(id(p) for p in plist)
-            elif len(plist) > 1:
-                self.param_buffers.append(HSDPParamBuffer(plist))
-                self._in_buffer.update(id(p) for p in plist)
+            rest = plist
+            if plist[0].shard.device.type == "cuda":
+                # the parameters that can live in symmetric memory do; one odd parameter (fp32, a
+                # DTensor, a shard that is not a whole number of vectors) no longer sends its whole
+                # group to the NCCL buffers
+                symm, rest = fused_hsdp.split_eligible(plist)
+                if symm:
+                    buf = fused_hsdp.SymmParamBuffer(symm, level3)   # NVLink gather + fused RS/AdamW
+                    self.symm_buffers.append(buf)
+                    self.param_buffers.append(buf)
+                    self._in_buffer.update(id(p) for p in symm)
+            if len(rest) > 1:
+                self.param_buffers.append(HSDPParamBuffer(rest))
+                self._in_buffer.update(id(p) for p in rest)
 
     def rebuild_param_buffers(self) -> None:
         """Re-create the flat parameter buffers from the current shards (after materialisation)."""
@@ -254,6 +260,8 @@ class HSDPState:
             return
         for p in self.sharded_params:
             p.to_sharded()
+        for b in self.symm_buffers:
+            b.release_staging()          # the gathered weights do not outlive their consumers
         self.is_sharded = True
 
     # ----------------------------------------------------------------- grads --
@@ -275,6 +283,33 @@ class HSDPState:
             if hp.param.requires_grad:
                 self.grad_hook.process(hp, view)
         buf.grad_fresh = True
+
+    def flush_partial_buckets(self):
+        """End of a backward pass: buckets in which some parameters produced no gradient (an unused
+        branch, an expert without tokens) are completed with zeros -- every rank does the same, so
+        the collectives stay matched -- and reduced.  Returns the pending reductions."""
+        pending = []
+        sync = self.grad_hook.requires_grad_sync
+        for b in self.grad_buffers:
+            if not b.ready or len(b.ready) == len(b.params):
+                continue
+            for p in b.params:
+                if id(p) not in b.ready:
+                    b.ready[id(p)] = torch.zeros(p.full_shape, dtype=p.leaf.dtype, device=p.leaf.device)
+            r = b.reduce(sync)
+            if r is not None:
+                pending.append(r)
+        for buf in self.symm_buffers:
+            if buf.flush_missing():
+                self.symm_bucket_done(buf)
+        return pending
+
+    def reset_buckets(self) -> None:
+        """Nothing of one backward pass leaks into the next."""
+        for b in self.grad_buffers:
+            b.ready = {}
+        for buf in self.symm_buffers:
+            buf.ready = set()
 
     def zero_grads(self) -> None:
         for b in self.symm_buffers:

@@ -104,6 +104,9 @@ class LlamaBlock(nn.Module):
         self.ffn_norm = nn.Parameter(torch.empty(h, **kw))
         self.w_gate_up = nn.Parameter(torch.empty(2 * cfg.ffn_size, h, **kw))
         self.w_down = nn.Parameter(torch.empty(h, cfg.ffn_size, **kw))
+        # these matrices are only ever consumed by ops.linear: HSDP may gather them inside the GEMM
+        for w in (self.wqkv, self.wo, self.w_gate_up, self.w_down):
+            w._hpb_gemm_only = True
 
     def reset_parameters(self):
         std = self.cfg.init_std
@@ -157,6 +160,7 @@ class Llama(nn.Module):
             self.lm_head = self.embed
         else:
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
+            self.lm_head._hpb_gemm_only = True
 
     def reset_parameters(self):
         nn.init.normal_(self.embed, mean=0.0, std=self.cfg.init_std)

@@ -35,12 +35,21 @@ struct DispatchParams {
   int* block_group;      // [cap_rows / 128]: local expert of the block, -1 = unused
   int* group_offsets;    // [El + 1]
   int* meta;             // [0] padded rows in use
+  int* counts_all;       // [n, E] local snapshot of every rank's counts (read by the combine kernel)
   uint32_t epoch;
   uint64_t limit_ns;
   int* status;
 };
 
 __device__ __forceinline__ int pad128(int x) { return (x + ROW_BLOCK - 1) / ROW_BLOCK * ROW_BLOCK; }
+
+// Error paths leave "no block in use" / "every expert empty" tables behind, so that the grouped
+// GEMMs queued after a failed dispatch skip every block instead of reading uninitialised tables.
+__device__ __forceinline__ void write_empty_tables(const DispatchParams& p) {
+  for (int b = threadIdx.x; b < p.cap_rows / ROW_BLOCK; b += blockDim.x) p.block_group[b] = -1;
+  for (int el = threadIdx.x; el <= p.E / p.n; el += blockDim.x) p.group_offsets[el] = 0;
+  if (threadIdx.x == 0) p.meta[0] = 0;
+}
 
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const DispatchParams p) {
@@ -51,7 +60,10 @@ ep_dispatch_kernel(const DispatchParams p) {
   const int El = p.E / p.n;
   if (p.n > 1) {
     if (blockIdx.x == 0) signal_peers(p.pads, p.rank, p.n, 0, p.epoch);   // my staging is complete
-    if (!wait_peers(p.pads, p.rank, p.n, 0, p.epoch, p.limit_ns, p.status)) return;
+    if (!wait_peers(p.pads, p.rank, p.n, 0, p.epoch, p.limit_ns, p.status)) {
+      if (blockIdx.x == 0) write_empty_tables(p);
+      return;
+    }
   }
   for (int i = threadIdx.x; i < p.n * p.E; i += blockDim.x) {
     const int s = i / p.E, e = i - s * p.E;
@@ -84,8 +96,16 @@ ep_dispatch_kernel(const DispatchParams p) {
   }
   __syncthreads();
   const int m_pad = s_start[El];
+  if (blockIdx.x == 0)
+    // the combine kernel of this layer reads the counts from this local snapshot, never from a
+    // peer: a rank that runs ahead may already be staging the counts of its next dispatch
+    for (int i = threadIdx.x; i < p.n * p.E; i += blockDim.x) p.counts_all[i] = s_cnt[i / p.E][i % p.E];
   if (m_pad > p.cap_rows) {
-    if (threadIdx.x == 0) report(p.status, 6 /*kBadArgument*/, 0x4000 | (m_pad / ROW_BLOCK));
+    // Overflow of the receive matrix is an error (code 6, surfaced by the host's status check).
+    if (blockIdx.x == 0) {
+      write_empty_tables(p);
+      if (threadIdx.x == 0) report(p.status, 6 /*kBadArgument*/, 0x4000 | (m_pad / ROW_BLOCK));
+    }
     return;
   }
   if (blockIdx.x == 0) {
@@ -167,7 +187,8 @@ ep_dispatch_kernel(const DispatchParams p) {
 
 struct CombineParams {
   int T, k, H, E, n, rank;
-  PeerTable out, counts, pads;     // expert-output matrices [cap_rows, H] and counts[E] of every rank
+  PeerTable out, pads;             // expert-output matrices [cap_rows, H] of every rank
+  const int* counts_all;           // [n, E] local snapshot written by the dispatch kernel of this layer
   const long long* topk_idx;       // [T, k] global expert of each pair
   const int* sorted_pos;           // [T * k] position of the pair in my sorted-by-expert list
   const float* weights;            // [T, k] or null (unit weights)
@@ -194,7 +215,7 @@ ep_combine_kernel(const CombineParams p) {
   for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
     int tot = 0, before = 0;
     for (int s = 0; s < p.n; ++s) {
-      const int c = reinterpret_cast<const int*>(p.counts.ptr[s])[e];
+      const int c = p.counts_all[s * p.E + e];
       if (s < p.rank) before += c;
       tot += c;
     }
@@ -213,7 +234,7 @@ ep_combine_kernel(const CombineParams p) {
   }
   if (threadIdx.x == 32) {
     int acc = 0;
-    const int* mine = reinterpret_cast<const int*>(p.counts.ptr[p.rank]);
+    const int* mine = p.counts_all + p.rank * p.E;
     for (int e = 0; e < p.E; ++e) {
       s_myoff[e] = acc;
       acc += mine[e];
@@ -277,10 +298,11 @@ using namespace hpb;
 
 // x_stage / sorted_token / sorted_scale / counts / pads: arrays of n device pointers (symmetric
 // memory; sorted_scale may be null).  recv [cap_rows, H], block_group [cap_rows / 128],
-// group_offsets [E / n + 1] and meta [1] are local outputs.
+// group_offsets [E / n + 1], meta [1] and counts_all [n, E] are local outputs.
 extern "C" int hpb_ep_dispatch(void* const* x_stage, void* const* sorted_token, void* const* sorted_scale,
                                void* const* counts, void* const* pads, void* recv, int* block_group,
-                               int* group_offsets, int* meta, int T, int k, int H, int E, int n, int rank,
+                               int* group_offsets, int* meta, int* counts_all, int T, int k, int H, int E, int n,
+                               int rank,
                                int cap_rows, unsigned epoch, unsigned long long limit_ns, int* status, int num_ctas,
                                cudaStream_t stream) {
   if (n < 1 || n > ep::kMaxEp || E > ep::kMaxExperts || E % n || E / n > ep::kMaxLocal || (H % 8) ||
@@ -295,6 +317,7 @@ extern "C" int hpb_ep_dispatch(void* const* x_stage, void* const* sorted_token, 
   p.pads = ep::table(pads, n);
   p.recv = reinterpret_cast<__nv_bfloat16*>(recv);
   p.block_group = block_group; p.group_offsets = group_offsets; p.meta = meta;
+  p.counts_all = counts_all;
   p.epoch = epoch; p.limit_ns = limit_ns; p.status = status;
   cudaFuncSetAttribute(ep::ep_dispatch_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                        cudaSharedmemCarveoutMaxShared);
@@ -302,9 +325,10 @@ extern "C" int hpb_ep_dispatch(void* const* x_stage, void* const* sorted_token, 
   return static_cast<int>(cudaGetLastError());
 }
 
-// out / counts / pads: arrays of n device pointers (symmetric memory).  topk_idx [T, k] int64,
+// out / pads: arrays of n device pointers (symmetric memory); counts_all [n, E] is the local
+// snapshot that the dispatch kernel of the same layer wrote.  topk_idx [T, k] int64,
 // sorted_pos [T*k] int32, weights [T, k] fp32 or null; y [T, H]; rows_save [T*k, H] or null.
-extern "C" int hpb_ep_combine(void* const* out, void* const* counts, void* const* pads, const void* topk_idx,
+extern "C" int hpb_ep_combine(void* const* out, const int* counts_all, void* const* pads, const void* topk_idx,
                               const int* sorted_pos, const float* weights, void* y, void* rows_save, int T, int k,
                               int H, int E, int n, int rank, unsigned epoch, unsigned long long limit_ns,
                               int* status, int num_ctas, cudaStream_t stream) {
@@ -312,7 +336,7 @@ extern "C" int hpb_ep_combine(void* const* out, void* const* counts, void* const
   ep::CombineParams p;
   p.T = T; p.k = k; p.H = H; p.E = E; p.n = n; p.rank = rank;
   p.out = ep::table(out, n);
-  p.counts = ep::table(counts, n);
+  p.counts_all = counts_all;
   p.pads = ep::table(pads, n);
   p.topk_idx = reinterpret_cast<const long long*>(topk_idx);
   p.sorted_pos = sorted_pos;

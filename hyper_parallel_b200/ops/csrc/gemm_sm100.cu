@@ -89,7 +89,10 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p) {
     const int per = num_m * num_n;
     ti.group = t / per;
     tile_coords(t - ti.group * per, num_m, num_n, m_blk, n_blk);
-    const int r0 = p.group_offsets[ti.group], r1 = p.group_offsets[ti.group + 1];
+    // offsets come from a device-side table: clamp them to the operands' row count (p.K in this
+    // mode) so that a corrupt table can never turn into an unbounded K loop
+    const int r0 = min(max(p.group_offsets[ti.group], 0), p.K);
+    const int r1 = min(max(p.group_offsets[ti.group + 1], r0), p.K);
     ti.k_row0 = r0;
     ti.num_k = (r1 - r0 + BLOCK_K - 1) / BLOCK_K;
   } else {
@@ -493,7 +496,9 @@ extern "C" int hpb_gemm_bf16_grouped(const void* A, int a_mn, int64_t lda, int64
   else
     r = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, b_rows, ldb, 64, BLOCK_K);
   if (r) return r;
-  GemmParams p{M, N, K, C, ldc, status, mode, block_group, group_offsets, num_groups, b_group_rows};
+  // mode 2 contracts over operand rows: K carries their total count (the bound of every expert's range)
+  GemmParams p{M, N, mode == 2 ? static_cast<int>(a_rows < b_rows ? a_rows : b_rows) : K, C, ldc, status, mode,
+               block_group, group_offsets, num_groups, b_group_rows};
   const int key = (a_mn ? 8 : 0) | (b_mn ? 4 : 0) | (out_f32 ? 2 : 0) | (accumulate ? 1 : 0);
   switch (key) {
 #define HPB_CASE(k, a, b, o, c) \

@@ -28,12 +28,13 @@ struct Segment {
   long long full_off;
   long long shard_off;
   long long n;
+  long long group;   // index into the AdamTable of the launch (optimizer parameter group)
 };
 
 __global__ void symm_barrier_kernel(PeerTable pads, int rank, int n, int slot, uint32_t epoch,
-                                    uint64_t limit_ns, int do_signal, int* status) {
+                                    uint64_t limit_ns, int do_signal, int do_wait, int* status) {
   if (do_signal) signal_peers(pads, rank, n, slot, epoch);
-  wait_peers(pads, rank, n, slot, epoch, limit_ns, status);
+  if (do_wait) wait_peers(pads, rank, n, slot, epoch, limit_ns, status);
 }
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
@@ -53,11 +54,14 @@ p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict
                      int num_segs, __nv_bfloat16* __restrict__ full, int rank, int n, uint32_t epoch,
                      uint64_t limit_ns, int* status, unsigned int* done_counter) {
   const bool sync = pads.ptr[0] != nullptr && n > 1;
+  bool ok = true;
   if (sync) {
     if (blockIdx.x == 0) signal_peers(pads, rank, n, 0, epoch);   // my shard is final
-    if (!wait_peers(pads, rank, n, 0, epoch, limit_ns, status)) return;
+    ok = wait_peers(pads, rank, n, 0, epoch, limit_ns, status);
   }
-  for (int s = 0; s < num_segs; ++s) {
+  // a CTA whose wait ran out copies nothing but still takes part in the last-CTA count below, so
+  // that the counter is back at zero for the next launch on this buffer
+  for (int s = 0; s < (ok ? num_segs : 0); ++s) {
     const Segment sg = segs[s];
     const long long nv = sg.n >> 3;  // 16-byte vectors (n and offsets are multiples of 8)
     for (int rr = 0; rr < n; ++rr) {
@@ -94,7 +98,7 @@ p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict
     if (s_last) {
       if (threadIdx.x == 0) *done_counter = 0;
       signal_peers(pads, rank, n, 1, epoch);
-      wait_peers(pads, rank, n, 1, epoch, limit_ns, status);
+      if (ok) wait_peers(pads, rank, n, 1, epoch, limit_ns, status);
     }
   }
 }
@@ -103,33 +107,94 @@ p2p_allgather_kernel(PeerTable shards, PeerTable pads, const Segment* __restrict
 struct AdamArgs {
   float lr, b1, b2, eps, wd, bc1, bc2, grad_scale;
 };
+constexpr int kMaxAdamGroups = 4;
+// One entry per optimizer parameter group that has a parameter in the flat buffer (Segment::group
+// selects the entry): learning rate, weight decay, ... may differ between the matrices and the
+// norm weights of one module.
+struct AdamTable {
+  AdamArgs g[kMaxAdamGroups];
+};
+
+// Sum over all ranks of the 8 bf16 gradients at `mc_addr` of a multicast (NVLS) mapping: the
+// NVSwitch reads the address on every GPU bound to the multicast object, adds in fp32 and returns
+// one rounded bf16 vector, so the data crosses this GPU's NVLink ingress once instead of N-1 times.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+
+__device__ __forceinline__ void adam8(const AdamArgs& a, const float (&acc)[8], float* __restrict__ master,
+                                      float* __restrict__ m, float* __restrict__ v,
+                                      __nv_bfloat16* __restrict__ param_shard, long long o) {
+  float4 m0 = *reinterpret_cast<float4*>(m + o), m1 = *reinterpret_cast<float4*>(m + o + 4);
+  float4 v0 = *reinterpret_cast<float4*>(v + o), v1 = *reinterpret_cast<float4*>(v + o + 4);
+  float4 w0 = *reinterpret_cast<float4*>(master + o), w1 = *reinterpret_cast<float4*>(master + o + 4);
+  float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+  float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float g = acc[e] * a.grad_scale;
+    mm[e] = a.b1 * mm[e] + (1.f - a.b1) * g;
+    vv[e] = a.b2 * vv[e] + (1.f - a.b2) * g * g;
+    ww[e] = ww[e] * (1.f - a.lr * a.wd) - a.lr * (mm[e] / a.bc1) / (sqrtf(vv[e] / a.bc2) + a.eps);
+  }
+  *reinterpret_cast<float4*>(m + o) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+  *reinterpret_cast<float4*>(m + o + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
+  *reinterpret_cast<float4*>(v + o) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+  *reinterpret_cast<float4*>(v + o + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+  *reinterpret_cast<float4*>(master + o) = make_float4(ww[0], ww[1], ww[2], ww[3]);
+  *reinterpret_cast<float4*>(master + o + 4) = make_float4(ww[4], ww[5], ww[6], ww[7]);
+  uint4 out;
+  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(ww[2 * e], ww[2 * e + 1]);
+  *reinterpret_cast<uint4*>(param_shard + o) = out;
+}
 
 // Launched with 512 threads; the bound of 768 caps the kernel at 80 registers per thread, so
 // that a CTA (40 K registers) fits beside a persistent GEMM CTA (192 threads x 96 registers)
 // in the 64 K register file of an SM -- otherwise the 8-peer instance would need the whole
 // file and could only run in the gaps between GEMM launches.
-template <int N>  // N > 0: compile-time peer count (loads fully unrolled); N == 0: runtime `n`
+//
+// N > 0: compile-time peer count (loads fully unrolled); N == 0: runtime `n`.
+// MC: the gradients are read through `mc_grads`, a multicast (NVLS) mapping of all ranks' flat
+// gradient buffers, with one multimem.ld_reduce per 16-byte vector instead of N peer loads.
+//
+// When the update is done the kernel publishes `version` on slot 4 of every peer's signal pad:
+// "my parameter shard has reached this version"; the fused all-gather inside the consumer GEMMs
+// of the next step waits for it.
+template <int N, bool MC>
 __global__ void __launch_bounds__(768)
-fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict__ segs,
-                      int num_segs, float* __restrict__ master, float* __restrict__ m,
-                      float* __restrict__ v, __nv_bfloat16* __restrict__ param_shard, AdamArgs a,
-                      int rank, int n, uint32_t epoch, uint64_t limit_ns, int* status,
-                      unsigned int* done_counter) {
+fused_rs_adamw_kernel(PeerTable grads, const __nv_bfloat16* __restrict__ mc_grads, PeerTable pads,
+                      const Segment* __restrict__ segs, int num_segs, float* __restrict__ master,
+                      float* __restrict__ m, float* __restrict__ v, __nv_bfloat16* __restrict__ param_shard,
+                      AdamTable tbl, int rank, int n, uint32_t epoch, uint32_t version, uint64_t limit_ns,
+                      int* status, unsigned int* done_counter) {
   const bool sync = pads.ptr[0] != nullptr && n > 1;
+  bool ok = true;
   if (sync) {
     if (blockIdx.x == 0) signal_peers(pads, rank, n, 2, epoch);   // my gradients are complete
-    if (!wait_peers(pads, rank, n, 2, epoch, limit_ns, status)) return;
+    ok = wait_peers(pads, rank, n, 2, epoch, limit_ns, status);
   }
-  for (int s = 0; s < num_segs; ++s) {
+  // a CTA whose wait ran out updates nothing but still takes part in the last-CTA count below
+  for (int s = 0; s < (ok ? num_segs : 0); ++s) {
     const Segment sg = segs[s];
+    const AdamArgs a = tbl.g[sg.group];
     const long long nv = sg.n >> 3;
+    const long long goff = sg.full_off + static_cast<long long>(rank) * sg.n;
     for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
       float acc[8];
+      if constexpr (MC) {
+        unpack8(multimem_ld_reduce_bf16x8(mc_grads + goff + (i << 3)), acc);
+      } else if constexpr (N > 0) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      const long long goff = sg.full_off + static_cast<long long>(rank) * sg.n;
-      if constexpr (N > 0) {
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
         // issue all peer loads first (they are independent), then reduce in fp32
         uint4 buf[N];
 #pragma unroll
@@ -146,6 +211,8 @@ fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict
           for (int e = 0; e < 8; ++e) acc[e] += f[e];
         }
       } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
         for (int rr = 0; rr < n; ++rr) {
           const int r = (rank + rr) % n;
           float f[8];
@@ -155,39 +222,14 @@ fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict
           for (int e = 0; e < 8; ++e) acc[e] += f[e];
         }
       }
-      const long long o = sg.shard_off + (i << 3);
-      float4 m0 = *reinterpret_cast<float4*>(m + o), m1 = *reinterpret_cast<float4*>(m + o + 4);
-      float4 v0 = *reinterpret_cast<float4*>(v + o), v1 = *reinterpret_cast<float4*>(v + o + 4);
-      float4 w0 = *reinterpret_cast<float4*>(master + o), w1 = *reinterpret_cast<float4*>(master + o + 4);
-      float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-      float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-      float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float g = acc[e] * a.grad_scale;
-        mm[e] = a.b1 * mm[e] + (1.f - a.b1) * g;
-        vv[e] = a.b2 * vv[e] + (1.f - a.b2) * g * g;
-        ww[e] = ww[e] * (1.f - a.lr * a.wd) - a.lr * (mm[e] / a.bc1) / (sqrtf(vv[e] / a.bc2) + a.eps);
-      }
-      *reinterpret_cast<float4*>(m + o) = make_float4(mm[0], mm[1], mm[2], mm[3]);
-      *reinterpret_cast<float4*>(m + o + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
-      *reinterpret_cast<float4*>(v + o) = make_float4(vv[0], vv[1], vv[2], vv[3]);
-      *reinterpret_cast<float4*>(v + o + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
-      *reinterpret_cast<float4*>(master + o) = make_float4(ww[0], ww[1], ww[2], ww[3]);
-      *reinterpret_cast<float4*>(master + o + 4) = make_float4(ww[4], ww[5], ww[6], ww[7]);
-      uint4 out;
-      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) ob[e] = __floats2bfloat162_rn(ww[2 * e], ww[2 * e + 1]);
-      *reinterpret_cast<uint4*>(param_shard + o) = out;
+      adam8(a, acc, master, m, v, param_shard, sg.shard_off + (i << 3));
     }
     // tail (n % 8) elements, one CTA
     if (blockIdx.x == 0) {
       for (long long j = (nv << 3) + threadIdx.x; j < sg.n; j += blockDim.x) {
         float g = 0.f;
         for (int r = 0; r < n; ++r)
-          g += __bfloat162float((reinterpret_cast<const __nv_bfloat16*>(grads.ptr[r]) + sg.full_off +
-                                 static_cast<long long>(rank) * sg.n)[j]);
+          g += __bfloat162float((reinterpret_cast<const __nv_bfloat16*>(grads.ptr[r]) + goff)[j]);
         g *= a.grad_scale;
         const long long o = sg.shard_off + j;
         const float mi = a.b1 * m[o] + (1.f - a.b1) * g;
@@ -198,7 +240,7 @@ fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict
       }
     }
   }
-  if (sync) {
+  {
     __syncthreads();
     __shared__ int s_last;
     if (threadIdx.x == 0) {
@@ -207,9 +249,16 @@ fused_rs_adamw_kernel(PeerTable grads, PeerTable pads, const Segment* __restrict
     }
     __syncthreads();
     if (s_last) {
-      if (threadIdx.x == 0) *done_counter = 0;
-      signal_peers(pads, rank, n, 3, epoch);   // done reading everybody's gradients
-      wait_peers(pads, rank, n, 3, epoch, limit_ns, status);
+      if (threadIdx.x == 0) {
+        *done_counter = 0;
+        __threadfence();
+      }
+      __syncthreads();
+      if (sync && ok) {
+        signal_peers(pads, rank, n, 3, epoch);     // done reading everybody's gradients
+        signal_peers(pads, rank, n, 4, version);   // my parameter shard has reached `version`
+        wait_peers(pads, rank, n, 3, epoch, limit_ns, status);
+      }
     }
   }
 }
@@ -264,7 +313,17 @@ extern "C" int hpb_symm_barrier(void* const* pads, int rank, int n, int slot, un
   if (n > kMaxPeers) return -2;
   prefer_shared(symm_barrier_kernel);
   symm_barrier_kernel<<<1, 32, 0, s>>>(make_table(pads, n), rank, n, slot, epoch, limit_ns,
-                                       do_signal, status);
+                                       do_signal, 1, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Publish `value` on `slot` of every peer's signal pad without waiting for anybody (stream
+// ordered: everything queued before it on `s` is visible to a peer that sees the value).
+extern "C" int hpb_symm_signal(void* const* pads, int rank, int n, int slot, unsigned value,
+                               cudaStream_t s) {
+  if (n > kMaxPeers) return -2;
+  prefer_shared(symm_barrier_kernel);
+  symm_barrier_kernel<<<1, 32, 0, s>>>(make_table(pads, n), rank, n, slot, value, 0, 1, 0, nullptr);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -281,26 +340,40 @@ extern "C" int hpb_p2p_allgather(void* const* shard_ptrs, void* const* pads, con
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int hpb_fused_rs_adamw(void* const* grad_ptrs, void* const* pads, const void* segs,
-                                  int num_segs, float* master, float* m, float* v, void* param_shard,
-                                  float lr, float b1, float b2, float eps, float wd, int step,
-                                  float grad_scale, int rank, int n, unsigned epoch,
+// hyper: num_groups x 5 floats {lr, beta1, beta2, eps, weight_decay}, one row per optimizer
+// parameter group referenced by the segments (num_groups <= 4).  mc_grads: multicast (NVLS)
+// address of the flat gradient buffers, or null for plain peer loads.  version: the value
+// published on slot 4 of the peers' signal pads when this rank's shard has been rewritten.
+extern "C" int hpb_fused_rs_adamw(void* const* grad_ptrs, const void* mc_grads, void* const* pads,
+                                  const void* segs, int num_segs, float* master, float* m, float* v,
+                                  void* param_shard, const float* hyper, int num_groups, int step,
+                                  float grad_scale, int rank, int n, unsigned epoch, unsigned version,
                                   unsigned long long limit_ns, int* status, unsigned* done_counter,
                                   int num_ctas, cudaStream_t s) {
-  if (n > kMaxPeers) return -2;
-  AdamArgs a{lr, b1, b2, eps, wd, 1.f - powf(b1, (float)step), 1.f - powf(b2, (float)step), grad_scale};
-#define HPB_RS(NN)                                                                              \
-  prefer_shared(fused_rs_adamw_kernel<NN>);                                                     \
-  fused_rs_adamw_kernel<NN><<<num_ctas, 512, 0, s>>>(                                           \
-      make_table(grad_ptrs, n), make_table(pads, n), reinterpret_cast<const Segment*>(segs),    \
-      num_segs, master, m, v, reinterpret_cast<__nv_bfloat16*>(param_shard), a, rank, n, epoch, \
-      limit_ns, status, done_counter)
-  switch (n) {
-    case 1: HPB_RS(1); break;
-    case 2: HPB_RS(2); break;
-    case 4: HPB_RS(4); break;
-    case 8: HPB_RS(8); break;
-    default: HPB_RS(0); break;
+  if (n > kMaxPeers || num_groups < 1 || num_groups > kMaxAdamGroups) return -2;
+  AdamTable tbl;
+  for (int g = 0; g < kMaxAdamGroups; ++g) {
+    const float* h = hyper + 5 * (g < num_groups ? g : 0);
+    tbl.g[g] = AdamArgs{h[0], h[1], h[2], h[3], h[4], 1.f - powf(h[1], (float)step),
+                        1.f - powf(h[2], (float)step), grad_scale};
+  }
+#define HPB_RS(NN, MCAST)                                                                        \
+  prefer_shared(fused_rs_adamw_kernel<NN, MCAST>);                                               \
+  fused_rs_adamw_kernel<NN, MCAST><<<num_ctas, 512, 0, s>>>(                                     \
+      make_table(grad_ptrs, n), reinterpret_cast<const __nv_bfloat16*>(mc_grads),                \
+      make_table(pads, n), reinterpret_cast<const Segment*>(segs), num_segs, master, m, v,       \
+      reinterpret_cast<__nv_bfloat16*>(param_shard), tbl, rank, n, epoch, version, limit_ns,     \
+      status, done_counter)
+  if (mc_grads != nullptr && n > 1) {
+    HPB_RS(0, true);
+  } else {
+    switch (n) {
+      case 1: HPB_RS(1, false); break;
+      case 2: HPB_RS(2, false); break;
+      case 4: HPB_RS(4, false); break;
+      case 8: HPB_RS(8, false); break;
+      default: HPB_RS(0, false); break;
+    }
   }
 #undef HPB_RS
   return static_cast<int>(cudaGetLastError());

@@ -94,7 +94,13 @@ class _Linear(torch.autograd.Function):
         # allocate with the final shape: the result must not be a view created inside the Function
         # (callers may update it in place, e.g. RoPE on the fused QKV buffer)
         y = torch.empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16, device=x.device)
-        gemm(x2, w, out=y.view(-1, w.shape[0]))
+        hs = getattr(w, "_hpb_symm", None)
+        if hs is not None and hs[0].gather_pending(hs[1]):
+            # HSDP: the weight has not been gathered yet -- this product gathers it from the peers
+            # inside the GEMM kernel (the all-gather is fused into its first consumer)
+            hs[0].gather_gemm(hs[1], x2, y.view(-1, w.shape[0]), w_mn=False)
+        else:
+            gemm(x2, w, out=y.view(-1, w.shape[0]))
         return y
 
     @staticmethod
@@ -104,8 +110,16 @@ class _Linear(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = None
+        hs = getattr(w, "_hpb_symm", None)
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+            if hs is not None and hs[0].gather_pending(hs[1]):
+                # level-3 backward: the input-gradient product is the first consumer of the
+                # re-gathered weight
+                dx = torch.empty((dy2.shape[0], w.shape[1]), dtype=torch.bfloat16, device=dy2.device)
+                hs[0].gather_gemm(hs[1], dy2, dx, w_mn=True)
+                dx = dx.view(ctx.x_shape)
+            else:
+                dx = gemm(dy2, w, b_mn=True).view(ctx.x_shape)
         if ctx.needs_input_grad[1] and ctx.symm is not None:
             # HSDP over symmetric memory: the epilogue writes dW into the flat gradient buffer that
             # the fused reduce-scatter + AdamW kernel of every peer reads
@@ -133,6 +147,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         symm = getattr(w, "_hpb_symm", None) if (w.requires_grad and torch.is_grad_enabled()) else None
         y = _Linear.apply(x, w, wgrad_into, symm)
         return y if bias is None else y + bias
+    hs = getattr(w, "_hpb_symm", None)
+    if hs is not None and hs[0].gather_pending(hs[1]):
+        hs[0].materialize(hs[1])
     return F.linear(x, w, bias)
 
 

@@ -11,6 +11,7 @@ advances the step counter.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Iterable
 
 import torch
@@ -33,6 +34,7 @@ class FusedAdamW(torch.optim.Optimizer):
         self._done_in_backward = set()
         self._fused_params = set()
         self._flat_states: Dict[int, dict] = {}
+        self._buffer_groups: Dict[int, list] = {}
         self._group_of: Dict[int, dict] = {}
         for g in self.param_groups:
             for p in g["params"]:
@@ -97,11 +99,37 @@ class FusedAdamW(torch.optim.Optimizer):
             if hp is None or id(p) not in self._group_of:
                 continue
             symm = getattr(hp, "_symm", None)
-            if symm is not None:
-                symm[0].optimizer = self
+            if symm is not None and self._attach_buffer(symm[0]):
                 self._fused_params.add(id(p))
-            else:
+            elif symm is None:
                 hp.grad_consumer = self._consume
+
+    def _attach_buffer(self, buf) -> bool:
+        """Let the fused reduce-scatter + AdamW kernel update ``buf``.  Its parameters may belong to
+        different parameter groups (no weight decay on the norm weights, per-group learning rates):
+        every segment of the flat buffer carries the index of its group's row in the hyper-parameter
+        table of the launch.  A buffer whose parameters are not all in this optimizer, or span more
+        groups than the table holds, is left to the unfused path."""
+        if buf.optimizer is self:
+            return True
+        groups, index = [], []
+        for hp in buf.params:
+            g = self._group_of.get(id(hp.param))
+            if g is None:
+                return False
+            for k, have in enumerate(groups):
+                if have is g:
+                    index.append(k)
+                    break
+            else:
+                groups.append(g)
+                index.append(len(groups) - 1)
+        if len(groups) > 4:
+            return False
+        buf.optimizer = self
+        buf.set_param_groups(index)
+        self._buffer_groups[id(buf)] = groups
+        return True
 
     def flat_state_for(self, buf) -> dict:
         """fp32 master / moments for the flat shard of a symmetric buffer."""
@@ -113,8 +141,14 @@ class FusedAdamW(torch.optim.Optimizer):
             self._flat_states[id(buf)] = st
         return st
 
-    def group_for(self, buf) -> dict:
-        return self._group_of[id(buf.params[0].param)]
+    def hyper_table_for(self, buf):
+        """``{lr, beta1, beta2, eps, weight_decay}`` of every parameter group of ``buf`` (ctypes floats,
+        read at launch time so that schedulers that change ``lr`` are honoured)."""
+        groups = self._buffer_groups[id(buf)]
+        vals = []
+        for g in groups:
+            vals += [g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"]]
+        return (ctypes.c_float * len(vals))(*vals)
 
     def _consume(self, hp, grad: torch.Tensor) -> None:
         p = hp.param

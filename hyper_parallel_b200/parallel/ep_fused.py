@@ -10,7 +10,10 @@ One :class:`EPWorkspace` per (group, shape) owns a symmetric region with the sta
 sorted pair lists, the per-expert counts and the expert-output matrix that peers pull from.  The
 receive matrix of a dispatch is an ordinary tensor sized for ``capacity`` x the balanced load
 (it is saved for the backward of the expert GEMMs); unused 128-row blocks are skipped by the
-GEMM kernel through a device-side block table, so no size ever returns to the host.
+GEMM kernel through a device-side block table, so no size ever returns to the host.  A router so
+imbalanced that one rank receives more than ``capacity`` x the balanced load is an ERROR: the
+dispatch kernel records status code 6, leaves empty tables (the expert GEMMs then do nothing) and
+``native.check_status()`` raises at the end of the step; raise ``capacity`` in that case.
 """
 from __future__ import annotations
 
@@ -35,10 +38,10 @@ def _lib():
     if not _bound:
         vp, ci, cu, cull = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_ulonglong
         pp = ctypes.POINTER(vp)
-        lib.hpb_ep_dispatch.argtypes = [pp, pp, pp, pp, pp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cu, cull, vp,
-                                        ci, vp]
+        lib.hpb_ep_dispatch.argtypes = [pp, pp, pp, pp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cu, cull,
+                                        vp, ci, vp]
         lib.hpb_ep_dispatch.restype = ci
-        lib.hpb_ep_combine.argtypes = [pp, pp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cu, cull, vp, ci, vp]
+        lib.hpb_ep_combine.argtypes = [pp, vp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cu, cull, vp, ci, vp]
         lib.hpb_ep_combine.restype = ci
         _bound = True
     return lib
@@ -77,6 +80,9 @@ class EPWorkspace:
         self.p_cnt, self.p_out = s.ptr_table(self.off_cnt), s.ptr_table(self.off_out)
         self.null_table = (ctypes.c_void_p * max(self.n, 1))()
         self.meta = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # every rank's counts as seen by the last dispatch on this rank (local: the combine kernel of
+        # the same layer reads them from here, not from a peer that may have moved on)
+        self.counts_all = torch.zeros(self.n * E, dtype=torch.int32, device=self.device)
         self.status = native.status_word(self.device)
         self.ctas = 2 * native.sm_count(self.device)
 
@@ -99,8 +105,8 @@ class EPWorkspace:
         offsets = torch.empty(self.e_local + 1, dtype=torch.int32, device=self.device)
         rc = _lib().hpb_ep_dispatch(self.p_x, self.p_tok, self.p_scale if scale is not None else self.null_table,
                                     self.p_cnt, self.symm.pad_ptrs, recv.data_ptr(), block_group.data_ptr(),
-                                    offsets.data_ptr(), self.meta.data_ptr(), self.T, self.k, self.H, self.E, self.n,
-                                    self.rank, self.cap_rows, self.symm.next_epoch(), limit_ns,
+                                    offsets.data_ptr(), self.meta.data_ptr(), self.counts_all.data_ptr(), self.T,
+                                    self.k, self.H, self.E, self.n, self.rank, self.cap_rows, self.symm.next_epoch(), limit_ns,
                                     self.status.data_ptr(), self.ctas, native.stream(self.device))
         native.check(rc, "hpb_ep_dispatch")
         return recv, block_group, offsets
@@ -109,7 +115,7 @@ class EPWorkspace:
         """Pull the k expert-output rows of every token out of the owners' ``out`` matrices."""
         y = torch.empty((self.T, self.H), dtype=torch.bfloat16, device=self.device)
         rows = torch.empty((self.T * self.k, self.H), dtype=torch.bfloat16, device=self.device) if save_rows else None
-        rc = _lib().hpb_ep_combine(self.p_out, self.p_cnt, self.symm.pad_ptrs, topk_idx.data_ptr(),
+        rc = _lib().hpb_ep_combine(self.p_out, self.counts_all.data_ptr(), self.symm.pad_ptrs, topk_idx.data_ptr(),
                                    sorted_pos.data_ptr(), native.ptr(weights), y.data_ptr(), native.ptr(rows),
                                    self.T, self.k, self.H, self.E, self.n, self.rank, self.symm.next_epoch(),
                                    limit_ns, self.status.data_ptr(), self.ctas, native.stream(self.device))

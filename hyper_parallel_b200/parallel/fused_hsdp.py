@@ -1,35 +1,53 @@
-"""HSDP over symmetric memory: P2P all-gather into place and fused reduce-scatter + AdamW.
+"""HSDP over symmetric memory: weight all-gather fused into the consumer GEMM, fused
+reduce-scatter + AdamW.
 
 This is the B200-native replacement of the two hot collectives of an HSDP step (the reference
 issues them as separate NCCL calls followed by cast / scale / optimizer kernels,
-hyper_parallel/core/hsdp/hsdp_param_buffer.py:74-97, hsdp_grad_buffer.py:95-135):
+hyper_parallel/platform/torch/hsdp/param.py:43-53, hyper_parallel/core/hsdp/hsdp_param_buffer.py:74-97,
+hsdp_grad_buffer.py:95-135):
 
 * the bf16 parameter shards of one wrapped module live in ONE flat buffer inside a
-  :class:`SymmetricMemory` region; unsharding is a single kernel in which every rank pulls all
-  peers' shard segments over NVLink straight into the per-parameter full tensors (no gather
-  buffer, no copy-out);
+  :class:`SymmetricMemory` region.  Unsharding a matrix that is only consumed by ``ops.linear``
+  costs no kernel of its own: the parameter receives a *ticket*, and the first GEMM that consumes
+  it (the forward product, or the input-gradient product of the level-3 backward) runs the
+  all-gather inside the GEMM kernel -- communication warps pull the peers' row panels over NVLink
+  into a staging matrix while the tensor cores already multiply the panels that have arrived.
+  The staging matrix comes from a small pool and goes back at reshard, so a gathered weight never
+  outlives its consumers (the semantics of the reference's only native component, the graph pass
+  platform/mindspore/custom_pass/passes/duplicate_on_multi_users/duplicate_on_multi_users.cc:287-353).
+  Everything else of the module (norm weights, embedding tables, matrices whose shape the fused
+  kernel does not take) is gathered by one peer-pull copy kernel on a side stream;
 * weight gradients are written by the wgrad GEMM epilogue directly into a flat gradient buffer
   in symmetric memory; when the module's backward is done ONE kernel reads this rank's slice of
-  every peer's gradient buffer, sums in fp32, scales, and applies AdamW to the fp32 master /
-  moments and the bf16 shard -- reduce-scatter, cast, scale and optimizer in a single pass over
+  every peer's gradient buffer -- through one ``multimem.ld_reduce`` per vector where the NVSwitch
+  supports multicast, else with N peer loads --, scales, and applies AdamW to the fp32 master /
+  moments and the bf16 shard: reduce-scatter, cast, scale and optimizer in a single pass over
   the data, overlapped with the backward of the next module on a side stream.
 
-Synchronisation between ranks is inside the kernels (signal pads, bounded waits); between the
-compute stream and the communication stream it is CUDA events.  The path is used when the group
-is a full-shard group of CUDA ranks on one node and the parameters are bf16; anything else falls
-back to the ``torch.distributed`` buffers.
+Synchronisation between ranks is inside the kernels (signal pads, bounded waits).  A rank publishes
+a *shard version* whenever its parameter shards have been rewritten (by the fused optimizer kernel,
+or after any optimizer step); the fused gather waits for the peers' version of the current step,
+which has normally been published long before.  A shard is only rewritten after every peer's
+gradients of that module have arrived, i.e. after every peer has finished reading it.
+
+The path is used when the group is a full-shard group of CUDA ranks on one node and the parameters
+are bf16; parameters of other kinds in the same module go through the ``torch.distributed``
+buffers.
 """
 from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, Optional
+import weakref
+from typing import Dict, List, Optional
 
 import torch
+import torch.distributed as dist
 
 from ..collectives import cc
 from ..ops import native
-from .symm import DEFAULT_WAIT_NS, SymmetricMemory
+from ..utils import tracing
+from .symm import DEFAULT_WAIT_NS, SLOT_SHARD_VERSION, SymmetricMemory
 
 _COMM_STREAMS: Dict[int, torch.cuda.Stream] = {}
 # CTAs of the communication kernels.  Both are bandwidth kernels (the fused reduce-scatter + AdamW
@@ -37,6 +55,9 @@ _COMM_STREAMS: Dict[int, torch.cuda.Stream] = {}
 # need most of the machine's memory-level parallelism; they co-reside with the GEMM CTAs.
 _NUM_COMM_CTAS = int(os.environ.get("HPB_COMM_CTAS", "96"))
 _NUM_RS_CTAS = int(os.environ.get("HPB_RS_CTAS", os.environ.get("HPB_COMM_CTAS", "148")))
+_MAX_GROUPS = 4            # optimizer parameter groups per flat buffer (kernel table size)
+_LIVE: "weakref.WeakSet[SymmParamBuffer]" = weakref.WeakSet()
+_STEP_HOOK = None
 
 
 def comm_stream(device: torch.device) -> torch.cuda.Stream:
@@ -50,33 +71,93 @@ def symm_path_enabled() -> bool:
     return os.environ.get("HPB_FUSED_COMM", "1") != "0"
 
 
-def can_use(params) -> bool:
-    """All parameters: CUDA, bf16, plain tensors, fully sharded over one group of this node."""
+def fused_gather_enabled() -> bool:
+    """``HPB_FUSED_AG=0`` gathers every weight with the stand-alone copy kernel instead."""
+    return os.environ.get("HPB_FUSED_AG", "1") != "0"
+
+
+def group_ok(params) -> bool:
+    """The group as a whole can use symmetric memory (which parameters join is decided per parameter)."""
     if not symm_path_enabled() or not params or not torch.cuda.is_available():
         return False
     if not cc.is_initialized() or cc.get_backend() != "nccl":
         return False
     p0 = params[0]
-    if p0.dp_size != 1 or p0.shard_size > 16 or p0.shard_size > torch.cuda.device_count():
-        return False
-    for p in params:
-        if p.is_dtensor or p.shard.dtype != torch.bfloat16 or not p.shard.is_cuda:
-            return False
-        if p.shard.numel() % 8:
-            return False
-    return True
+    return p0.dp_size == 1 and 1 < p0.shard_size <= 16 and p0.shard_size <= torch.cuda.device_count()
+
+
+def eligible(p) -> bool:
+    """One parameter: a plain CUDA bf16 tensor whose shard is a whole number of 16-byte vectors."""
+    return (not p.is_dtensor) and p.shard.dtype == torch.bfloat16 and p.shard.is_cuda and p.shard.numel() % 8 == 0
+
+
+def split_eligible(params):
+    """``(symmetric-memory parameters, the rest)`` of one (group, dtype, device) parameter list."""
+    if not group_ok(params):
+        return [], list(params)
+    yes = [p for p in params if eligible(p)]
+    no = [p for p in params if not eligible(p)]
+    return yes, no
+
+
+def can_use(params) -> bool:
+    """Every parameter of the list can live in one symmetric buffer."""
+    yes, no = split_eligible(params)
+    return bool(yes) and not no
 
 
 def _bind(lib):
-    vp, ci, cu, cull = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_ulonglong
+    if getattr(lib, "_hpb_fused_hsdp_bound", False):
+        return lib
+    vp, ci, cu, cull, c64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_ulonglong, ctypes.c_int64
     pp = ctypes.POINTER(vp)
+    cf = ctypes.c_float
     lib.hpb_p2p_allgather.argtypes = [pp, pp, vp, ci, vp, ci, ci, cu, cull, vp, vp, ci, vp]
     lib.hpb_p2p_allgather.restype = ci
-    cf = ctypes.c_float
-    lib.hpb_fused_rs_adamw.argtypes = [pp, pp, vp, ci, vp, vp, vp, vp, cf, cf, cf, cf, cf, ci, cf, ci, ci, cu,
-                                       cull, vp, vp, ci, vp]
+    lib.hpb_fused_rs_adamw.argtypes = [pp, vp, pp, vp, ci, vp, vp, vp, vp, ctypes.POINTER(cf), ci, ci, cf, ci, ci,
+                                       cu, cu, cull, vp, vp, ci, vp]
     lib.hpb_fused_rs_adamw.restype = ci
+    lib.hpb_gemm2_agw.argtypes = [vp, c64, pp, vp, ci, c64, c64, vp, c64, ci, ci, ci, vp, vp, cu, vp, ci, cu, cull,
+                                  vp, ci, vp]
+    lib.hpb_gemm2_agw.restype = ci
+    lib._hpb_fused_hsdp_bound = True
     return lib
+
+
+class _StagingPool:
+    """Full-size weight staging buffers, shared by all wrapped modules of a device: a module takes
+    one at unshard and gives it back at reshard.  Reuse is ordered by the streams: a buffer is next
+    written either by a GEMM on the compute stream or by the gather kernel, whose stream first waits
+    for the compute stream."""
+
+    def __init__(self):
+        self.free: Dict[tuple, List[torch.Tensor]] = {}
+
+    def take(self, numel: int, device) -> torch.Tensor:
+        lst = self.free.get((device, numel))
+        if lst:
+            return lst.pop()
+        return torch.empty(numel, dtype=torch.bfloat16, device=device)
+
+    def give(self, t: torch.Tensor) -> None:
+        self.free.setdefault((t.device, t.numel()), []).append(t)
+
+
+_POOL = _StagingPool()
+
+
+def _on_optimizer_step(optimizer, args, kwargs) -> None:
+    """After ANY optimizer step: parameter shards that were rewritten outside the fused kernel get
+    their new version published."""
+    for buf in list(_LIVE):
+        buf.after_optimizer_step()
+
+
+def _install_step_hook() -> None:
+    global _STEP_HOOK
+    if _STEP_HOOK is None:
+        from torch.optim.optimizer import register_optimizer_step_post_hook
+        _STEP_HOOK = register_optimizer_step_post_hook(_on_optimizer_step)
 
 
 class SymmParamBuffer:
@@ -89,8 +170,10 @@ class SymmParamBuffer:
         self.n = p0.shard_size
         self.rank = p0.sharded_group_info.index
         self.device = p0.shard.device
+        self.level3 = level3
         self.lib = _bind(native.lib())
         numels = [p.shard.numel() for p in params]
+        self.numels = numels
         self.shard_off, self.full_off = [], []
         so = fo = 0
         for k in numels:
@@ -101,48 +184,99 @@ class SymmParamBuffer:
         self.shard_numel, self.full_numel = so, fo
         # symmetric region: [flat shard | flat full gradients]
         self.grad_byte_off = (so * 2 + 255) // 256 * 256
-        self.symm = SymmetricMemory(self.group, self.grad_byte_off + fo * 2, self.device)
+        self.symm = SymmetricMemory(self.group, self.grad_byte_off + fo * 2, self.device, multicast=True)
         self.flat_shard = self.symm.tensor(torch.bfloat16, so, 0)
         self.flat_grad = self.symm.tensor(torch.bfloat16, fo, self.grad_byte_off)
         self.shard_ptrs = self.symm.ptr_table(0)
         self.grad_ptrs = self.symm.ptr_table(self.grad_byte_off)
-        segs = torch.tensor([[f, s, k] for f, s, k in zip(self.full_off, self.shard_off, numels)],
-                            dtype=torch.int64, device=self.device)
-        self.segs = segs.contiguous()
-        self.full = torch.empty(fo, dtype=torch.bfloat16, device=self.device)
+        self.mc_grad = None if self.symm.mc_base is None else self.symm.mc_base + self.grad_byte_off
         for p, s, k in zip(params, self.shard_off, numels):
             view = self.flat_shard[s:s + k].view(p.shard_shape)
             view.copy_(p.shard)
             p.rebind_shard(view)
-        self.full_views = [self.full[f:f + k * self.n].view(p.full_shape)
-                           for p, f, k in zip(params, self.full_off, numels)]
         self.grad_views = [self.flat_grad[f:f + k * self.n].view(p.full_shape)
                            for p, f, k in zip(params, self.full_off, numels)]
+        # which parameters get their all-gather inside the consumer GEMM
+        self.fusable = [self._fusable(p) for p in params]
+        self.param_shard_ptrs = [self.symm.ptr_table(s * 2) for s in self.shard_off]
+        self.panel_cnt: List[Optional[torch.Tensor]] = []
+        for p, f in zip(params, self.fusable):
+            rows = p.full_shape[0]
+            self.panel_cnt.append(torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=self.device)
+                                  if f else None)       # last word: the work-queue head
+        self.gather_seq = [0] * len(params)
+        self.pending = [False] * len(params)
+        self._build_segments(None)
         self.status = native.status_word(self.device)
+        self.full: Optional[torch.Tensor] = None          # staging buffer while unsharded
+        self.full_views: List[Optional[torch.Tensor]] = [None] * len(params)
         self.gather_event: Optional[torch.cuda.Event] = None
         self.reduce_event: Optional[torch.cuda.Event] = None
-        self.free_event: Optional[torch.cuda.Event] = None     # compute finished with `full`
         self.grad_fresh = True        # nothing accumulated in flat_grad yet in this window
         self.ready = set()
         self.optimizer = None         # set by FusedAdamW.fuse_into_backward
         self.opt_state = None
         self.handle = None
+        self.version = 0              # parameter-shard version published to the peers
+        self._fused_step_done = False
         for i, p in enumerate(params):
             p._symm = (self, i)
+        _LIVE.add(self)
+        _install_step_hook()
+        if self.n > 1:
+            # every rank's shards are in place before anybody gathers them
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------ set-up --
+    def _fusable(self, p) -> bool:
+        """The fused gather takes 2-D weights that are only consumed by ``ops.linear`` (the model
+        marks them ``_hpb_gemm_only``) and whose shape fits the kernel's granularity."""
+        if not fused_gather_enabled() or self.n < 2 or not getattr(p.param, "_hpb_gemm_only", False):
+            return False
+        shape = p.full_shape
+        if len(shape) != 2 or shape[1] % 64 or shape[0] % self.n:
+            return False
+        shard_elems = shape[0] // self.n * shape[1]
+        return shard_elems % 8 == 0 and shard_elems >= 8192 and shape[0] >= 256 and shape[1] >= 64
+
+    def _build_segments(self, group_index) -> None:
+        """Segment tables: all parameters (optimizer kernel) and the non-fusable ones (copy kernel)."""
+        gi = group_index or [0] * len(self.params)
+        rows = [[f, s, k, g] for f, s, k, g in zip(self.full_off, self.shard_off, self.numels, gi)]
+        self.segs = torch.tensor(rows, dtype=torch.int64, device=self.device).contiguous()
+        rest = [r for r, fz in zip(rows, self.fusable) if not fz]
+        self.num_rest = len(rest)
+        self.segs_rest = (torch.tensor(rest, dtype=torch.int64, device=self.device).contiguous()
+                          if rest else None)
+
+    def set_param_groups(self, group_index: List[int]) -> None:
+        """``group_index[i]``: row of the hyper-parameter table used for parameter ``i``."""
+        self._build_segments(group_index)
 
     # ------------------------------------------------------------- all-gather --
+    def _take_staging(self) -> None:
+        if self.full is None:
+            self.full = _POOL.take(self.full_numel, self.device)
+            self.full_views = [self.full[f:f + k * self.n].view(p.full_shape)
+                               for p, f, k in zip(self.params, self.full_off, self.numels)]
+
     def prefetch(self) -> None:
+        """Start gathering what the consumer GEMMs will not gather themselves."""
         if self.gather_event is not None or not self.params[0].is_sharded_now:
+            return
+        self._take_staging()
+        if self.num_rest == 0:
             return
         cs = comm_stream(self.device)
         cur = torch.cuda.current_stream(self.device)
         ev = torch.cuda.Event()
         ev.record(cur)
-        cs.wait_event(ev)                       # everything that read `full` before is finished
-        with torch.cuda.stream(cs):
+        cs.wait_event(ev)                       # everything that read the staging buffer before is finished
+        with torch.cuda.stream(cs), tracing.nvtx_range("hpb.hsdp.allgather"):
             ep = self.symm.next_epoch()
-            rc = self.lib.hpb_p2p_allgather(self.shard_ptrs, self.symm.pad_ptrs, self.segs.data_ptr(),
-                                            len(self.params), self.full.data_ptr(), self.rank, self.n, ep,
+            rc = self.lib.hpb_p2p_allgather(self.shard_ptrs, self.symm.pad_ptrs, self.segs_rest.data_ptr(),
+                                            self.num_rest, self.full.data_ptr(), self.rank, self.n, ep,
                                             DEFAULT_WAIT_NS, self.status.data_ptr(),
                                             self.symm.done_counter.data_ptr(), _NUM_COMM_CTAS, cs.cuda_stream)
             native.check(rc, "hpb_p2p_allgather")
@@ -154,15 +288,62 @@ class SymmParamBuffer:
             return
         if self.gather_event is None:
             self.prefetch()
-        torch.cuda.current_stream(self.device).wait_event(self.gather_event)
-        self.gather_event = None
-        for p, v in zip(self.params, self.full_views):
+        if self.gather_event is not None:
+            torch.cuda.current_stream(self.device).wait_event(self.gather_event)
+            self.gather_event = None
+        for i, (p, v) in enumerate(zip(self.params, self.full_views)):
             p.leaf.data = v
             p.is_sharded_now = False
+            self.pending[i] = self.fusable[i]
 
     def reshard(self) -> None:
         for p in self.params:
             p.to_sharded()
+        self.release_staging()
+
+    def release_staging(self) -> None:
+        """Hand the staging buffer back (the parameters point at their shards again)."""
+        if self.full is not None and self.gather_event is None and all(p.is_sharded_now for p in self.params):
+            _POOL.give(self.full)
+            self.full = None
+            self.full_views = [None] * len(self.params)
+            self.pending = [False] * len(self.params)
+
+    def gather_pending(self, i: int) -> bool:
+        return self.pending[i]
+
+    def gather_gemm(self, i: int, a: torch.Tensor, out: torch.Tensor, w_mn: bool) -> None:
+        """``out = a @ W_i^T`` (``w_mn=False``) or ``out = a @ W_i`` (``w_mn=True``) where the full
+        ``W_i`` is gathered from the peers inside the GEMM kernel; afterwards the parameter's full
+        view holds the whole weight for any later consumer."""
+        p = self.params[i]
+        rows, cols = p.full_shape
+        if a.stride(-1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
+            a = a.contiguous()
+        cnt = self.panel_cnt[i]
+        self.gather_seq[i] += 1
+        with tracing.nvtx_range("hpb.hsdp.allgather_gemm"):
+            rc = self.lib.hpb_gemm2_agw(
+                a.data_ptr(), a.stride(0), self.param_shard_ptrs[i], self.full_views[i].data_ptr(), int(w_mn),
+                rows, cols, out.data_ptr(), out.stride(0), a.shape[0], self.n, self.rank, cnt.data_ptr(),
+                cnt.data_ptr() + 4 * (cnt.numel() - 1), self.gather_seq[i],
+                self.symm.pad_ptrs[self.rank], SLOT_SHARD_VERSION, self.version, DEFAULT_WAIT_NS,
+                self.status.data_ptr(), native.sm_count(self.device), native.stream(self.device))
+        native.check(rc, "hpb_gemm2_agw")
+        self.pending[i] = False
+
+    def materialize(self, i: int) -> None:
+        """Gather parameter ``i`` now with the copy kernel (a consumer that is not ``ops.linear``)."""
+        if not self.pending[i]:
+            return
+        seg = self.segs[i:i + 1].contiguous()
+        ep = self.symm.next_epoch()
+        rc = self.lib.hpb_p2p_allgather(self.shard_ptrs, self.symm.pad_ptrs, seg.data_ptr(), 1,
+                                        self.full.data_ptr(), self.rank, self.n, ep, DEFAULT_WAIT_NS,
+                                        self.status.data_ptr(), self.symm.done_counter.data_ptr(),
+                                        _NUM_COMM_CTAS, native.stream(self.device))
+        native.check(rc, "hpb_p2p_allgather")
+        self.pending[i] = False
 
     # ------------------------------------------------------------------ grads --
     def wgrad_target(self, i: int):
@@ -173,9 +354,12 @@ class SymmParamBuffer:
             self.reduce_event = None
         return self.grad_views[i], (not self.grad_fresh) or (i in self.ready)
 
+    def num_grad_params(self) -> int:
+        return sum(1 for p in self.params if p.param.requires_grad)
+
     def mark_ready(self, i: int) -> bool:
         self.ready.add(i)
-        return len(self.ready) == sum(1 for p in self.params if p.param.requires_grad)
+        return len(self.ready) == self.num_grad_params()
 
     def store_grad(self, i: int, grad: torch.Tensor) -> bool:
         """Copy (or accumulate) an autograd-produced gradient into the flat buffer."""
@@ -185,6 +369,21 @@ class SymmParamBuffer:
         else:
             view.copy_(grad.view_as(view))
         return self.mark_ready(i)
+
+    def flush_missing(self) -> bool:
+        """End of a backward pass in which some parameters of this buffer received no gradient (an
+        unused branch): their slots are zero-filled -- on every rank alike, so the ranks' kernels
+        stay matched -- and the buffer counts as complete.  Returns True when there was anything to
+        flush."""
+        if not self.ready or len(self.ready) == self.num_grad_params():
+            return False
+        for i, p in enumerate(self.params):
+            if p.param.requires_grad and i not in self.ready:
+                view, acc = self.wgrad_target(i)
+                if not acc:
+                    view.zero_()
+                self.ready.add(i)
+        return True
 
     def reduce_and_step(self, sync: bool, grad_scale: float) -> bool:
         """All gradients of this state are in ``flat_grad``.  On a sync step launch the fused
@@ -197,18 +396,20 @@ class SymmParamBuffer:
         if opt is None:
             return False
         st = opt.flat_state_for(self)
-        g = opt.group_for(self)
+        hyper = opt.hyper_table_for(self)
         cs = comm_stream(self.device)
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(self.device))
         cs.wait_event(ev)
-        with torch.cuda.stream(cs):
+        with torch.cuda.stream(cs), tracing.nvtx_range("hpb.hsdp.reduce_scatter_adamw"):
             ep = self.symm.next_epoch()
+            self.version += 1
+            self._fused_step_done = True
             rc = self.lib.hpb_fused_rs_adamw(
-                self.grad_ptrs, self.symm.pad_ptrs, self.segs.data_ptr(), len(self.params),
+                self.grad_ptrs, self.mc_grad, self.symm.pad_ptrs, self.segs.data_ptr(), len(self.params),
                 st["master"].data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(),
-                self.flat_shard.data_ptr(), g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
-                opt._step_count + 1, grad_scale, self.rank, self.n, ep, DEFAULT_WAIT_NS, self.status.data_ptr(),
+                self.flat_shard.data_ptr(), hyper, len(hyper) // 5, opt._step_count + 1, grad_scale, self.rank,
+                self.n, ep, self.version, DEFAULT_WAIT_NS, self.status.data_ptr(),
                 self.symm.done_counter.data_ptr() + 8, _NUM_RS_CTAS, cs.cuda_stream)
             native.check(rc, "hpb_fused_rs_adamw")
             self.reduce_event = torch.cuda.Event()
@@ -220,3 +421,20 @@ class SymmParamBuffer:
         if self.reduce_event is not None:
             torch.cuda.current_stream(self.device).wait_event(self.reduce_event)
             self.reduce_event = None
+
+    # --------------------------------------------------------------- versions --
+    def after_optimizer_step(self) -> None:
+        """Runs after every optimizer step.  If the fused kernel rewrote the shards in this step it
+        has published the new version itself; otherwise (an optimizer that writes the shards with
+        its own kernels) publish it now, ordered after those kernels on the current stream."""
+        if self._fused_step_done:
+            self._fused_step_done = False
+            return
+        self.params_written()
+
+    def params_written(self) -> None:
+        """The shards of this buffer were rewritten on the current stream (optimizer step, state-dict
+        load): publish a new version.  Every rank must call it the same number of times."""
+        self.version += 1
+        if self.n > 1:
+            self.symm.signal(SLOT_SHARD_VERSION, self.version)

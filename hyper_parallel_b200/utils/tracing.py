@@ -15,9 +15,15 @@ import torch
 from torch import nn
 
 
+_NVTX = None
+
+
 @contextlib.contextmanager
 def nvtx_range(name: str):
-    if torch.cuda.is_available():
+    global _NVTX
+    if _NVTX is None:
+        _NVTX = torch.cuda.is_available()
+    if _NVTX:
         torch.cuda.nvtx.range_push(name)
         try:
             yield

@@ -393,3 +393,43 @@ def test_flash_attention_score_kernel_path(fmt, mode):
     assert torch.allclose(smax[..., 0] + ssum[..., 0].log(), rmax[..., 0] + rsum[..., 0].log(), atol=2e-2)
     for a, b in ((qa, qb), (ka, kb), (va, vb)):
         assert torch.allclose(a.grad.float(), b.grad, atol=6e-2, rtol=6e-2)
+
+
+@pytest.mark.parametrize("w_mn", [False, True])
+@pytest.mark.parametrize("M,rows,cols,n", [(512, 1024, 512, 2), (300, 1536, 320, 4), (1024, 2016, 256, 8),
+                                           (2048, 4096, 1024, 8)])
+def test_gemm_with_fused_weight_allgather_emulated_ranks(M, rows, cols, n, w_mn):
+    """The weight all-gather fused into the GEMM, with the n ranks emulated on one GPU: the "peer"
+    shards are n separate local tensors, so the panel / chunk / rotation arithmetic of every rank
+    is checked against the fp32 product and the staging matrix against the full weight.  Two
+    launches per rank exercise the per-weight counters that only grow."""
+    import ctypes
+    from hyper_parallel_b200.parallel import fused_hsdp
+    lib = fused_hsdp._bind(native.lib())
+    torch.manual_seed(3)
+    dev = _dev()
+    w = (torch.randn(rows, cols, device=dev, dtype=torch.bfloat16) * 0.1)
+    shards = [c.clone() for c in w.chunk(n, dim=0)]
+    K = rows if w_mn else cols
+    N = cols if w_mn else rows
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    ref = a.float() @ (w.float() if w_mn else w.float().t())
+    ptrs = (ctypes.c_void_p * n)(*[s.data_ptr() for s in shards])
+    pad = torch.zeros(1024, dtype=torch.int32, device=dev)      # version flags: all zero, version 0
+    st = native.status_word(dev)
+    for rank in range(n):
+        staging = torch.full((rows, cols), float("nan"), device=dev, dtype=torch.bfloat16)
+        cnt = torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=dev)
+        for seq in (1, 2):
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            if seq == 2:
+                staging.fill_(float("nan"))
+            rc = lib.hpb_gemm2_agw(a.data_ptr(), a.stride(0), ptrs, staging.data_ptr(), int(w_mn), rows, cols,
+                                   out.data_ptr(), out.stride(0), M, n, rank, cnt.data_ptr(),
+                                   cnt.data_ptr() + 4 * (cnt.numel() - 1), seq, pad.data_ptr(), 4, 0,
+                                   2_000_000_000, st.data_ptr(), native.sm_count(dev), native.stream(dev))
+            assert rc == 0, rc
+            native.check_status()
+            assert torch.equal(staging, w), (rank, seq)
+            assert _rel_err(out, ref) < 5e-3, (rank, seq)
+            assert int(cnt[-1].item()) == 0          # the work queue is idle again
