@@ -130,7 +130,7 @@ def main():
         w_shard = sm.tensor(torch.bfloat16, shard_rows * cols, 0).view(shard_rows, cols)
         w_shard.normal_(0, 0.02)
         staging = torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
-        cnt = torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=dev)
+        cnt = torch.zeros((rows + 127) // 128 + 2, dtype=torch.int32, device=dev)
         K, N = (rows, cols) if w_mn else (cols, rows)
         a = torch.randn(T, K, device=dev, dtype=torch.bfloat16)
         y = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
@@ -141,8 +141,7 @@ def main():
         def fused():
             seq[0] += 1
             native.check(lib.hpb_gemm2_agw(a.data_ptr(), a.stride(0), sm.ptrs, staging.data_ptr(), int(w_mn), rows,
-                                           cols, y.data_ptr(), y.stride(0), T, n, rank, cnt.data_ptr(),
-                                           cnt.data_ptr() + 4 * (cnt.numel() - 1), seq[0], sm.pad_ptrs[rank],
+                                           cols, y.data_ptr(), y.stride(0), T, n, rank, cnt.data_ptr(), seq[0], sm.pad_ptrs[rank],
                                            SLOT_SHARD_VERSION, 0, DEFAULT_WAIT_NS, status.data_ptr(),
                                            native.sm_count(dev), stream), "hpb_gemm2_agw")
 

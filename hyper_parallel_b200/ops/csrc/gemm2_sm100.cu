@@ -17,6 +17,8 @@
 // Operand loads are plain per-CTA TMA copies.  Every wait is bounded (see sm100_common.cuh).
 #include "sm100_common.cuh"
 
+#include <stdlib.h>
+
 namespace hpb {
 namespace g2 {
 
@@ -390,10 +392,14 @@ struct GatherParams {
   const uint32_t* my_pad;     // this rank's signal pad (null: single rank / versions not used)
   uint4* staging;             // local full weight [rows, row_elems], contiguous
   unsigned* panel_cnt;        // [num_panels] chunk counters, grow by the panel's chunk count per launch
+  unsigned* done_total;       // chunks copied so far over all launches (grows by num_chunks per launch)
+  int num_panels;
   unsigned* claim;            // work-queue head; zero between launches (the last claimer resets it)
   long long shard_elems;      // elements per rank
   long long total_vecs;       // n * shard_elems / 8
-  long long panel_vecs;       // 128 * row_elems / 8 (a multiple of kChunkVecs)
+  long long panel_vecs;       // 128 * row_elems / 8 (a multiple of chunk_vecs)
+  int chunk_vecs;             // 16-byte vectors per work-queue item: 1024 or 2048
+  int group_m;                // m blocks per raster group (forward: how fast the sweep over W is)
   int n, rank;
   int first_unit;             // forward: first n block of the rotation; dgrad: first k block
   int first_chunk;            // first chunk of the copy order (the chunk that holds my first element)
@@ -404,7 +410,7 @@ struct GatherParams {
 };
 
 constexpr int kCommThreads = 128;
-constexpr int kChunkVecs = 1024;               // 16 KB
+constexpr int kMaxChunkVecs = 2048;            // 32 KB: 16 independent 16-byte loads per thread in flight
 constexpr int THREADS_G = THREADS + kCommThreads;
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -417,13 +423,19 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ unsigned ld_relaxed_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 // the staging rows were written with generic-proxy stores; TMA reads through the async proxy
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ unsigned panel_chunks(const GatherParams& g, int panel) {
   const long long left = g.total_vecs - static_cast<long long>(panel) * g.panel_vecs;
   const long long v = left < g.panel_vecs ? left : g.panel_vecs;
-  return v <= 0 ? 0u : static_cast<unsigned>((v + kChunkVecs - 1) / kChunkVecs);
+  return v <= 0 ? 0u : static_cast<unsigned>((v + g.chunk_vecs - 1) / g.chunk_vecs);
 }
 
 // Bounded wait until panel `panel` of the staging matrix is complete.
@@ -444,6 +456,16 @@ __device__ __forceinline__ bool wait_panel(const GatherParams& g, int panel, vol
     }
   }
   return true;
+}
+
+__device__ __forceinline__ void tile_coords_g(int t, int num_m, int num_n, int group_m, int& m_blk, int& n_blk) {
+  const int per_group = group_m * num_n;
+  const int group = t / per_group;
+  const int first_m = group * group_m;
+  const int gsz = min(num_m - first_m, group_m);
+  const int r = t - group * per_group;
+  m_blk = first_m + r % gsz;
+  n_blk = r / gsz;
 }
 
 template <bool B_MN>
@@ -505,16 +527,35 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       int have_panel = -1;
+      int ahead = 0;
+      // Readiness checks are kept off the producer's critical path.  (1) `done_total` says when the
+      // WHOLE weight has arrived: its value is fetched with a relaxed load one tile ahead (the load
+      // is in flight while the tile's TMA copies are issued) and, once it has reached the target,
+      // one acquire fence + one proxy fence make every later check unnecessary.  (2) Until then a
+      // forward tile waits for its own panel, and a dgrad tile, which sweeps all panels, checks
+      // them eight at a time (eight loads in one round trip instead of one round trip each).
+      bool all_ready = false;
+      const unsigned total_target = g.seq * static_cast<unsigned>((g.total_vecs + g.chunk_vecs - 1) / g.chunk_vecs);
+      unsigned seen_total = ld_relaxed_gpu_u32(g.done_total);
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int m_blk, n_blk;
-        tile_coords(t, num_m, num_n, m_blk, n_blk);
+        tile_coords_g(t, num_m, num_n, g.group_m, m_blk, n_blk);
         n_blk += n_rot;
         if (n_blk >= num_n) n_blk -= num_n;
         const int m0 = m_blk * TILE_M + cta * CTA_M;
         const int n0 = n_blk * TILE_N + cta * CTA_NB;
+        if (!all_ready) {
+          if (static_cast<int>(seen_total - total_target) >= 0) {
+            fence_acq_rel_gpu();
+            fence_proxy_async_all();
+            all_ready = true;
+          } else {
+            seen_total = ld_relaxed_gpu_u32(g.done_total);      // consumed at the next tile
+          }
+        }
         if constexpr (!B_MN) {
           // my 128 rows of W are exactly one panel
-          if (n0 < p.N) {
+          if (!all_ready && n0 < p.N) {
             ok = wait_panel(g, n0 >> 7, abort_flag, p.status);
             if (!ok) break;
             fence_proxy_async_all();
@@ -526,11 +567,19 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int k0 = kr * BLOCK_K;
           if constexpr (B_MN) {
             const int panel = k0 >> 7;
-            if (panel != have_panel) {
-              ok = wait_panel(g, panel, abort_flag, p.status);
-              if (!ok) break;
-              fence_proxy_async_all();
+            if (!all_ready && panel != have_panel) {
               have_panel = panel;
+              if (ahead == 0) {
+                for (int j = 0; j < 8 && ok; ++j) {
+                  int pj = panel + j;
+                  if (pj >= g.num_panels) pj -= g.num_panels;
+                  ok = wait_panel(g, pj, abort_flag, p.status);
+                }
+                if (!ok) break;
+                fence_proxy_async_all();
+                ahead = 8;
+              }
+              --ahead;
             }
           }
           ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier,
@@ -549,6 +598,7 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+        if (B_MN && ok) all_ready = true;       // a dgrad tile has swept (and checked) every panel
       }
     }
   } else if (warp == 1) {
@@ -599,7 +649,7 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local_tile) {
       int m_blk, n_blk;
-      tile_coords(t, num_m, num_n, m_blk, n_blk);
+      tile_coords_g(t, num_m, num_n, g.group_m, m_blk, n_blk);
       n_blk += n_rot;
       if (n_blk >= num_n) n_blk -= num_n;
       const int buf = local_tile & 1;
@@ -643,7 +693,8 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ------------------------------------------- communication warps: gather the weight --
     const int ct = threadIdx.x - 6 * 32;                  // 0 .. kCommThreads-1
-    const unsigned num_chunks = static_cast<unsigned>((g.total_vecs + kChunkVecs - 1) / kChunkVecs);
+    const int cv = g.chunk_vecs;
+    const unsigned num_chunks = static_cast<unsigned>((g.total_vecs + cv - 1) / cv);
     unsigned verified = 1u << g.rank;                     // peers whose shard version has been seen
     for (;;) {
       if (ct == 0) {
@@ -654,8 +705,8 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (cc >= num_chunks) cc -= num_chunks;
           c = static_cast<int>(cc);
           if (g.my_pad != nullptr) {
-            const long long e0 = static_cast<long long>(cc) * kChunkVecs * 8;
-            const long long e1 = min(e0 + kChunkVecs * 8, g.total_vecs * 8) - 1;
+            const long long e0 = static_cast<long long>(cc) * cv * 8;
+            const long long e1 = min(e0 + static_cast<long long>(cv) * 8, g.total_vecs * 8) - 1;
             const int o0 = static_cast<int>(e0 / g.shard_elems), o1 = static_cast<int>(e1 / g.shard_elems);
             for (int o = o0; o <= o1 && c >= 0; ++o) {
               if (verified & (1u << o)) continue;
@@ -682,15 +733,16 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int c = *s_chunk;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (c < 0) break;
-      const long long v0 = static_cast<long long>(c) * kChunkVecs;
+      const long long v0 = static_cast<long long>(c) * cv;
       const long long e0 = v0 * 8;
       const int o0 = static_cast<int>(e0 / g.shard_elems);
       const long long bnd = static_cast<long long>(o0 + 1) * g.shard_elems;
-      uint4 buf[kChunkVecs / kCommThreads];
+      const long long v_end = min(v0 + cv, g.total_vecs);
+      uint4 buf[kMaxChunkVecs / kCommThreads];
 #pragma unroll
-      for (int u = 0; u < kChunkVecs / kCommThreads; ++u) {
+      for (int u = 0; u < kMaxChunkVecs / kCommThreads; ++u) {
         const long long v = v0 + ct + u * kCommThreads;
-        if (v < g.total_vecs) {
+        if (v < v_end) {
           const long long e = v * 8;
           const int o = o0 + (e >= bnd ? 1 : 0);
           buf[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g.shard[o]) +
@@ -698,15 +750,16 @@ gemm2_agw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
 #pragma unroll
-      for (int u = 0; u < kChunkVecs / kCommThreads; ++u) {
+      for (int u = 0; u < kMaxChunkVecs / kCommThreads; ++u) {
         const long long v = v0 + ct + u * kCommThreads;
-        if (v < g.total_vecs) g.staging[v] = buf[u];
+        if (v < v_end) g.staging[v] = buf[u];
       }
       __threadfence();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (ct == 0) {
         __threadfence();
         atomicAdd(g.panel_cnt + static_cast<int>(v0 / g.panel_vecs), 1u);
+        atomicAdd(g.done_total, 1u);
       }
     }
   }
@@ -809,14 +862,15 @@ extern "C" int hpb_gemm2_bf16(const void* A, int a_mn, int64_t lda, const void* 
 //   w_mn = 1 : C[M, N] = A[M, K] * W,    W = [K, N]   (dgrad; W rows are the contraction)
 // shard_ptrs: n device pointers, rank r's shard of W (w_rows / n rows of w_cols elements each);
 // staging: local [w_rows, w_cols] bf16 that receives the gathered weight (it holds all of W when
-// the kernel returns); panel_cnt: [ceil(w_rows / 128)] counters and claim: [1] word, both zeroed
-// once at allocation and owned by this weight; seq: 1, 2, ... per launch on this weight.
+// the kernel returns); counters: ceil(w_rows / 128) + 2 words (per-panel chunk counters, the
+// total, the work-queue head), zeroed once at allocation and owned by this weight; seq: 1, 2, ...
+// per launch on this weight.
 // my_pad / version_slot / version: the peers' "shard version" flags to wait for (my_pad may be
 // null: no wait).  Returns -6 when the shape does not meet the kernel's granularity rules
-// (w_cols % 64, shard_elems % 8, shard_elems >= 8192); the caller then gathers separately.
+// (w_cols % 64, shard_elems % 8, shard_elems >= 16384); the caller then gathers separately.
 extern "C" int hpb_gemm2_agw(const void* A, int64_t lda, void* const* shard_ptrs, void* staging, int w_mn,
                              int64_t w_rows, int64_t w_cols, void* C, int64_t ldc, int M, int n, int rank,
-                             unsigned* panel_cnt, unsigned* claim, unsigned seq, const void* my_pad,
+                             unsigned* counters, unsigned seq, const void* my_pad,
                              int version_slot, unsigned version, unsigned long long limit_ns, int* status,
                              int num_sms, cudaStream_t stream) {
   using namespace hpb;
@@ -825,7 +879,7 @@ extern "C" int hpb_gemm2_agw(const void* A, int64_t lda, void* const* shard_ptrs
   if ((lda % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(staging) & 15)) return -2;
   if ((w_rows % n) || (w_cols % 64)) return -6;
   const long long shard_elems = (w_rows / n) * w_cols;
-  if ((shard_elems % 8) || shard_elems < 8192 || w_rows * w_cols / 8 / kChunkVecs > 0x7fffffffLL) return -6;
+  if ((shard_elems % 8) || shard_elems < 8 * kMaxChunkVecs || w_rows * w_cols / 8 / 1024 > 0x7fffffffLL) return -6;
   const int N = w_mn ? static_cast<int>(w_cols) : static_cast<int>(w_rows);
   const int K = w_mn ? static_cast<int>(w_rows) : static_cast<int>(w_cols);
   cudaFree(nullptr);
@@ -840,8 +894,10 @@ extern "C" int hpb_gemm2_agw(const void* A, int64_t lda, void* const* shard_ptrs
   for (int i = 0; i < 16; ++i) g.shard[i] = i < n ? shard_ptrs[i] : nullptr;
   g.my_pad = n > 1 ? reinterpret_cast<const uint32_t*>(my_pad) : nullptr;
   g.staging = reinterpret_cast<uint4*>(staging);
-  g.panel_cnt = panel_cnt;
-  g.claim = claim;
+  g.num_panels = static_cast<int>((w_rows + 127) / 128);
+  g.panel_cnt = counters;
+  g.done_total = counters + g.num_panels;
+  g.claim = counters + g.num_panels + 1;
   g.shard_elems = shard_elems;
   g.total_vecs = w_rows * w_cols / 8;
   g.panel_vecs = 128 * w_cols / 8;
@@ -855,7 +911,21 @@ extern "C" int hpb_gemm2_agw(const void* A, int64_t lda, void* const* shard_ptrs
     const int num_k = (K + BLOCK_K - 1) / BLOCK_K;
     g.first_unit = static_cast<int>(((my_row0 + BLOCK_K - 1) / BLOCK_K) % num_k);
   }
-  g.first_chunk = static_cast<int>(static_cast<long long>(rank) * shard_elems / 8 / kChunkVecs);
+  g.chunk_vecs = (w_cols % 128 == 0) ? 2048 : 1024;       // a chunk never straddles two panels
+  g.first_chunk = static_cast<int>(static_cast<long long>(rank) * shard_elems / 8 / g.chunk_vecs);
+  // Forward: a raster group of `group_m` row blocks sweeps all of W once, so the gather has
+  // group_m / num_m of the kernel's duration to deliver it: 16 row blocks instead of the 8 of the
+  // plain kernel (measured: a full-height group loses more to L2 misses on A than it gains).
+  {
+    const int num_m = (M + TILE_M - 1) / TILE_M;
+    int gm = 2 * GROUP_M;
+    if (gm > num_m) gm = num_m;
+    g.group_m = w_mn ? GROUP_M : gm;
+    if (const char* e = getenv("HPB_AGW_GROUP_M")) {       // tuning override
+      const int v = atoi(e);
+      if (v > 0) g.group_m = v;
+    }
+  }
   g.seq = seq;
   g.version = version;
   g.version_slot = version_slot;

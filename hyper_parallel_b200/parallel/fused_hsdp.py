@@ -117,7 +117,7 @@ def _bind(lib):
     lib.hpb_fused_rs_adamw.argtypes = [pp, vp, pp, vp, ci, vp, vp, vp, vp, ctypes.POINTER(cf), ci, ci, cf, ci, ci,
                                        cu, cu, cull, vp, vp, ci, vp]
     lib.hpb_fused_rs_adamw.restype = ci
-    lib.hpb_gemm2_agw.argtypes = [vp, c64, pp, vp, ci, c64, c64, vp, c64, ci, ci, ci, vp, vp, cu, vp, ci, cu, cull,
+    lib.hpb_gemm2_agw.argtypes = [vp, c64, pp, vp, ci, c64, c64, vp, c64, ci, ci, ci, vp, cu, vp, ci, cu, cull,
                                   vp, ci, vp]
     lib.hpb_gemm2_agw.restype = ci
     lib._hpb_fused_hsdp_bound = True
@@ -202,8 +202,9 @@ class SymmParamBuffer:
         self.panel_cnt: List[Optional[torch.Tensor]] = []
         for p, f in zip(params, self.fusable):
             rows = p.full_shape[0]
-            self.panel_cnt.append(torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=self.device)
-                                  if f else None)       # last word: the work-queue head
+            # per-panel chunk counters, then the total, then the work-queue head
+            self.panel_cnt.append(torch.zeros((rows + 127) // 128 + 2, dtype=torch.int32, device=self.device)
+                                  if f else None)
         self.gather_seq = [0] * len(params)
         self.pending = [False] * len(params)
         self._build_segments(None)
@@ -238,7 +239,7 @@ class SymmParamBuffer:
         if len(shape) != 2 or shape[1] % 64 or shape[0] % self.n:
             return False
         shard_elems = shape[0] // self.n * shape[1]
-        return shard_elems % 8 == 0 and shard_elems >= 8192 and shape[0] >= 256 and shape[1] >= 64
+        return shard_elems % 8 == 0 and shard_elems >= 16384 and shape[0] >= 256 and shape[1] >= 64
 
     def _build_segments(self, group_index) -> None:
         """Segment tables: all parameters (optimizer kernel) and the non-fusable ones (copy kernel)."""
@@ -326,7 +327,7 @@ class SymmParamBuffer:
             rc = self.lib.hpb_gemm2_agw(
                 a.data_ptr(), a.stride(0), self.param_shard_ptrs[i], self.full_views[i].data_ptr(), int(w_mn),
                 rows, cols, out.data_ptr(), out.stride(0), a.shape[0], self.n, self.rank, cnt.data_ptr(),
-                cnt.data_ptr() + 4 * (cnt.numel() - 1), self.gather_seq[i],
+                self.gather_seq[i],
                 self.symm.pad_ptrs[self.rank], SLOT_SHARD_VERSION, self.version, DEFAULT_WAIT_NS,
                 self.status.data_ptr(), native.sm_count(self.device), native.stream(self.device))
         native.check(rc, "hpb_gemm2_agw")

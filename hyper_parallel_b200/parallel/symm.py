@@ -25,6 +25,7 @@ and the object degenerates to a plain local buffer.
 """
 from __future__ import annotations
 
+import array
 import ctypes
 import os
 import socket
@@ -95,6 +96,16 @@ def nvls_enabled() -> bool:
     return os.environ.get("HPB_NVLS", "1") != "0"
 
 
+_NOTES: List[str] = []        # why a VMM / multicast set-up step fell back (first few, for diagnostics)
+
+
+def _note(msg: str) -> None:
+    if len(_NOTES) < 16:
+        _NOTES.append(msg)
+    if os.environ.get("HPB_SYMM_DEBUG", "0") == "1":
+        print(f"[hpb symm] {msg}", flush=True)
+
+
 def _all_agree(group, ok: bool) -> bool:
     """True only when every rank of the group reports success (keeps the ranks on one code path)."""
     flags = [None] * cc.group_size(group)
@@ -117,11 +128,16 @@ class _FdExchange:
         dist.all_gather_object(names, self.name, group=group)      # every socket is bound after this
         self.names = names
 
+    def _send(self, fd: int, dst: int) -> None:
+        # sendmsg with an explicit address: the socket is unconnected (socket.send_fds drops the address)
+        self.sock.sendmsg([self.rank.to_bytes(4, "little")],
+                          [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", [fd]))], 0, self.names[dst])
+
     def all_to_all(self, fd: int) -> List[int]:
         """Every rank sends ``fd`` to every peer; returns the received descriptors by source rank."""
         for r in range(self.world):
             if r != self.rank:
-                socket.send_fds(self.sock, [self.rank.to_bytes(4, "little")], [fd], 0, self.names[r])
+                self._send(fd, r)
         out = [-1] * self.world
         for _ in range(self.world - 1):
             msg, fds, _flags, _addr = socket.recv_fds(self.sock, 16, 1)
@@ -133,7 +149,7 @@ class _FdExchange:
         if self.rank == src:
             for r in range(self.world):
                 if r != src:
-                    socket.send_fds(self.sock, [src.to_bytes(4, "little")], [fd], 0, self.names[r])
+                    self._send(fd, r)
             return fd
         _msg, fds, _flags, _addr = socket.recv_fds(self.sock, 16, 1)
         return fds[0]
@@ -206,14 +222,20 @@ class SymmetricMemory:
         gran = ctypes.c_size_t(0)
         with torch.cuda.device(self.device):
             vmm, mc = ctypes.c_int(0), ctypes.c_int(0)
-            ok = lib.hpb_vmm_supported(ctypes.byref(vmm), ctypes.byref(mc)) == 0 and vmm.value == 1
+            rc = lib.hpb_vmm_supported(ctypes.byref(vmm), ctypes.byref(mc))
+            ok = rc == 0 and vmm.value == 1
+            if not ok:
+                _note(f"vmm_supported rc={rc} vmm={vmm.value} multicast={mc.value}")
             use_mc = multicast and mc.value == 1
             flags = [None] * self.world
             dist.all_gather_object(flags, (ok, use_mc), group=self.group)
             if not all(f[0] for f in flags):
                 return None
             use_mc = all(f[1] for f in flags)
-            ok = lib.hpb_vmm_granularity(self.world, int(use_mc), ctypes.byref(gran)) == 0
+            rc = lib.hpb_vmm_granularity(self.world, int(use_mc), ctypes.byref(gran))
+            ok = rc == 0
+            if not ok:
+                _note(f"vmm_granularity rc={rc}")
             if not _all_agree(self.group, ok):
                 return None
             g = gran.value
@@ -222,6 +244,8 @@ class SymmetricMemory:
             rc = lib.hpb_vmm_alloc(size, g, ctypes.byref(ptr), ctypes.byref(handle), ctypes.byref(fd))
             if rc == 0:
                 self._vmm_maps.append((ptr.value, size, handle.value))
+            else:
+                _note(f"vmm_alloc({size}, gran {g}) rc={rc}")
             if not _all_agree(self.group, rc == 0):
                 self._release_vmm()
                 return None
@@ -239,8 +263,11 @@ class SymmetricMemory:
                     if rc == 0:
                         self._vmm_maps.append((p.value, size, h.value))
                         peer_bases[r] = p.value
-            except OSError:
+            except OSError as e:
+                _note(f"fd exchange failed: {e!r}")
                 rc = -1
+            if rc != 0:
+                _note(f"vmm_import rc={rc}")
             if not _all_agree(self.group, rc == 0):
                 os.close(fd.value)
                 ex.close()
@@ -262,6 +289,8 @@ class SymmetricMemory:
         rc = 0
         if self.rank == 0:
             rc = lib.hpb_mc_create(self.world, size, ctypes.byref(mc), ctypes.byref(fd))
+        if rc != 0:
+            _note(f"mc_create rc={rc}")
         ok0 = [rc == 0]
         dist.broadcast_object_list(ok0, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
                                    group=self.group)
@@ -272,16 +301,21 @@ class SymmetricMemory:
             if self.rank != 0:
                 rc = lib.hpb_mc_import(got, ctypes.byref(mc))
             os.close(got)
-        except OSError:
+        except OSError as e:
+            _note(f"multicast fd exchange failed: {e!r}")
             rc = -1
         if rc == 0:
             rc = lib.hpb_mc_add_device(mc.value)
+        if rc != 0:
+            _note(f"mc_import / mc_add_device rc={rc}")
         if not _all_agree(self.group, rc == 0):     # also the barrier "every device was added"
             return
         mc_ptr = ctypes.c_void_p()
         rc = lib.hpb_mc_bind_map(mc.value, mem_handle, size, gran, ctypes.byref(mc_ptr))
         if rc == 0:
             self._mc = (mc.value, mc_ptr.value, size)
+        else:
+            _note(f"mc_bind_map rc={rc}")
         if _all_agree(self.group, rc == 0):
             self.mc_base = mc_ptr.value
         elif self._mc is not None:

@@ -417,19 +417,20 @@ def test_gemm_with_fused_weight_allgather_emulated_ranks(M, rows, cols, n, w_mn)
     ptrs = (ctypes.c_void_p * n)(*[s.data_ptr() for s in shards])
     pad = torch.zeros(1024, dtype=torch.int32, device=dev)      # version flags: all zero, version 0
     st = native.status_word(dev)
+    cv = 2048 if cols % 128 == 0 else 1024          # 16-byte vectors per work-queue item
     for rank in range(n):
         staging = torch.full((rows, cols), float("nan"), device=dev, dtype=torch.bfloat16)
-        cnt = torch.zeros((rows + 127) // 128 + 1, dtype=torch.int32, device=dev)
+        cnt = torch.zeros((rows + 127) // 128 + 2, dtype=torch.int32, device=dev)
         for seq in (1, 2):
             out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
             if seq == 2:
                 staging.fill_(float("nan"))
             rc = lib.hpb_gemm2_agw(a.data_ptr(), a.stride(0), ptrs, staging.data_ptr(), int(w_mn), rows, cols,
-                                   out.data_ptr(), out.stride(0), M, n, rank, cnt.data_ptr(),
-                                   cnt.data_ptr() + 4 * (cnt.numel() - 1), seq, pad.data_ptr(), 4, 0,
+                                   out.data_ptr(), out.stride(0), M, n, rank, cnt.data_ptr(), seq, pad.data_ptr(), 4, 0,
                                    2_000_000_000, st.data_ptr(), native.sm_count(dev), native.stream(dev))
             assert rc == 0, rc
             native.check_status()
             assert torch.equal(staging, w), (rank, seq)
             assert _rel_err(out, ref) < 5e-3, (rank, seq)
             assert int(cnt[-1].item()) == 0          # the work queue is idle again
+            assert int(cnt[-2].item()) == seq * ((rows * cols // 8 + cv - 1) // cv)
