@@ -161,6 +161,7 @@ class Llama(nn.Module):
         else:
             self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw))
             self.lm_head._hpb_gemm_only = True
+            self.lm_head._hpb_gather_late = True      # consumed at the very end of the forward pass
 
     def reset_parameters(self):
         nn.init.normal_(self.embed, mean=0.0, std=self.cfg.init_std)

@@ -33,6 +33,18 @@ def set_gemm_pair_mode(mode: str) -> None:
     _PAIR_MODE = mode
 
 
+_RIDE_PROVIDER = None      # callable(device, flops) -> gather spec that this GEMM should carry, or None
+_RIDE_ORDERS = {(False, False), (False, True), (True, True)}
+
+
+def set_ride_provider(fn) -> None:
+    """HSDP over symmetric memory registers the source of weight gathers that ride on GEMM launches
+    (the communication warps of the GEMM kernel copy a later GEMM's weight while the tensor cores
+    work on this one)."""
+    global _RIDE_PROVIDER
+    _RIDE_PROVIDER = fn
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          accumulate: bool = False) -> torch.Tensor:
@@ -73,6 +85,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lib = native.lib()
     # CTA-pair (256x256, cta_group::2) kernel for large problems, single-CTA 128x256 otherwise
     use_pair = _PAIR_MODE == "1" or (_PAIR_MODE == "auto" and M >= 512 and N >= 512 and hasattr(lib, "hpb_gemm2_bf16"))
+    if (use_pair and _RIDE_PROVIDER is not None and out.dtype == torch.bfloat16 and (a_mn, b_mn) in _RIDE_ORDERS
+            and (not accumulate or (a_mn and b_mn))):
+        ride = _RIDE_PROVIDER(dev, 2.0 * M * N * K)
+        if ride is not None:
+            import ctypes
+            rc = lib.hpb_gemm2_gather(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
+                                      out.data_ptr(), out.stride(0), int(accumulate), M, N, K, None, 0,
+                                      ctypes.byref(ride), 2_000_000_000, native.status_word(dev).data_ptr(),
+                                      native.sm_count(dev), native.stream(dev))
+            native.check(rc, "hpb_gemm2_gather")
+            return out
     fn = lib.hpb_gemm2_bf16 if use_pair else lib.hpb_gemm_bf16
     rc = fn(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
             out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), int(accumulate),

@@ -120,8 +120,70 @@ def _bind(lib):
     lib.hpb_gemm2_agw.argtypes = [vp, c64, pp, vp, ci, c64, c64, vp, c64, ci, ci, ci, vp, cu, vp, ci, cu, cull,
                                   vp, ci, vp]
     lib.hpb_gemm2_agw.restype = ci
+    pg = ctypes.POINTER(HpbGather)
+    lib.hpb_gemm2_gather.argtypes = [vp, ci, c64, vp, ci, c64, vp, c64, ci, ci, ci, ci, pg, ci, pg, cull, vp, ci, vp]
+    lib.hpb_gemm2_gather.restype = ci
+    lib.hpb_gather_shape_ok.argtypes = [c64, c64, ci]
+    lib.hpb_gather_shape_ok.restype = ci
     lib._hpb_fused_hsdp_bound = True
     return lib
+
+
+class HpbGather(ctypes.Structure):
+    """One weight to gather (mirror of the C struct of the same name)."""
+    _fields_ = [("shard_ptrs", ctypes.POINTER(ctypes.c_void_p)), ("staging", ctypes.c_void_p),
+                ("rows", ctypes.c_int64), ("cols", ctypes.c_int64), ("n", ctypes.c_int), ("rank", ctypes.c_int),
+                ("counters", ctypes.c_void_p), ("seq", ctypes.c_uint), ("my_pad", ctypes.c_void_p),
+                ("version_slot", ctypes.c_int), ("version", ctypes.c_uint)]
+
+
+def rides_enabled() -> bool:
+    """``HPB_RIDE=0``: a weight is gathered only by the GEMM that consumes it."""
+    return os.environ.get("HPB_RIDE", "1") != "0"
+
+
+class _Ticket:
+    """A weight whose gather has been requested: it rides on the GEMMs that run before its consumer."""
+    __slots__ = ("buf", "i", "spec", "left", "late")
+
+    def __init__(self, buf, i, spec, nbytes, late):
+        self.buf, self.i, self.spec, self.left, self.late = buf, i, spec, float(nbytes), late
+
+
+# per device: tickets in the order in which their consumers will run
+_RIDE_QUEUE: Dict[int, List[_Ticket]] = {}
+_RIDE_GBS = 500.0         # bytes a host GEMM is assumed to move per second of its own duration (x 1e9)
+_GEMM_TFLOPS = 1400.0
+
+
+def _queue(device) -> List[_Ticket]:
+    return _RIDE_QUEUE.setdefault(device.index, [])
+
+
+def next_ride(device, flops: float, exclude=None):
+    """The gather that a GEMM of ``flops`` floating-point operations should carry: the first ticket of
+    the queue (tickets marked ``late`` only when nothing else waits).  The ticket's estimate of what
+    is left shrinks by what this host can be expected to move; a ticket estimated complete leaves
+    the queue (its consumer finishes whatever is really left)."""
+    q = _RIDE_QUEUE.get(device.index)
+    if not q:
+        return None
+    pick = None
+    for t in q:
+        if t is not exclude and not t.late:
+            pick = t
+            break
+    if pick is None:
+        for t in q:
+            if t is not exclude:
+                pick = t
+                break
+    if pick is None:
+        return None
+    pick.left -= flops / (_GEMM_TFLOPS * 1e12) * _RIDE_GBS * 1e9
+    if pick.left <= 0:
+        q.remove(pick)
+    return pick.spec
 
 
 class _StagingPool:
@@ -207,8 +269,11 @@ class SymmParamBuffer:
                                   if f else None)
         self.gather_seq = [0] * len(params)
         self.pending = [False] * len(params)
+        self.tickets: List[Optional[_Ticket]] = [None] * len(params)
+        self.specs: List[Optional[HpbGather]] = [None] * len(params)
         self._build_segments(None)
         self.status = native.status_word(self.device)
+        self.staged_round = False     # tickets of the current unshard have been opened
         self.full: Optional[torch.Tensor] = None          # staging buffer while unsharded
         self.full_views: List[Optional[torch.Tensor]] = [None] * len(params)
         self.gather_event: Optional[torch.cuda.Event] = None
@@ -224,6 +289,8 @@ class SymmParamBuffer:
             p._symm = (self, i)
         _LIVE.add(self)
         _install_step_hook()
+        from ..ops import functional as _fn
+        _fn.set_ride_provider(next_ride)
         if self.n > 1:
             # every rank's shards are in place before anybody gathers them
             torch.cuda.synchronize(self.device)
@@ -238,8 +305,7 @@ class SymmParamBuffer:
         shape = p.full_shape
         if len(shape) != 2 or shape[1] % 64 or shape[0] % self.n:
             return False
-        shard_elems = shape[0] // self.n * shape[1]
-        return shard_elems % 8 == 0 and shard_elems >= 16384 and shape[0] >= 256 and shape[1] >= 64
+        return shape[0] >= 256 and self.lib.hpb_gather_shape_ok(shape[0], shape[1], self.n) == 0
 
     def _build_segments(self, group_index) -> None:
         """Segment tables: all parameters (optimizer kernel) and the non-fusable ones (copy kernel)."""
@@ -267,6 +333,7 @@ class SymmParamBuffer:
         if self.gather_event is not None or not self.params[0].is_sharded_now:
             return
         self._take_staging()
+        self._open_tickets()
         if self.num_rest == 0:
             return
         cs = comm_stream(self.device)
@@ -283,6 +350,35 @@ class SymmParamBuffer:
             native.check(rc, "hpb_p2p_allgather")
             self.gather_event = torch.cuda.Event()
             self.gather_event.record(cs)
+
+    def _open_tickets(self) -> None:
+        """Start a gather round for every weight that its consumer GEMM gathers: from now on the
+        GEMMs that run before the consumer carry it (in consumption order: parameter order in a
+        forward pass, the reverse inside a backward pass)."""
+        if self.staged_round:
+            return
+        self.staged_round = True
+        order = [i for i, f in enumerate(self.fusable) if f]
+        if torch._C._current_graph_task_id() != -1:
+            order.reverse()
+        q = _queue(self.device)
+        for i in order:
+            p = self.params[i]
+            rows, cols = p.full_shape
+            self.gather_seq[i] += 1
+            spec = self.specs[i]
+            if spec is None:
+                spec = HpbGather(ctypes.cast(self.param_shard_ptrs[i], ctypes.POINTER(ctypes.c_void_p)), 0, rows, cols, self.n, self.rank,
+                                 self.panel_cnt[i].data_ptr(), 0, self.symm.pad_ptrs[self.rank],
+                                 SLOT_SHARD_VERSION, 0)
+                self.specs[i] = spec
+            spec.staging = self.full_views[i].data_ptr()
+            spec.seq = self.gather_seq[i]
+            spec.version = self.version
+            t = _Ticket(self, i, spec, rows * cols * 2, bool(getattr(p.param, "_hpb_gather_late", False)))
+            self.tickets[i] = t
+            if rides_enabled():
+                q.append(t)
 
     def unshard(self) -> None:
         if not self.params[0].is_sharded_now:
@@ -305,38 +401,59 @@ class SymmParamBuffer:
     def release_staging(self) -> None:
         """Hand the staging buffer back (the parameters point at their shards again)."""
         if self.full is not None and self.gather_event is None and all(p.is_sharded_now for p in self.params):
+            for i, t in enumerate(self.tickets):
+                if t is not None:
+                    self._abandon(i)         # requested but never consumed
             _POOL.give(self.full)
             self.full = None
             self.full_views = [None] * len(self.params)
             self.pending = [False] * len(self.params)
+            self.staged_round = False
 
     def gather_pending(self, i: int) -> bool:
         return self.pending[i]
 
+    def _close_ticket(self, i: int):
+        t = self.tickets[i]
+        self.tickets[i] = None
+        if t is not None:
+            q = _RIDE_QUEUE.get(self.device.index)
+            if q and t in q:
+                q.remove(t)
+        return t
+
+    def _abandon(self, i: int) -> None:
+        """A gather round that will not be completed by a consumer: forget it and zero the weight's
+        counters (stream ordered), so that the next round starts from a clean queue."""
+        self._close_ticket(i)
+        self.panel_cnt[i].zero_()
+        self.gather_seq[i] = 0
+
     def gather_gemm(self, i: int, a: torch.Tensor, out: torch.Tensor, w_mn: bool) -> None:
-        """``out = a @ W_i^T`` (``w_mn=False``) or ``out = a @ W_i`` (``w_mn=True``) where the full
-        ``W_i`` is gathered from the peers inside the GEMM kernel; afterwards the parameter's full
-        view holds the whole weight for any later consumer."""
-        p = self.params[i]
-        rows, cols = p.full_shape
+        """``out = a @ W_i^T`` (``w_mn=False``) or ``out = a @ W_i`` (``w_mn=True``).  This launch is
+        the consumer of ``W_i``: its communication warps finish whatever part of the gather the
+        earlier GEMMs have not done, its tiles wait for the panels they need; afterwards the
+        parameter's full view holds the whole weight for any later consumer.  The launch also
+        carries the gather of the next weight in the queue."""
         if a.stride(-1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
             a = a.contiguous()
-        cnt = self.panel_cnt[i]
-        self.gather_seq[i] += 1
+        t = self._close_ticket(i)
+        spec = t.spec
+        rows, cols = self.params[i].full_shape
+        ride = next_ride(self.device, 2.0 * a.shape[0] * rows * cols)
         with tracing.nvtx_range("hpb.hsdp.allgather_gemm"):
-            rc = self.lib.hpb_gemm2_agw(
-                a.data_ptr(), a.stride(0), self.param_shard_ptrs[i], self.full_views[i].data_ptr(), int(w_mn),
-                rows, cols, out.data_ptr(), out.stride(0), a.shape[0], self.n, self.rank, cnt.data_ptr(),
-                self.gather_seq[i],
-                self.symm.pad_ptrs[self.rank], SLOT_SHARD_VERSION, self.version, DEFAULT_WAIT_NS,
+            rc = self.lib.hpb_gemm2_gather(
+                a.data_ptr(), 0, a.stride(0), None, 0, 0, out.data_ptr(), out.stride(0), 0, a.shape[0], 0, 0,
+                ctypes.byref(spec), int(w_mn), ctypes.byref(ride) if ride is not None else None, DEFAULT_WAIT_NS,
                 self.status.data_ptr(), native.sm_count(self.device), native.stream(self.device))
-        native.check(rc, "hpb_gemm2_agw")
+        native.check(rc, "hpb_gemm2_gather")
         self.pending[i] = False
 
     def materialize(self, i: int) -> None:
         """Gather parameter ``i`` now with the copy kernel (a consumer that is not ``ops.linear``)."""
         if not self.pending[i]:
             return
+        self._abandon(i)
         seg = self.segs[i:i + 1].contiguous()
         ep = self.symm.next_epoch()
         rc = self.lib.hpb_p2p_allgather(self.shard_ptrs, self.symm.pad_ptrs, seg.data_ptr(), 1,

@@ -434,3 +434,55 @@ def test_gemm_with_fused_weight_allgather_emulated_ranks(M, rows, cols, n, w_mn)
             assert _rel_err(out, ref) < 5e-3, (rank, seq)
             assert int(cnt[-1].item()) == 0          # the work queue is idle again
             assert int(cnt[-2].item()) == seq * ((rows * cols // 8 + cv - 1) // cv)
+
+
+@pytest.mark.parametrize("w_mn", [False, True])
+def test_weight_gather_rides_on_earlier_gemms_emulated_ranks(w_mn):
+    """A weight gather that starts on the communication warps of two unrelated GEMMs (a small one that
+    ends before the gather does, a weight-gradient-shaped one with accumulation) and is finished by
+    its consumer; ranks emulated on one GPU.  All three products and the gathered weight are checked,
+    over two rounds of the same weight."""
+    import ctypes
+    from hyper_parallel_b200.parallel import fused_hsdp
+    from hyper_parallel_b200.parallel.fused_hsdp import HpbGather
+    lib = fused_hsdp._bind(native.lib())
+    torch.manual_seed(5)
+    dev = _dev()
+    n, rank, rows, cols, M = 4, 1, 4096, 1024, 1024
+    w = torch.randn(rows, cols, device=dev, dtype=torch.bfloat16) * 0.1
+    shards = [c.clone() for c in w.chunk(n, dim=0)]
+    ptrs = (ctypes.c_void_p * n)(*[s.data_ptr() for s in shards])
+    pad = torch.zeros(1024, dtype=torch.int32, device=dev)
+    cnt = torch.zeros((rows + 127) // 128 + 2, dtype=torch.int32, device=dev)
+    staging = torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
+    st = native.status_word(dev)
+    spec = HpbGather(ctypes.cast(ptrs, ctypes.POINTER(ctypes.c_void_p)), staging.data_ptr(), rows, cols, n, rank,
+                     cnt.data_ptr(), 0, pad.data_ptr(), 4, 0)
+    a1 = torch.randn(512, 512, device=dev, dtype=torch.bfloat16)
+    b1 = torch.randn(512, 512, device=dev, dtype=torch.bfloat16)
+    a2 = torch.randn(2048, 1024, device=dev, dtype=torch.bfloat16)      # [K, M] (MN-major)
+    b2 = torch.randn(2048, 768, device=dev, dtype=torch.bfloat16)       # [K, N]
+    K3 = rows if w_mn else cols
+    a3 = torch.randn(M, K3, device=dev, dtype=torch.bfloat16)
+    args = (2_000_000_000, st.data_ptr(), native.sm_count(dev), native.stream(dev))
+    for seq in (1, 2):
+        spec.seq = seq
+        staging.fill_(float("nan"))
+        c1 = torch.empty(512, 512, device=dev, dtype=torch.bfloat16)
+        rc = lib.hpb_gemm2_gather(a1.data_ptr(), 0, 512, b1.data_ptr(), 0, 512, c1.data_ptr(), 512, 0, 512, 512, 512,
+                                  None, 0, ctypes.byref(spec), *args)
+        assert rc == 0
+        c2 = torch.ones(1024, 768, device=dev, dtype=torch.bfloat16)
+        rc = lib.hpb_gemm2_gather(a2.data_ptr(), 1, 1024, b2.data_ptr(), 1, 768, c2.data_ptr(), 768, 1, 1024, 768,
+                                  2048, None, 0, ctypes.byref(spec), *args)
+        assert rc == 0
+        c3 = torch.empty(M, cols if w_mn else rows, device=dev, dtype=torch.bfloat16)
+        rc = lib.hpb_gemm2_gather(a3.data_ptr(), 0, a3.stride(0), None, 0, 0, c3.data_ptr(), c3.stride(0), 0, M, 0, 0,
+                                  ctypes.byref(spec), int(w_mn), None, *args)
+        assert rc == 0
+        native.check_status()
+        assert torch.equal(staging, w), seq
+        assert _rel_err(c1, a1.float() @ b1.float().t()) < 5e-3
+        assert _rel_err(c2, a2.float().t() @ b2.float() + 1.0) < 5e-3
+        assert _rel_err(c3, a3.float() @ (w.float() if w_mn else w.float().t())) < 5e-3
+        assert int(cnt[-1].item()) == 0 and int(cnt[-2].item()) == seq * (rows * cols // 8 // 2048)
