@@ -187,11 +187,43 @@ fused_rs_adamw_kernel(PeerTable grads, const __nv_bfloat16* __restrict__ mc_grad
     const AdamArgs a = tbl.g[sg.group];
     const long long nv = sg.n >> 3;
     const long long goff = sg.full_off + static_cast<long long>(rank) * sg.n;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nv;
+    if constexpr (MC) {
+      // Software pipeline: the kMcDepth reduced vectors of the NEXT trip are requested from the
+      // switch before the current ones are consumed, so every thread keeps kMcDepth NVLink round
+      // trips (about 3 us each) in flight behind the HBM traffic of the optimizer state.
+      constexpr int kMcDepth = 4;
+      const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+      const long long nthr = static_cast<long long>(gridDim.x) * blockDim.x;
+      uint4 cur[kMcDepth];
+#pragma unroll
+      for (int u = 0; u < kMcDepth; ++u) {
+        const long long i = tid + u * nthr;
+        if (i < nv) cur[u] = multimem_ld_reduce_bf16x8(mc_grads + goff + (i << 3));
+      }
+      for (long long base = tid; base < nv; base += kMcDepth * nthr) {
+        uint4 nxt[kMcDepth];
+#pragma unroll
+        for (int u = 0; u < kMcDepth; ++u) {
+          const long long i = base + (kMcDepth + u) * nthr;
+          if (i < nv) nxt[u] = multimem_ld_reduce_bf16x8(mc_grads + goff + (i << 3));
+        }
+#pragma unroll
+        for (int u = 0; u < kMcDepth; ++u) {
+          const long long i = base + u * nthr;
+          if (i < nv) {
+            float acc[8];
+            unpack8(cur[u], acc);
+            adam8(a, acc, master, m, v, param_shard, sg.shard_off + (i << 3));
+          }
+          cur[u] = nxt[u];
+        }
+      }
+    }
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; !MC && i < nv;
          i += static_cast<long long>(gridDim.x) * blockDim.x) {
       float acc[8];
       if constexpr (MC) {
-        unpack8(multimem_ld_reduce_bf16x8(mc_grads + goff + (i << 3)), acc);
+        // handled above
       } else if constexpr (N > 0) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.f;
