@@ -137,6 +137,14 @@ class _Clocks:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
 
 
+def bench_config(args, layers, hidden, world):
+    """The ``config`` entry of the JSON line; bench.py builds the same dict for its own arm."""
+    return {"model": args.model, "layers": layers, "hidden": hidden,
+            "global_batch": world * args.batch_per_gpu, "seq_len": args.seq_len,
+            "parallelism": f"hsdp level3 full shard x{world}", "optimizer": "AdamW, fp32 master/m/v",
+            "l2": "no flush needed: each step streams >100 GB of weights/activations, far above the 126 MB L2"}
+
+
 def _unavailable(why):
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}))
@@ -165,40 +173,108 @@ def run_reference(args):
     c = dict(CONFIGS[args.model])
     if args.layers is not None:
         c["layers"] = args.layers
-    try:
+
+    def build(comm_async, comm_fusion):
+        """Model + optimizer + step function for one communication mode of the reference's hsdp()."""
         torch.manual_seed(0)
         model = RefLlama(c).to(dev)
         for p in model.parameters():
             if p.dim() > 1:
                 nn.init.normal_(p, 0.0, 0.02)
-        # comm_async=False: with torch 2.11 the reference's asynchronous gradient hook raises
-        # "The size of tensor a (N) must match the size of tensor b (N/2)" in backward for every
-        # optimizer level as soon as a parameter is sharded; its synchronous hook runs.
+        kw = dict(shard_size=world, optimizer_level="level3", comm_async=comm_async, comm_fusion=comm_fusion)
         for layer in model.layers:
-            hsdp(layer, shard_size=world, optimizer_level="level3", comm_async=False)
-        hsdp(model, shard_size=world, optimizer_level="level3", comm_async=False)
+            hsdp(layer, **kw)
+        hsdp(model, **kw)
         for i, layer in enumerate(model.layers):
             if i + 1 < len(model.layers):
                 layer.set_forward_prefetch_cells([model.layers[i + 1]])
             if i > 0:
                 layer.set_backward_prefetch_cells([model.layers[i - 1]])
-        params = [p for p in model.parameters() if p.requires_grad]
-        masters = [p.detach().float().clone().requires_grad_() for p in params]
-        opt = torch.optim.AdamW(masters, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)
-
+        # One optimizer per wrapped module: the fp32 copies of its gradients exist only while that
+        # module is stepped (with one optimizer over everything, 4 bytes per parameter of fp32
+        # gradients stay alive on top of master / exp_avg / exp_avg_sq, which does not fit one GPU).
+        groups = [[p for p in layer.parameters() if p.requires_grad] for layer in model.layers]
+        seen = {id(p) for g in groups for p in g}
+        groups.append([p for p in model.parameters() if p.requires_grad and id(p) not in seen])
+        units = []
+        for params in groups:
+            masters = [p.detach().float().clone().requires_grad_() for p in params]
+            units.append((params, masters, torch.optim.AdamW(masters, lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
+                                                             weight_decay=0.1, fused=True)))
         anchor = torch.zeros(1, device=dev)
 
         def step(tok):
             loss = model(anchor, tok[:, :-1], tok[:, 1:])
             loss.backward(torch.ones_like(loss))
             hsdp_sync_stream()
-            for p, m in zip(params, masters):
-                m.grad = p.grad.float().view_as(m) if p.grad is not None else None
-                p.grad = None
-            opt.step()
-            with torch.no_grad():
-                torch._foreach_copy_([p.data for p in params], [m.data.view_as(p.data) for p, m in zip(params, masters)])
+            for params, masters, opt in units:
+                for p, m in zip(params, masters):
+                    m.grad = p.grad.float().view_as(m) if p.grad is not None else None
+                    p.grad = None
+                opt.step()
+                opt.zero_grad(set_to_none=True)
+                with torch.no_grad():
+                    torch._foreach_copy_([p.data for p in params],
+                                         [m.data.view_as(p.data) for p, m in zip(params, masters)])
             return loss
+
+        return step
+
+    def probe(mode, tok, steps=2):
+        """Seconds per step of one mode over a few steps, or None (and the traceback on rank 0's
+        stderr and in gpurun_out/) when the reference raises in that mode."""
+        import gc
+        import traceback
+        try:
+            step = build(*mode)
+            step(tok)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                step(tok)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / steps
+        except Exception:  # noqa: BLE001
+            if rank == 0:
+                text = traceback.format_exc()
+                sys.stderr.write(f"[reference arm] mode comm_async={mode[0]} comm_fusion={mode[1]} failed:\n{text}")
+                try:
+                    os.makedirs(os.path.join(os.path.dirname(HERE), "gpurun_out"), exist_ok=True)
+                    with open(os.path.join(os.path.dirname(HERE), "gpurun_out",
+                                           f"reference_mode_async{int(mode[0])}_fusion{int(mode[1])}_N{world}.txt"),
+                              "w") as f:
+                        f.write(text)
+                except OSError:
+                    pass
+            dt = None
+        step = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        ok = torch.tensor([0.0 if dt is None else 1.0, dt or 0.0], device=dev, dtype=torch.float64)
+        if world > 1:
+            lo = ok.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(ok, op=dist.ReduceOp.MAX)
+            return None if lo[0].item() == 0.0 else ok[1].item()
+        return dt
+
+    try:
+        # The reference's fastest WORKING communication mode is the baseline: every combination of
+        # its comm_async / comm_fusion switches is tried for a few steps first.
+        g0 = torch.Generator().manual_seed(12345 + rank)
+        tok0 = torch.randint(0, c["vocab"], (args.batch_per_gpu, args.seq_len + 1), generator=g0).to(dev)
+        modes = [(True, True), (False, True), (True, False), (False, False)] if world > 1 else [(False, False)]
+        tried = {}
+        for mode in modes:
+            tried[mode] = probe(mode, tok0)
+        working = {m: t for m, t in tried.items() if t is not None}
+        if not working:
+            raise RuntimeError("no communication mode of the reference's hsdp() ran: "
+                               + ", ".join(f"async={m[0]} fusion={m[1]}" for m in tried))
+        best = min(working, key=working.get)
+        step = build(*best)
+        mode_note = {f"async={int(m[0])},fusion={int(m[1])}": (None if t is None else round(t * 1e3, 1))
+                     for m, t in tried.items()}
 
         n_total = args.warmup + args.steps
         g = torch.Generator().manual_seed(0 + rank)
@@ -257,10 +333,11 @@ def run_reference(args):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform token ids, seed 0; random-init N(0,0.02) weights)",
             "impl": "reference",
-            "config": {"model": args.model, "layers": c["layers"], "hidden": c["hidden"],
-                       "global_batch": world * args.batch_per_gpu, "seq_len": args.seq_len,
-                       "parallelism": f"reference hsdp level3 full shard x{world}",
-                       "optimizer": "torch.optim.AdamW(fused) on fp32 master copies"},
+            "config": bench_config(args, c["layers"], c["hidden"], world),
+            "arm": {"sharding": f"reference hsdp(optimizer_level='level3', shard_size={world}, comm_async={best[0]}, "
+                                f"comm_fusion={best[1]})",
+                    "optimizer": "torch.optim.AdamW(fused) on fp32 master copies, one optimizer per wrapped module",
+                    "modes_tried_ms_per_step": mode_note},
             "loss": last, "clocks": clocks.summary(),
             "e2e": {"value": toks / (e2e_ms / args.steps / 1e3), "unit": "tokens/s",
                     "ms_per_step": e2e_ms / args.steps,

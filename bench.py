@@ -61,6 +61,14 @@ def make_batches(cfg, args, rank, n):
     return toks.pin_memory()
 
 
+def _shared_config(args, layers, hidden, world):
+    """One ``config`` dict for both arms (the reference arm's module defines it and imports nothing of
+    this package)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    from reference_arm import bench_config
+    return bench_config(args, layers, hidden, world)
+
+
 def run_ours(args):
     import torch.distributed as dist
     import hyper_parallel_b200 as hp
@@ -170,11 +178,7 @@ def run_ours(args):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform token ids, seed 0; random-init N(0,0.02) weights)",
             "impl": "ours",
-            "config": {"model": args.model, "layers": cfg.num_layers, "hidden": cfg.hidden_size,
-                       "global_batch": world * args.batch_per_gpu, "seq_len": args.seq_len,
-                       "parallelism": f"hsdp level3 full shard x{world}",
-                       "optimizer": "AdamW, fp32 master/m/v",
-                       "l2": "no flush needed: each step streams >100 GB of weights/activations, far above the 126 MB L2"},
+            "config": _shared_config(args, cfg.num_layers, cfg.hidden_size, world),
             "mfu_of_measured_sustained_bf16": mfu, "loss": last_loss,
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

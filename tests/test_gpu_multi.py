@@ -31,7 +31,12 @@ def _train(rank, world, fused, steps, out):
     hp.init_parameters(model, device=dev, seed=0)
     n_symm = sum(len(m.hsdp_scheduler.hsdp_state.symm_buffers) for m in model.modules() if "hsdp_scheduler" in m.__dict__)
     assert (n_symm > 0) == fused
-    opt = FusedAdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    # two parameter groups (no weight decay and a larger step for the norm weights): they share the flat
+    # buffer of their module with the matrices, and both paths must honour the per-group values
+    decay = [p for p in model.parameters() if p.dim() > 1]
+    no_decay = [p for p in model.parameters() if p.dim() <= 1]
+    opt = FusedAdamW([{"params": decay}, {"params": no_decay, "weight_decay": 0.0, "lr": 5e-2}], lr=1e-3,
+                     betas=(0.9, 0.95), weight_decay=0.1)
     opt.fuse_into_backward(model)
     g = torch.Generator().manual_seed(100 + rank)
     losses = []
@@ -49,8 +54,11 @@ def _train(rank, world, fused, steps, out):
     w = model.layers[0].wqkv.detach().float().contiguous()
     parts = [torch.empty_like(w) for _ in range(world)]
     dist.all_gather(parts, w)
+    nw = model.layers[0].attn_norm.detach().float().contiguous()
+    nparts = [torch.empty_like(nw) for _ in range(world)]
+    dist.all_gather(nparts, nw)
     if rank == 0:
-        torch.save({"losses": losses, "w": torch.cat(parts, 0).cpu()}, out)
+        torch.save({"losses": losses, "w": torch.cat(parts, 0).cpu(), "norm": torch.cat(nparts, 0).cpu()}, out)
 
 
 def _worker(rank, world, port, tmp):
@@ -80,6 +88,9 @@ def test_symmetric_hsdp_matches_nccl_path(tmp_path, world):
         assert abs(x - y) < 2e-2 * abs(x), (a["losses"], b["losses"])
     rel = (a["w"] - b["w"]).norm() / a["w"].norm()
     assert rel < 5e-3, rel.item()
+    # the norm weights moved (lr 5e-2) and moved alike: the per-group hyper-parameters reached the fused kernel
+    assert (a["norm"] - 1.0).abs().max() > 1e-2
+    assert (a["norm"] - b["norm"]).abs().max() < 2e-2, (a["norm"] - b["norm"]).abs().max()
     # the fused path run twice from the same seeds gives the same bits (no race shows up as noise)
     c = torch.load(tmp_path / "fused2.pt")
     assert b["losses"] == c["losses"] and torch.equal(b["w"], c["w"])

@@ -102,3 +102,52 @@ CASES = [("level1", 1, 1, "sync"),                       # pure data parallel
 @pytest.mark.parametrize("level,shard_size,acc,mode", CASES)
 def test_hsdp_matches_single_process(level, shard_size, acc, mode):
     run_distributed(_worker, 4, level, shard_size, acc, mode)
+
+
+class _Branchy(nn.Module):
+    """A module one of whose parameters gets no gradient (its branch is not on the loss path)."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(7)
+        self.used = nn.Linear(HID, HID)
+        self.unused = nn.Linear(HID, HID)
+
+    def forward(self, x):
+        return torch.tanh(self.used(x))
+
+
+def _unused_worker(rank, world, level):
+    import torch.distributed as dist
+    import hyper_parallel_b200 as hp
+    ref = _Branchy()
+    net = _Branchy()
+    hp.hsdp(net, shard_size=world, threshold=0, optimizer_level=level, grad_scale=1.0 / world, comm_fusion=True,
+            bucket_size=-1)
+    xs, ys = _data()
+    opt = torch.optim.SGD(net.parameters(), lr=LR)
+    ropt = torch.optim.SGD(ref.parameters(), lr=LR)
+    for s in range(STEPS):
+        ropt.zero_grad()
+        F.mse_loss(ref(xs[s]), ys[s]).backward()
+        ropt.step()
+        net.zero_grads()
+        x, y = xs[s].chunk(world)[rank], ys[s].chunk(world)[rank]
+        F.mse_loss(net(x), y).backward()
+        hp.hsdp_sync_stream()
+        opt.step()
+    # the bucket was reduced although `unused` never fired its hook: `used` trained like the reference
+    # and nothing stale was left behind for the next step
+    state = net.hsdp_scheduler.hsdp_state
+    assert all(not b.ready for b in state.grad_buffers)
+    w = net.used.weight.detach()
+    full = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(full, w.contiguous())
+    got = torch.cat(full, 0) if w.shape != ref.used.weight.shape else w
+    assert torch.allclose(got, ref.used.weight.detach(), atol=1e-5), (got - ref.used.weight).abs().max()
+    assert torch.allclose(net.unused.weight.detach().new_tensor(0.0), torch.tensor(0.0))
+
+
+@pytest.mark.parametrize("level", ["level1", "level2", "level3"])
+def test_bucket_with_a_parameter_that_gets_no_gradient(level):
+    run_distributed(_unused_worker, 2, level)
