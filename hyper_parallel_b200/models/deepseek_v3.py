@@ -53,6 +53,10 @@ class DeepSeekV3Config:
     rope_theta: float = 10000.0
     norm_eps: float = 1e-6
     init_std: float = 0.006
+    # block-scaled fp8 (e4m3; 1x128 activation tiles, 128x128 weight tiles) for the forward GEMMs of
+    # the attention / dense / shared-expert projections and of the routed experts; master weights,
+    # the backward GEMMs, the router and the lm head stay bf16 / fp32
+    fp8: bool = False
 
     @staticmethod
     def tiny() -> "DeepSeekV3Config":
@@ -74,6 +78,14 @@ class DeepSeekV3Config:
         mm = self.num_layers * attn_p + self.first_k_dense * dense + n_moe * moe + self.vocab_size * h
         attn = self.num_layers * 6 * self.num_heads * (qk + self.v_head_dim) * seq_len / 2
         return 6.0 * mm + attn
+
+
+def _lin(x: torch.Tensor, w: torch.Tensor, fp8: bool) -> torch.Tensor:
+    """Projection ``x @ w.T``: fp8 block-scaled forward GEMM when asked for (CUDA, K % 128 == 0)."""
+    if fp8 and x.is_cuda and x.shape[-1] % 128 == 0:
+        from ..ops import fp8 as f8
+        return f8.fp8_linear(x, w)
+    return ops.linear(x, w)
 
 
 def _rope_last(x: torch.Tensor, seq_len: int, theta: float) -> torch.Tensor:
@@ -106,26 +118,28 @@ class MLA(nn.Module):
         c = self.cfg
         nh, dn, dr, dv = c.num_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
         T = x.shape[0]
-        q = ops.linear(ops.rmsnorm(ops.linear(x, self.wq_a), self.q_norm, c.norm_eps), self.wq_b)
+        f8 = c.fp8
+        q = _lin(ops.rmsnorm(_lin(x, self.wq_a, f8), self.q_norm, c.norm_eps), self.wq_b, f8)
         q = q.view(T, nh, dn + dr)
         q_nope, q_rope = q.split([dn, dr], dim=-1)
         q_rope = _rope_last(q_rope.contiguous(), seq_len, c.rope_theta)
-        kv_a = ops.linear(x, self.wkv_a)
+        kv_a = _lin(x, self.wkv_a, f8)
         kv_c, k_rope = kv_a.split([c.kv_lora_rank, dr], dim=-1)
         k_rope = _rope_last(k_rope.contiguous().view(T, 1, dr), seq_len, c.rope_theta)
-        kv = ops.linear(ops.rmsnorm(kv_c.contiguous(), self.kv_norm, c.norm_eps), self.wkv_b).view(T, nh, dn + dv)
+        kv = _lin(ops.rmsnorm(kv_c.contiguous(), self.kv_norm, c.norm_eps), self.wkv_b, f8).view(T, nh, dn + dv)
         k_nope, v = kv.split([dn, dv], dim=-1)
         qh = torch.cat([q_nope, q_rope], dim=-1).view(batch, seq_len, nh, dn + dr)
         kh = torch.cat([k_nope, k_rope.expand(T, nh, dr)], dim=-1).view(batch, seq_len, nh, dn + dr)
         vh = v.reshape(batch, seq_len, nh, dv)
         o = ops.attention.causal_attention(qh, kh, vh)          # [B, S, nh, dv]
-        return ops.linear(o.reshape(T, nh * dv), self.wo)
+        return _lin(o.reshape(T, nh * dv), self.wo, f8)
 
 
 class DenseFFN(nn.Module):
-    def __init__(self, hidden: int, ffn: int, std: float, device=None, dtype=torch.bfloat16):
+    def __init__(self, hidden: int, ffn: int, std: float, device=None, dtype=torch.bfloat16, fp8: bool = False):
         super().__init__()
         self.std = std
+        self.fp8 = fp8
         self.w_gate_up = nn.Parameter(torch.empty(2 * ffn, hidden, device=device, dtype=dtype))
         self.w_down = nn.Parameter(torch.empty(hidden, ffn, device=device, dtype=dtype))
 
@@ -134,7 +148,7 @@ class DenseFFN(nn.Module):
         nn.init.normal_(self.w_down, 0.0, self.std)
 
     def forward(self, x):
-        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up)), self.w_down)
+        return _lin(ops.swiglu(_lin(x, self.w_gate_up, self.fp8)), self.w_down, self.fp8)
 
 
 class MoE(nn.Module):
@@ -156,7 +170,7 @@ class MoE(nn.Module):
         self.register_buffer("gate_bias", torch.zeros(E, device=device, dtype=torch.float32))   # aux-free bias
         self.w_gate_up = nn.Parameter(torch.empty(self.local_experts, 2 * f, h, **kw))
         self.w_down = nn.Parameter(torch.empty(self.local_experts, h, f, **kw))
-        self.shared = DenseFFN(h, f * cfg.n_shared_experts, cfg.init_std, device, dtype) \
+        self.shared = DenseFFN(h, f * cfg.n_shared_experts, cfg.init_std, device, dtype, cfg.fp8) \
             if cfg.n_shared_experts else None
         # expert weights are expert-parallel, not data-parallel replicas: HSDP must not shard them
         self.w_gate_up.hsdp_shard_size = 1
@@ -187,7 +201,7 @@ class MoE(nn.Module):
         if ep_fused.usable(x, topk_idx, self.w_gate_up, c.n_routed_experts, self.ep_group):
             # dispatch / combine kernels over NVLink peer memory around the grouped expert GEMMs
             y = ep_fused.fused_expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down,
-                                                   c.n_routed_experts, self.ep_group)
+                                                   c.n_routed_experts, self.ep_group, fp8=c.fp8)
         else:
             y = moe_ops.expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down, c.n_routed_experts,
                                             self.ep_group)
@@ -206,7 +220,7 @@ class DeepSeekBlock(nn.Module):
         self.ffn_norm = nn.Parameter(torch.empty(cfg.hidden_size, **kw))
         self.is_moe = layer_idx >= cfg.first_k_dense
         self.ffn = MoE(cfg, ep_group, device, dtype) if self.is_moe else \
-            DenseFFN(cfg.hidden_size, cfg.dense_ffn_size, cfg.init_std, device, dtype)
+            DenseFFN(cfg.hidden_size, cfg.dense_ffn_size, cfg.init_std, device, dtype, cfg.fp8)
 
     def reset_parameters(self):
         nn.init.ones_(self.attn_norm)

@@ -35,7 +35,20 @@ struct Params {
   __nv_bfloat16* C;
   long long ldc;
   int* status;
+  // grouped (expert) mode: rows of A / C are grouped by expert, every group padded to a multiple of
+  // 128; block_group[m_blk] names the expert of each 128-row block (-1: unused block, skipped);
+  // B stacks the experts' [b_group_rows, K] weights along its rows, sb their [b_group_rows/128, K/128]
+  // scale tiles.  block_group == nullptr: plain GEMM.
+  const int* block_group;
+  int b_group_rows;
 };
+
+// Expert of the row block (0 for a plain GEMM) and the number of K blocks the tile runs (0: skip).
+__device__ __forceinline__ int tile_group(const Params& p, int m_blk, int num_k, int& k_blocks) {
+  const int g = p.block_group != nullptr ? p.block_group[m_blk] : 0;
+  k_blocks = g < 0 ? 0 : num_k;
+  return g < 0 ? 0 : g;
+}
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -86,8 +99,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        const int m0 = (t % num_m) * BM;
+        int kbs;
+        const int n0 = tile_group(p, t % num_m, num_k, kbs) * p.b_group_rows + (t / num_m) * BN;
+        for (int kb = 0; kb < kbs; ++kb) {
           ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier, blockIdx.x);
           if (!ok) break;
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -106,7 +121,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       long it = 0;                                                      // k blocks issued so far
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
+        int kbs;
+        tile_group(p, t % num_m, num_k, kbs);
+        for (int kb = 0; kb < kbs; ++kb, ++it) {
           const int pb = static_cast<int>(it % NBUF);
           const uint32_t pphase = static_cast<uint32_t>((it / NBUF) & 1);
           ok = mbar_wait_bounded(&part_empty[pb], pphase ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
@@ -144,13 +161,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const int m0 = (t % num_m) * BM, n_blk = t / num_m, n0 = n_blk * BN + half * HN;
+      int kbs;
+      const int grp = tile_group(p, t % num_m, num_k, kbs);
+      if (kbs == 0) continue;                 // unused row block: no products, output rows left alone
       const int row = m0 + q * 32 + lane;
       const int srow = row < p.M ? row : p.M - 1;
       float2 acc[HN / 2];
 #pragma unroll
       for (int j = 0; j < HN / 2; ++j) acc[j] = make_float2(0.f, 0.f);
       const float* sa_row = p.sa + srow;
-      const float* sb_row = p.sb + static_cast<long long>(n_blk) * kblocks;
+      const float* sb_row = p.sb + (static_cast<long long>(grp) * (p.b_group_rows / BN) + n_blk) * kblocks;
       // scales are fetched four blocks ahead (an L2 round trip is longer than one block) and
       // multiplied only when they are used, so that the loads never stall the promotion
       constexpr int PF = 4;
@@ -342,8 +362,39 @@ extern "C" int hpb_gemm_fp8_blockscale(const void* Aq, const float* sa, const vo
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status};
+  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, nullptr, 0};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  gemm_fp8_kernel<<<tiles < num_sms ? tiles : num_sms, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Grouped (expert) form: Aq [M, K] with sa [K/128, M], rows grouped by expert in 128-row blocks
+// (block_group [M/128], -1 = unused block); Bq [E * N, K] with sb [E * N/128, K/128]; C [M, N] bf16
+// with C rows of expert e = A rows of e times W_e^T.  N must be a multiple of 128, M of 128.
+extern "C" int hpb_gemm_fp8_blockscale_grouped(const void* Aq, const float* sa, const void* Bq, const float* sb,
+                                               void* C, long long ldc, int M, int N, int K, int num_experts,
+                                               const int* block_group, int* status, int num_sms,
+                                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || num_experts <= 0) return 0;
+  if ((K % 128) || (N % 128) || (M % 128) || block_group == nullptr || (reinterpret_cast<uintptr_t>(Aq) & 15) ||
+      (reinterpret_cast<uintptr_t>(Bq) & 15))
+    return -2;
+  cudaFree(nullptr);
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, Aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, K, BK, BM);
+  if (r) return r;
+  r = make_tmap_2d(&tb, Bq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, static_cast<uint64_t>(num_experts) * N, K, BK, BN);
+  if (r) return r;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, block_group, N};
+  const int tiles = (M / BM) * (N / BN);
   gemm_fp8_kernel<<<tiles < num_sms ? tiles : num_sms, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -28,6 +28,8 @@ def _lib():
         vp, ci, cll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.hpb_gemm_fp8_blockscale.argtypes = [vp, vp, vp, vp, vp, cll, ci, ci, ci, vp, ci, vp]
         lib.hpb_gemm_fp8_blockscale.restype = ci
+        lib.hpb_gemm_fp8_blockscale_grouped.argtypes = [vp, vp, vp, vp, vp, cll, ci, ci, ci, ci, vp, vp, ci, vp]
+        lib.hpb_gemm_fp8_blockscale_grouped.restype = ci
         lib.hpb_quant_act_1x128.argtypes = [vp, vp, vp, ci, ci, vp]
         lib.hpb_quant_act_1x128.restype = ci
         lib.hpb_quant_weight_128x128.argtypes = [vp, vp, vp, ci, ci, vp]
@@ -97,6 +99,30 @@ def gemm_fp8(aq, sa, bq, sb) -> torch.Tensor:
                                         out.stride(0), M, N, K, native.status_word(dev).data_ptr(),
                                         native.sm_count(dev), native.stream(dev))
     native.check(rc, "hpb_gemm_fp8_blockscale")
+    return out
+
+
+def gemm_fp8_grouped(aq, sa, bq, sb, block_group, num_experts: int, out=None) -> torch.Tensor:
+    """Grouped (expert) fp8 GEMM: rows of ``aq[M, K]`` are grouped by expert in 128-row blocks
+    (``block_group[M/128]``, ``-1`` = unused block, left untouched in the output); ``bq[E*N, K]``
+    stacks the experts' weights, ``sb[E*N/128, K/128]`` their scale tiles.  Returns ``[M, N]`` bf16."""
+    M, K = aq.shape
+    N = bq.shape[0] // num_experts
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
+    if not aq.is_cuda:
+        a = dequantize(aq, scale_act=sa)
+        b = dequantize(bq, scale_w=sb).view(num_experts, N, K)
+        for blk, e in enumerate(block_group.tolist()):
+            if e >= 0:
+                out[blk * 128:(blk + 1) * 128] = (a[blk * 128:(blk + 1) * 128] @ b[e].t()).to(torch.bfloat16)
+        return out
+    dev = aq.device
+    rc = _lib().hpb_gemm_fp8_blockscale_grouped(aq.data_ptr(), sa.data_ptr(), bq.data_ptr(), sb.data_ptr(),
+                                                out.data_ptr(), out.stride(0), M, N, K, num_experts,
+                                                block_group.data_ptr(), native.status_word(dev).data_ptr(),
+                                                native.sm_count(dev), native.stream(dev))
+    native.check(rc, "hpb_gemm_fp8_blockscale_grouped")
     return out
 
 

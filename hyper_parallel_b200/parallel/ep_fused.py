@@ -143,7 +143,7 @@ class _FusedExperts(torch.autograd.Function):
     """dispatch -> grouped SwiGLU FFN -> combine, forward and backward, on the kernels above."""
 
     @staticmethod
-    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, ws: EPWorkspace):
+    def forward(ctx, x, topk_idx, topk_w, w_gate_up, w_down, ws: EPWorkspace, fp8: bool = False):
         T, k = topk_idx.shape
         E, El, H, cap = ws.E, ws.e_local, ws.H, ws.cap_rows
         F2 = w_gate_up.shape[1]
@@ -156,11 +156,23 @@ class _FusedExperts(torch.autograd.Function):
         topk_idx = topk_idx.contiguous()
         recv, block_group, offsets = ws.dispatch(x, sorted_token, counts)
         h = torch.empty((cap, F2), dtype=x.dtype, device=x.device)
-        _grouped(recv, False, cap, w_gate_up.view(El * F2, H), False, El * F2, h, cap, F2, H, 1, block_group, None,
-                 El, F2)
-        act = _swiglu_raw(h)
-        _grouped(act, False, cap, w_down.view(El * H, F2 // 2), False, El * H, ws.out, cap, H, F2 // 2, 1,
-                 block_group, None, El, H)
+        if fp8:
+            # forward expert GEMMs on the fp8 tensor cores: 1x128 activation scales, 128x128 weight
+            # scales, fp32 promotion per 128-deep block; the backward runs in bf16 on the master weights
+            from ..ops import fp8 as f8
+            aq, sa = f8.quantize_act_1x128(recv)
+            wq, wsc = f8.quantize_weight_128x128(w_gate_up.view(El * F2, H))
+            f8.gemm_fp8_grouped(aq, sa, wq, wsc, block_group, El, out=h)
+            act = _swiglu_raw(h)
+            aq, sa = f8.quantize_act_1x128(act)
+            wq, wsc = f8.quantize_weight_128x128(w_down.view(El * H, F2 // 2))
+            f8.gemm_fp8_grouped(aq, sa, wq, wsc, block_group, El, out=ws.out)
+        else:
+            _grouped(recv, False, cap, w_gate_up.view(El * F2, H), False, El * F2, h, cap, F2, H, 1, block_group,
+                     None, El, F2)
+            act = _swiglu_raw(h)
+            _grouped(act, False, cap, w_down.view(El * H, F2 // 2), False, El * H, ws.out, cap, H, F2 // 2, 1,
+                     block_group, None, El, H)
         y, rows = ws.combine(topk_idx, sorted_pos, topk_w.float().contiguous(), save_rows=True)
         ctx.save_for_backward(recv, h, block_group, offsets, topk_idx, topk_w, order, sorted_token, counts,
                               sorted_pos, rows, w_gate_up, w_down)
@@ -196,15 +208,19 @@ class _FusedExperts(torch.autograd.Function):
         dw_gate_up = torch.empty_like(w_gate_up)
         _grouped(d_h, True, cap, recv, True, cap, dw_gate_up.view(El * F2, H), F2, H, 0, 2, None, offsets, El, 0)
         dx, _ = ws.combine(topk_idx, sorted_pos, None, save_rows=False)
-        return dx, None, dw_topk, dw_gate_up, dw_down, None
+        return dx, None, dw_topk, dw_gate_up, dw_down, None, None
 
 
 def fused_expert_parallel_ffn(x, topk_idx, topk_w, w_gate_up, w_down, num_experts: int, ep_group,
-                              capacity: float = 2.0):
-    """``y[t] = sum_k topk_w[t,k] * expert_{topk_idx[t,k]}(x[t])`` with experts sharded over ``ep_group``."""
+                              capacity: float = 2.0, fp8: bool = False):
+    """``y[t] = sum_k topk_w[t,k] * expert_{topk_idx[t,k]}(x[t])`` with experts sharded over ``ep_group``.
+    ``fp8``: the two forward expert GEMMs run block-scaled in e4m3 (hidden and expert width must be
+    multiples of 128; otherwise bf16 is used)."""
     T, k = topk_idx.shape
     ws = EPWorkspace.get(ep_group, T, k, x.shape[-1], num_experts, capacity)
-    return _FusedExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up.contiguous(), w_down.contiguous(), ws)
+    fp8 = bool(fp8) and x.shape[-1] % 128 == 0 and w_down.shape[-1] % 128 == 0
+    return _FusedExperts.apply(x.contiguous(), topk_idx, topk_w, w_gate_up.contiguous(), w_down.contiguous(), ws,
+                               fp8)
 
 
 def usable(x, topk_idx, w_gate_up, num_experts: int, ep_group) -> bool:

@@ -48,14 +48,17 @@ def _scatter_sum_tokens(x: torch.Tensor, group) -> torch.Tensor:
 
 
 def _workspace(group, x: torch.Tensor, shard_rows: int, k: int, n_out: int):
-    """Symmetric-memory workspace of the fused kernels, or ``None`` when they do not apply."""
+    """Symmetric-memory workspace of the fused kernels, or ``None`` when they do not apply.  It is
+    sized for the forward product and for the two backward products of the same layer (which gather
+    / scatter along the other matrix dimension), so that it never has to grow inside a step."""
     n = cc.group_size(group)
     if n == 1 or n > 8 or not _fused_enabled() or not x.is_cuda or x.dtype != torch.bfloat16:
         return None
     if cc.get_backend(group) != "nccl" or (k % 8) or (n_out % 8) or (shard_rows * k) % 8:
         return None
     from .tp_fused import TPWorkspace
-    return TPWorkspace.get(group, shard_rows * k * 2, n * shard_rows * n_out * 2)
+    wide = max(k, n_out)
+    return TPWorkspace.get(group, shard_rows * wide * 2, n * shard_rows * wide * 2)
 
 
 def _mm(a, b, **kw):
@@ -85,14 +88,23 @@ class _ColumnParallel(torch.autograd.Function):
         x_shard, w = ctx.saved_tensors
         group = ctx.group
         dy = dy.contiguous()
-        x = _gather_tokens(x_shard, group)                 # re-gather instead of keeping the full activation
         dx = dw = None
-        if ctx.needs_input_grad[0]:
-            if dy.is_cuda and dy.dtype == torch.bfloat16:
-                dx_full = _mm(dy, w, b_mn=True)
-            else:
-                dx_full = dy @ w
-            dx = _scatter_sum_tokens(dx_full, group)
+        ws = _workspace(group, x_shard, x_shard.shape[0], x_shard.shape[1], w.shape[0])
+        if ws is not None and dy.shape[0] == x_shard.shape[0] * ws.n:
+            # fused backward: dx = reduce-scatter(dy W) inside the GEMM epilogue (the weight shard is
+            # transposed once so that the kernel sees a K-major operand); the token shards are
+            # re-gathered by peer pulls for the weight-gradient product
+            if ctx.needs_input_grad[0]:
+                dx = ws.gemm_rs(dy, w.t().contiguous())
+            x = ws.gather(x_shard.contiguous()) if ctx.needs_input_grad[1] else None
+        else:
+            x = _gather_tokens(x_shard, group)             # re-gather instead of keeping the full activation
+            if ctx.needs_input_grad[0]:
+                if dy.is_cuda and dy.dtype == torch.bfloat16:
+                    dx_full = _mm(dy, w, b_mn=True)
+                else:
+                    dx_full = dy @ w
+                dx = _scatter_sum_tokens(dx_full, group)
         if ctx.needs_input_grad[1]:
             if ctx.symm is not None and dy.is_cuda:
                 buf, i = ctx.symm
@@ -126,11 +138,23 @@ class _RowParallel(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy_shard):
         a, w = ctx.saved_tensors
-        dy = _gather_tokens(dy_shard.contiguous(), ctx.group)
         da = dw = None
-        cuda = dy.is_cuda and dy.dtype == torch.bfloat16
-        if ctx.needs_input_grad[0]:
-            da = _mm(dy, w, b_mn=True) if cuda else dy @ w
+        n = cc.group_size(ctx.group)
+        ws = _workspace(ctx.group, a, a.shape[0] // max(n, 1), a.shape[1], w.shape[0]) \
+            if a.shape[0] % max(n, 1) == 0 else None
+        if ws is not None:
+            # fused backward: da = all-gather(dy) W inside one kernel (transposed weight shard as the
+            # K-major operand); the gathered dy stays in the workspace's staging matrix and feeds the
+            # weight-gradient product directly
+            dy_shard = dy_shard.contiguous()
+            da = ws.ag_gemm(dy_shard, w.t().contiguous())
+            dy = ws.gathered(dy_shard.shape[0] * n, dy_shard.shape[1])
+            cuda = True
+        else:
+            dy = _gather_tokens(dy_shard.contiguous(), ctx.group)
+            cuda = dy.is_cuda and dy.dtype == torch.bfloat16
+            if ctx.needs_input_grad[0]:
+                da = _mm(dy, w, b_mn=True) if cuda else dy @ w
         if ctx.needs_input_grad[1]:
             if ctx.symm is not None and cuda:
                 buf, i = ctx.symm

@@ -30,6 +30,8 @@ def _lib():
         lib.hpb_ag_gemm.restype = ci
         lib.hpb_gemm_rs.argtypes = [vp, vp, pp, pp, vp, vp, ci, ci, ci, ci, ci, cu, cull, vp, ci, vp]
         lib.hpb_gemm_rs.restype = ci
+        lib.hpb_p2p_allgather.argtypes = [pp, pp, vp, ci, vp, ci, ci, cu, cull, vp, vp, ci, vp]
+        lib.hpb_p2p_allgather.restype = ci
         _bound = True
     return lib
 
@@ -81,6 +83,27 @@ class TPWorkspace:
                                 native.sm_count(self.device), native.stream(self.device))
         native.check(rc, "hpb_ag_gemm")
         return out
+
+    def gathered(self, rows: int, cols: int) -> torch.Tensor:
+        """The ``[rows, cols]`` matrix that the last :meth:`ag_gemm` / :meth:`gather` call assembled in
+        the local staging buffer (valid until the next such call on this workspace)."""
+        return self.staging[:rows * cols].view(rows, cols)
+
+    def gather(self, x_shard: torch.Tensor, limit_ns: int = DEFAULT_WAIT_NS) -> torch.Tensor:
+        """``concat_r(x_r)`` by peer pulls over NVLink (no product attached): the operand of a
+        weight-gradient GEMM whose contraction runs over the gathered rows."""
+        Ms, K = x_shard.shape
+        assert Ms * K * 2 <= self.shard_bytes and x_shard.dtype == torch.bfloat16 and (Ms * K) % 8 == 0
+        off = (self.ag_calls & 1) * self.shard_bytes
+        self.ag_calls += 1
+        self.symm.tensor(torch.bfloat16, Ms * K, off).view(Ms, K).copy_(x_shard)
+        seg = torch.tensor([[0, 0, Ms * K, 0]], dtype=torch.int64, device=self.device)
+        rc = _lib().hpb_p2p_allgather(self.symm.ptr_table(off), self.symm.pad_ptrs, seg.data_ptr(), 1,
+                                      self.staging.data_ptr(), self.rank, self.n, self.symm.next_epoch(), limit_ns,
+                                      self.status.data_ptr(), self.symm.done_counter.data_ptr(), 96,
+                                      native.stream(self.device))
+        native.check(rc, "hpb_p2p_allgather")
+        return self.gathered(self.n * Ms, K)
 
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, limit_ns: int = DEFAULT_WAIT_NS) -> torch.Tensor:
         """``reduce_scatter_rows(a[n*Ms, K] @ w[N, K].T)`` with the scatter fused into the GEMM epilogue."""

@@ -164,6 +164,72 @@ def test_fused_ag_gemm_and_gemm_rs_match_reference(tmp_path, world):
     assert torch.load(tmp_path / "tp.pt")["ok"]
 
 
+def _tp_bwd_worker(rank, world, port, tmp):
+    """Column- and row-parallel linears through autograd: all four backward products (fused
+    GEMM->reduce-scatter, peer-pull gather + wgrad, fused all-gather->GEMM, wgrad from the staged
+    gather) against the single-process formulas."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from hyper_parallel_b200.ops import native
+    from hyper_parallel_b200.parallel import tensor_parallel as tp
+    Ms, K, Ns = 256, 384, 320            # token rows per rank, hidden, output columns per rank
+    T = Ms * world
+    g = torch.Generator(device=dev).manual_seed(7)          # same seed everywhere: every rank sees all shards
+
+    def rnd(*shape, s=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * s).to(torch.bfloat16)
+    xs = [rnd(Ms, K) for _ in range(world)]
+    wcs = [rnd(Ns, K, s=0.05) for _ in range(world)]
+    gys = [rnd(T, Ns) for _ in range(world)]
+    as_ = [rnd(T, K) for _ in range(world)]
+    wrs = [rnd(Ns, K, s=0.05) for _ in range(world)]
+    gzs = [rnd(Ms, Ns) for _ in range(world)]
+    ok = True
+
+    def close(a, b, tol=1e-2):
+        return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-9)).item() < tol
+    for _ in range(2):                                      # twice: both parities of the workspace buffers
+        x = xs[rank].clone().requires_grad_()
+        wc = wcs[rank].clone().requires_grad_()
+        y = tp.column_parallel_linear(x, wc, dist.group.WORLD)
+        y.backward(gys[rank])
+        X = torch.cat(xs).float()
+        dX = sum(gys[r].float() @ wcs[r].float() for r in range(world))
+        ok &= close(y, X @ wcs[rank].float().t())
+        ok &= close(x.grad, dX[rank * Ms:(rank + 1) * Ms])
+        ok &= close(wc.grad, gys[rank].float().t() @ X)
+        a = as_[rank].clone().requires_grad_()
+        wr = wrs[rank].clone().requires_grad_()
+        z = tp.row_parallel_linear(a, wr, dist.group.WORLD)
+        z.backward(gzs[rank])
+        Z = sum(as_[r].float() @ wrs[r].float().t() for r in range(world))
+        dZ = torch.cat(gzs).float()
+        ok &= close(z, Z[rank * Ms:(rank + 1) * Ms], 2e-2)
+        ok &= close(a.grad, dZ @ wrs[rank].float())
+        ok &= close(wr.grad, dZ.t() @ as_[rank].float())
+    torch.cuda.synchronize()
+    native.check_status()
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"ok": bool(t.item())}, os.path.join(tmp, "tpb.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_backward_products_are_fused_and_correct(tmp_path, world):
+    _need(world)
+    import torch.multiprocessing as mp
+    from dist_utils import _free_port
+    mp.spawn(_tp_bwd_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert torch.load(tmp_path / "tpb.pt")["ok"]
+
+
 def _ep_worker(rank, world, port, tmp):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
