@@ -61,8 +61,24 @@ def _matmul_layout(op_name, x, w, w_is_out_in=False):
     return make(x, out_axes, partial)
 
 
+def _native_ok(*tensors) -> bool:
+    """Local operands that the hand-written tcgen05 GEMM takes: CUDA, bf16."""
+    import torch
+    return all(isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 for t in tensors)
+
+
 class MatMulExtDistributedOp(DistributedOp):
     """``torch.matmul`` / ``mm`` / ``bmm`` / ``@``."""
+
+    def get_expand_impl(self, func, output_layout, layouts, extra_args):
+        # the local product of two DTensors runs on this library's tcgen05 GEMM (forward, dgrad and
+        # wgrad) whenever the shards are bf16 CUDA matrices; anything else keeps the framework call
+        def impl(x, w, *args, **kwargs):
+            if not args and not kwargs and _native_ok(x, w) and w.dim() == 2 and x.dim() >= 2 and w.is_contiguous():
+                from ....ops import functional as Fn
+                return Fn.matmul(x, w)
+            return func(x, w, *args, **kwargs)
+        return impl
 
     def infer_layout(self, layouts, extra_args):
         self._check_partial_inputs(layouts)
@@ -91,15 +107,17 @@ class LinearDistributedOp(DistributedOp):
         return out
 
     def get_expand_impl(self, func, output_layout, layouts, extra_args):
-        if not output_layout.is_partial():
-            return None
         n = 1
-        for a, op in enumerate(output_layout.partial):
-            if op is not None:
-                n *= output_layout.mesh.mesh_shape[a]
-        if n == 1:
-            return None
+        if output_layout.is_partial():
+            for a, op in enumerate(output_layout.partial):
+                if op is not None:
+                    n *= output_layout.mesh.mesh_shape[a]
 
         def impl(x, w, bias=None):
-            return func(x, w, None if bias is None else bias / n)
+            b = bias if (bias is None or n == 1) else bias / n
+            if _native_ok(x, w) and w.dim() == 2:
+                # the local product runs on this library's tcgen05 GEMM (forward, dgrad and wgrad)
+                from ....ops import functional as Fn
+                return Fn.linear(x, w, b)
+            return func(x, w, b)
         return impl

@@ -20,6 +20,10 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD_DIR = HERE / "build"
 LIB_PATH = HERE / "libhpb200.so"
+# debug flavour: every kernel compiled with -DHPB_DEBUG_BOUNDS (index checks that record status
+# code 7 and skip the access); selected at run time with HPB_DEBUG_BOUNDS=1
+DEBUG_BUILD_DIR = HERE / "build_dbg"
+DEBUG_LIB_PATH = HERE / "libhpb200_dbg.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -49,17 +53,26 @@ def sources():
     return sorted(CSRC.glob("*.cu"))
 
 
-def is_current() -> bool:
-    stamp = BUILD_DIR / "stamp"
-    if not LIB_PATH.exists() or not stamp.exists():
+def lib_path(debug_bounds: bool = False) -> Path:
+    return DEBUG_LIB_PATH if debug_bounds else LIB_PATH
+
+
+def is_current(debug_bounds: bool = False) -> bool:
+    stamp = (DEBUG_BUILD_DIR if debug_bounds else BUILD_DIR) / "stamp"
+    if not lib_path(debug_bounds).exists() or not stamp.exists():
         return False
-    return stamp.read_text().strip() == _digest(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")))
+    return stamp.read_text().strip() == _digest(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) +
+                                                list(CSRC.glob("*.h")))
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``libhpb200.so``."""
-    if not force and is_current():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libhpb200.so`` (``debug_bounds``: the
+    ``-DHPB_DEBUG_BOUNDS`` flavour ``libhpb200_dbg.so``)."""
+    if not force and is_current(debug_bounds):
+        return lib_path(debug_bounds)
+    BUILD_DIR = DEBUG_BUILD_DIR if debug_bounds else globals()["BUILD_DIR"]
+    LIB_PATH = lib_path(debug_bounds)
+    extra = ["-DHPB_DEBUG_BOUNDS"] if debug_bounds else []
     BUILD_DIR.mkdir(exist_ok=True)
     nvcc = _nvcc()
     srcs = sources()
@@ -67,7 +80,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(src: Path) -> Path:
         obj = BUILD_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         log_lines.append(f"$ {' '.join(cmd)}\n{r.stdout}{r.stderr}")
         if r.returncode != 0:
@@ -82,12 +95,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     (BUILD_DIR / "ptxas.log").write_text("\n".join(log_lines))
     (BUILD_DIR / "stamp").write_text(
-        _digest(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh"))))
+        _digest(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))))
     if verbose:
         print("\n".join(log_lines))
     return LIB_PATH
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug_bounds="--debug-bounds" in sys.argv)
     print(path)

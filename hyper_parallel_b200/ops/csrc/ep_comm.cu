@@ -147,6 +147,9 @@ ep_dispatch_kernel(const DispatchParams p) {
     }
     token = __shfl_sync(0xffffffffu, token, 0);
     scale = __shfl_sync(0xffffffffu, scale, 0);
+    if (!HPB_BOUNDS_OK(token >= 0 && token < p.T && j >= 0 && j < p.T * p.k && slot < p.cap_rows, p.status,
+                       0x100000 | slot))
+      continue;
     const uint4* src =
         reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x_stage.ptr[s]) +
                                        static_cast<long long>(token) * p.H);
@@ -246,17 +249,23 @@ ep_combine_kernel(const CombineParams p) {
     if (threadIdx.x < p.k) {
       const int pair = t * p.k + threadIdx.x;
       const int e = static_cast<int>(p.topk_idx[pair]);
-      const int slot = s_dst[e] + (p.sorted_pos[pair] - s_myoff[e]);
-      s_row[threadIdx.x] = reinterpret_cast<const uint4*>(
-          reinterpret_cast<const __nv_bfloat16*>(p.out.ptr[e / El]) + static_cast<long long>(slot) * p.H);
-      s_w[threadIdx.x] = p.weights ? p.weights[pair] : 1.f;
+      const bool e_ok = HPB_BOUNDS_OK(e >= 0 && e < p.E, p.status, 0x200000 | pair);
+      const int slot = e_ok ? s_dst[e] + (p.sorted_pos[pair] - s_myoff[e]) : -1;
+      if (e_ok && HPB_BOUNDS_OK(slot >= 0, p.status, 0x300000 | pair)) {
+        s_row[threadIdx.x] = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(p.out.ptr[e / El]) + static_cast<long long>(slot) * p.H);
+        s_w[threadIdx.x] = p.weights ? p.weights[pair] : 1.f;
+      } else {        // only reachable in the debug build: the row is skipped (treated as zeros)
+        s_row[threadIdx.x] = nullptr;
+        s_w[threadIdx.x] = 0.f;
+      }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < vec_per_row; c += blockDim.x) {
       uint4 v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        if (j < p.k) v[j] = s_row[j][c];
+        if (j < p.k) v[j] = s_row[j] != nullptr ? s_row[j][c] : make_uint4(0u, 0u, 0u, 0u);
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;

@@ -195,6 +195,11 @@ __device__ __forceinline__ bool gather_loop(const GatherParams& g, int ct, volat
       if (v < v_end) {
         const long long e = v * 8;
         const int o = o0 + (e >= bnd ? 1 : 0);
+        if (!HPB_BOUNDS_OK(o >= 0 && o < g.n && e - static_cast<long long>(o) * g.shard_elems + 8 <= g.shard_elems,
+                           status, 0x500000 | o)) {
+          buf[u] = make_uint4(0u, 0u, 0u, 0u);
+          continue;
+        }
         buf[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(g.shard[o]) +
                                                  (e - static_cast<long long>(o) * g.shard_elems));
       }

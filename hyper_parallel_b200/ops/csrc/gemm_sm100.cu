@@ -98,6 +98,7 @@ __device__ __forceinline__ TileInfo tile_info(int t, const GemmParams& p) {
   } else {
     tile_coords(t, num_m, num_n, m_blk, n_blk);
     ti.group = p.mode == 1 ? p.block_group[m_blk] : 0;
+    if (!HPB_BOUNDS_OK(ti.group < p.num_groups, p.status, 0x400000 | m_blk)) ti.group = -1;   // debug build: skip
     ti.k_row0 = 0;
     // a negative group marks an unused row block of an over-allocated (capacity-sized) operand:
     // no loads, no products, and the epilogue leaves the output rows alone

@@ -25,6 +25,7 @@ enum StatusCode : int {
   kTimeoutTmemEmpty = 4,
   kTimeoutPeerFlag = 5,
   kBadArgument = 6,
+  kOutOfBounds = 7,      // an index check of the debug build (-DHPB_DEBUG_BOUNDS) failed; the access was skipped
 };
 
 __device__ __forceinline__ void report_error(int* status, int code, int detail) {
@@ -32,6 +33,17 @@ __device__ __forceinline__ void report_error(int* status, int code, int detail) 
     if (atomicCAS(status, 0, code) == 0) status[1] = detail;
   }
 }
+
+// Index checks of the debug build flavour (-DHPB_DEBUG_BOUNDS, the stand-in for compute-sanitizer's
+// memcheck): a failed check records kOutOfBounds with a detail word in the status word and evaluates
+// to false so that the caller SKIPS the access; nothing traps.  In the normal build the checks cost
+// nothing.
+#ifdef HPB_DEBUG_BOUNDS
+#define HPB_BOUNDS_OK(cond, status, detail) \
+  ((cond) ? true : (::hpb::report_error((status), ::hpb::kOutOfBounds, static_cast<int>(detail)), false))
+#else
+#define HPB_BOUNDS_OK(cond, status, detail) (true)
+#endif
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;

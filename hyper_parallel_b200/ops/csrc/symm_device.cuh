@@ -32,6 +32,15 @@ __device__ __forceinline__ void report(int* status, int code, int detail) {
   if (status && atomicCAS(status, 0, code) == 0) status[1] = detail;
 }
 
+// Debug-build index checks (see sm100_common.cuh): record code 7 and skip the access.
+#ifndef HPB_BOUNDS_OK
+#ifdef HPB_DEBUG_BOUNDS
+#define HPB_BOUNDS_OK(cond, status, detail) ((cond) ? true : (::hpb::report((status), 7, static_cast<int>(detail)), false))
+#else
+#define HPB_BOUNDS_OK(cond, status, detail) (true)
+#endif
+#endif
+
 // Signal every peer: "rank `rank` reached `epoch` on `slot`".
 __device__ __forceinline__ void signal_peers(const PeerTable& pads, int rank, int n, int slot,
                                              uint32_t epoch) {

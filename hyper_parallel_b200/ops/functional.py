@@ -16,7 +16,7 @@ import torch.nn.functional as F
 from . import native
 
 __all__ = [
-    "gemm", "linear", "rmsnorm", "add_rmsnorm", "swiglu", "rope_", "apply_rope",
+    "gemm", "linear", "matmul", "rmsnorm", "add_rmsnorm", "swiglu", "rope_", "apply_rope",
     "cross_entropy_fwd_bwd", "fused_cross_entropy", "adamw_step_",
 ]
 
@@ -174,6 +174,37 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if hs is not None and hs[0].gather_pending(hs[1]):
         hs[0].materialize(hs[1])
     return F.linear(x, w, bias)
+
+
+class _MatMul(torch.autograd.Function):
+    """y = x W with W stored [K, N]: forward, dgrad and wgrad on the tcgen05 GEMM, no transposes."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        y = torch.empty(*x.shape[:-1], w.shape[1], dtype=torch.bfloat16, device=x.device)
+        gemm(x2, w, b_mn=True, out=y.view(-1, w.shape[1]))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm(dy2, w).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = gemm(x2, dy2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w`` for ``x[..., K]`` and a 2-D ``w[K, N]``; bf16 CUDA operands use the tcgen05 GEMM."""
+    if (native.use_native(x) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
+            and x.dim() >= 2 and w.is_contiguous()):
+        return _MatMul.apply(x, w)
+    return torch.matmul(x, w)
 
 
 # ------------------------------------------------------------------ RMSNorm --

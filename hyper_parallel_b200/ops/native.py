@@ -56,7 +56,11 @@ def lib() -> ctypes.CDLL:
         return _lib
     with _lock:
         if _lib is None:
-            path = _build.LIB_PATH
+            # HPB_DEBUG_BOUNDS=1: the flavour whose kernels check their indices (status code 7)
+            debug = os.environ.get("HPB_DEBUG_BOUNDS", "0") == "1"
+            path = _build.lib_path(debug)
+            if debug and not path.exists():
+                _build.build(debug_bounds=True)
             if not path.exists():
                 if os.environ.get("HPB_BUILD_ON_IMPORT", "0") == "1":
                     _build.build()
@@ -125,6 +129,7 @@ _STATUS_TEXT = {
     4: "timeout waiting for accumulator drain (tmem empty)",
     5: "timeout waiting for a peer flag",
     6: "bad argument seen on device",
+    7: "index out of bounds caught by a debug-build check (the access was skipped)",
 }
 
 

@@ -39,6 +39,8 @@ from ..collectives import cc
 from ..ops import native
 
 _PAD_BYTES = 4096          # 64 slots x 16 ranks x 4 B
+_CANARY_BYTES = 256        # guard words in front of the data region and behind the signal pad
+_CANARY = 0x5A
 DEFAULT_WAIT_NS = 2_000_000_000
 
 # signal-pad slots with a fixed meaning (every kernel family uses its own slots of its own region)
@@ -171,7 +173,8 @@ class SymmetricMemory:
         self._mc = None                       # (mc handle, mc ptr)
         self.mc_base: Optional[int] = None    # multicast address of the buffers (None: no multicast)
         self.transport = "ipc"
-        total = self.nbytes + _PAD_BYTES
+        # [canary | data (nbytes) | signal pad | canary]; every pointer handed out is relative to the data
+        total = _CANARY_BYTES + self.nbytes + _PAD_BYTES + _CANARY_BYTES
         want_vmm = os.environ.get("HPB_SYMM", "vmm") != "ipc" and self.world > 1
         peer_bases = None
         if want_vmm:
@@ -179,7 +182,15 @@ class SymmetricMemory:
         if peer_bases is None:
             peer_bases = self._init_ipc(total)
         self._holder = _Holder(self._base, self._total)
-        self._bytes = torch.as_tensor(self._holder, device=self.device)
+        raw = torch.as_tensor(self._holder, device=self.device)
+        self._guards = (raw[:_CANARY_BYTES], raw[_CANARY_BYTES + self.nbytes + _PAD_BYTES:
+                                                 2 * _CANARY_BYTES + self.nbytes + _PAD_BYTES])
+        for g in self._guards:
+            g.fill_(_CANARY)
+        self._bytes = raw[_CANARY_BYTES:_CANARY_BYTES + self.nbytes + _PAD_BYTES]
+        peer_bases = [b + _CANARY_BYTES for b in peer_bases]
+        if self.mc_base is not None:
+            self.mc_base += _CANARY_BYTES
         arr = ctypes.c_void_p * max(self.world, 1)
         self.ptrs = arr(*peer_bases)
         self.pad_ptrs = arr(*[b + self.nbytes for b in peer_bases])
@@ -363,6 +374,15 @@ class SymmetricMemory:
         native.check(self.lib.hpb_symm_signal(self.pad_ptrs, self.rank, self.world, slot, value,
                                               native.stream(self.device)), "hpb_symm_signal")
 
+    def check_canaries(self) -> None:
+        """Raise if anything wrote in front of the data region or behind the signal pad of the LOCAL
+        buffer (a peer's or an own kernel running past the end of a symmetric region).  Synchronises."""
+        for name, g in zip(("front", "back"), self._guards):
+            bad = (g != _CANARY).nonzero()
+            if bad.numel():
+                raise RuntimeError(f"symmetric memory guard ({name}) overwritten at byte {int(bad[0])} of "
+                                   f"{_CANARY_BYTES} on rank {self.rank}")
+
     def reset_counters(self) -> None:
         """Zero the last-CTA counters (after a kernel reported a bounded-wait expiry they may be off)."""
         self.done_counter.zero_()
@@ -378,6 +398,7 @@ class SymmetricMemory:
             if self.world > 1 and dist.is_initialized():
                 dist.barrier(group=self.group)
             self._bytes = None
+            self._guards = ()
             if self.transport == "vmm":
                 own = self._vmm_maps[0]
                 if self._mc is not None:

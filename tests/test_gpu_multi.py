@@ -50,6 +50,11 @@ def _train(rank, world, fused, steps, out):
         losses.append(loss.item())
     native.check_status()
     torch.cuda.synchronize()
+    # nothing wrote outside the symmetric regions (guard words in front of and behind every buffer)
+    for m in model.modules():
+        if "hsdp_scheduler" in m.__dict__:
+            for buf in m.hsdp_scheduler.hsdp_state.symm_buffers:
+                buf.symm.check_canaries()
     # gather the final weights of one parameter for comparison
     w = model.layers[0].wqkv.detach().float().contiguous()
     parts = [torch.empty_like(w) for _ in range(world)]
@@ -147,6 +152,7 @@ def _tp_worker(rank, world, port, tmp):
         ok &= ((z.float() - refz).norm() / refz.norm()).item() < 1e-2
     torch.cuda.synchronize()
     native.check_status()
+    ws.symm.check_canaries()
     t = torch.tensor([1.0 if ok else 0.0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:
