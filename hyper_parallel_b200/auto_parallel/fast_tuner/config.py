@@ -86,7 +86,9 @@ class TunerConfig:
     yaml_path: Optional[str] = None
     shell_path: Optional[str] = None
     model_json: Optional[str] = None
-    trainer_path: Optional[str] = None   # torchtitan_path / mindformers_dir / mindspeed_path
+    trainer_path: Optional[str] = None   # torchtitan_path / mindformers_dir / mindspeed_path; None = built-in trainer
+    profile_timeout: int = 1800          # seconds per profiled candidate
+    profile_port: int = 29591            # rendezvous port of the first profile run
 
     @staticmethod
     def from_json(path: str) -> "TunerConfig":

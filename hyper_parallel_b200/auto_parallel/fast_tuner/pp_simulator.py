@@ -5,6 +5,14 @@ given per-(stage, chunk) forward / backward times and a p2p latency it replays t
 compute order with data dependencies and reports the makespan, per-stage busy time, bubble
 ratio and the peak number of live micro-batch activations per stage.  The compute orders come
 from the same generators the runtime uses, so what is simulated is what runs.
+
+Communication is modelled as blocks of its own (reference pp_simulator.py:820-1397 draws them as
+separate lanes): an activation or gradient that crosses ranks occupies the sender's p2p lane for
+``p2p`` time units, transfers of one sender are serialised in issue order, and the consumer can start
+when the block ends.  Memory is tracked per stage as a timeline: ``static_bytes[s]`` plus
+``act_bytes[v]`` for every micro-batch whose forward on virtual stage ``v`` has started and whose
+backward has not finished.  ``render_text`` draws the lanes as text, ``timeline_rows`` gives them as
+rows for a CSV file.
 """
 from __future__ import annotations
 
@@ -22,6 +30,9 @@ class SimResult:
     bubble_ratio: float
     peak_live: List[int]
     timeline: Dict[int, list]
+    comm: Dict[int, list] = None            # per sending stage: (start, end, "F"|"B", micro, from_v, to_stage)
+    mem_timeline: Dict[int, list] = None    # per stage: (time, bytes) after every change
+    peak_bytes: List[float] = None
 
 
 def compute_order(kind: str, micro: int, stages: int, chunks: int = 1) -> Dict[int, List[MetaStep]]:
@@ -32,9 +43,19 @@ def compute_order(kind: str, micro: int, stages: int, chunks: int = 1) -> Dict[i
 
 
 def simulate(order: Dict[int, List[MetaStep]], fwd: Sequence[float], bwd: Sequence[float], stages: int,
-             p2p: float = 0.0) -> SimResult:
-    """``fwd[v]`` / ``bwd[v]``: time of one micro-batch on virtual stage ``v``."""
+             p2p: float = 0.0, act_bytes: Sequence[float] = None, static_bytes: Sequence[float] = None) -> SimResult:
+    """``fwd[v]`` / ``bwd[v]``: time of one micro-batch on virtual stage ``v``; ``p2p``: duration of one
+    stage-boundary transfer; ``act_bytes[v]``: activation bytes one micro-batch keeps on virtual stage
+    ``v`` between its forward and its backward; ``static_bytes[s]``: weights + optimizer state of stage ``s``."""
     n_virtual = len(fwd)
+    act = list(act_bytes) if act_bytes is not None else [0.0] * n_virtual
+    static = list(static_bytes) if static_bytes is not None else [0.0] * stages
+    lane_free = [0.0] * stages                       # when the p2p lane of a stage is free again
+    arrive: Dict[tuple, float] = {}                  # (kind, micro, v) -> time its output reached the next rank
+    comm = {s: [] for s in range(stages)}
+    mem = list(static)
+    mem_tl = {s: [(0.0, static[s])] for s in range(stages)}
+    peak_b = list(static)
     F, B = MetaStepType.FWD, MetaStepType.BWD
     finish: Dict[tuple, float] = {}
     clock = [0.0] * stages
@@ -59,12 +80,28 @@ def simulate(order: Dict[int, List[MetaStep]], fwd: Sequence[float], bwd: Sequen
                     break
                 ready = 0.0
                 for d in deps:
-                    same_rank = (d[2] % stages) == s
-                    ready = max(ready, finish[d] + (0.0 if same_rank else p2p))
+                    src = d[2] % stages
+                    if src == s or p2p <= 0.0 or d[2] == v:
+                        ready = max(ready, finish[d])
+                        continue
+                    if d not in arrive:
+                        # the transfer is a block on the sender's p2p lane, issued when the data exists
+                        t0 = max(finish[d], lane_free[src])
+                        lane_free[src] = t0 + p2p
+                        arrive[d] = t0 + p2p
+                        comm[src].append((t0, t0 + p2p, d[0].name[0], d[1], d[2], s))
+                    ready = max(ready, arrive[d])
                 start = max(clock[s], ready)
                 dur = fwd[v] if st.type == F else bwd[v]
                 clock[s] = start + dur
                 finish[(st.type, m, v)] = clock[s]
+                if st.type == F:
+                    mem[s] += act[v]
+                    mem_tl[s].append((start, mem[s]))
+                    peak_b[s] = max(peak_b[s], mem[s])
+                else:
+                    mem[s] -= act[v]
+                    mem_tl[s].append((clock[s], mem[s]))
                 busy[s] += dur
                 live[s] += 1 if st.type == F else -1
                 peak[s] = max(peak[s], live[s])
@@ -76,4 +113,42 @@ def simulate(order: Dict[int, List[MetaStep]], fwd: Sequence[float], bwd: Sequen
             raise RuntimeError("simulated schedule deadlocks")
     makespan = max(clock)
     bubble = 1.0 - sum(busy) / (makespan * stages) if makespan > 0 else 0.0
-    return SimResult(makespan, busy, bubble, peak, timeline)
+    return SimResult(makespan, busy, bubble, peak, timeline, comm, mem_tl, peak_b)
+
+
+def timeline_rows(res: SimResult) -> List[list]:
+    """``[lane, stage, start, end, kind, micro, virtual stage]`` rows (compute and p2p lanes) for a CSV."""
+    rows = []
+    for s, items in res.timeline.items():
+        rows += [["compute", s, round(a, 6), round(b, 6), k, m, v] for a, b, k, m, v in items]
+    for s, items in (res.comm or {}).items():
+        rows += [["p2p", s, round(a, 6), round(b, 6), k, m, v] for a, b, k, m, v, _dst in items]
+    return sorted(rows, key=lambda r: (r[1], r[0], r[2]))
+
+
+def render_text(res: SimResult, width: int = 100) -> str:
+    """The schedule as text: one compute lane per stage (forward = micro-batch digit, backward = letter),
+    one p2p lane per stage ('>' forward activation, '<' gradient), and the peak memory per stage."""
+    if res.makespan <= 0:
+        return ""
+    scale = width / res.makespan
+    out = []
+    for s in sorted(res.timeline):
+        lane = [" "] * width
+        for a, b, k, m, _v in res.timeline[s]:
+            ch = str(m % 10) if k == "FWD" else chr(ord("a") + m % 26)
+            for x in range(int(a * scale), max(int(b * scale), int(a * scale) + 1)):
+                if x < width:
+                    lane[x] = ch
+        out.append(f"stage {s} |" + "".join(lane) + "|")
+        if res.comm and res.comm.get(s):
+            lane = [" "] * width
+            for a, b, k, _m, _v, _d in res.comm[s]:
+                for x in range(int(a * scale), max(int(b * scale), int(a * scale) + 1)):
+                    if x < width:
+                        lane[x] = ">" if k == "F" else "<"
+            out.append(f"  p2p {s} |" + "".join(lane) + "|")
+    if res.peak_bytes and any(res.peak_bytes):
+        out.append("peak bytes per stage: " + ", ".join(f"{b:.3g}" for b in res.peak_bytes))
+    out.append(f"makespan {res.makespan:.4g}, bubble {res.bubble_ratio:.3f}")
+    return "\n".join(out)

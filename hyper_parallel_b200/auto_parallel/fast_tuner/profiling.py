@@ -93,11 +93,18 @@ def write_profile_config(c: Config, spec: ModelSpec, out_dir: str, idx: int) -> 
     return path
 
 
-def launch_profile(config_path: str, trainer: str, nproc: int, timeout: int = 1800, env=None) -> int:
+BUILTIN_TRAINER = "hyper_parallel_b200.auto_parallel.fast_tuner.profile_trainer"
+
+
+def launch_profile(config_path: str, trainer: Optional[str], nproc: int, timeout: int = 1800, env=None,
+                   port: int = 29591) -> int:
     """Run the trainer (``python -m torch.distributed.run ... trainer --profile-config path``) in its own
-    process group so that a timeout can end exactly the processes that were started."""
+    process group so that a timeout can end exactly the processes that were started.  ``trainer`` is a
+    script path, a module name, or ``None`` for this package's own :mod:`profile_trainer`."""
+    trainer = trainer or BUILTIN_TRAINER
+    target = [trainer] if trainer.endswith(".py") else ["-m", trainer]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", "29591", trainer, "--profile-config", config_path]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), *target, "--profile-config", config_path]
     proc = subprocess.Popen(cmd, env={**os.environ, **(env or {})}, start_new_session=True)
     try:
         return proc.wait(timeout=timeout)

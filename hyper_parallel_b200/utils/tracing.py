@@ -57,14 +57,18 @@ class CudaTimer:
         self.pending.append((key, s, e))
 
     def start(self, key: str):
-        ev = torch.cuda.Event(enable_timing=True) if self.cuda else None
-        if ev is not None:
-            ev.record()
+        if not self.cuda:
+            import time
+            return (key, time.perf_counter())          # CPU runs (the gloo tests): host clock
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
         return (key, ev)
 
     def stop(self, token) -> None:
         key, s = token
-        if s is None:
+        if not self.cuda:
+            import time
+            self._add(key, (time.perf_counter() - s) * 1e3)
             return
         e = torch.cuda.Event(enable_timing=True)
         e.record()

@@ -1,4 +1,5 @@
 """Fast-Tuner: space sizes, rule pruning, memory model, simulator, balancer, CLI dry-run."""
+import csv
 import json
 import os
 
@@ -93,3 +94,28 @@ def test_cli_dryrun_ranks_candidates(tmp_path):
     assert os.path.exists(tmp_path / "out" / "pipeline_output" / "ranked_configs.csv")
     cfg.alg_phase = 1
     assert "summary" in taylor_search_tool(cfg)[0]
+
+
+def test_search_profile_balance_csv_end_to_end(tmp_path):
+    """The whole loop without --dryrun on two CPU ranks: search -> the built-in trainer profiles a
+    shrunk candidate (gloo, tiny model, LayerTimer records) -> the balancer uses those times -> the
+    survivors are replayed in the simulator -> ranked CSV with the re-check columns."""
+    tiny = ModelSpec(num_layers=8, hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, num_kv_heads=2,
+                     vocab_size=256, seq_length=32, world_size=2, global_batch_size=8)
+    mj = tmp_path / "model.json"
+    mj.write_text(json.dumps({k: getattr(tiny, k) for k in tiny.__dataclass_fields__}))
+    cfg = TunerConfig(rank_num=2, gbs=8, gpus_per_node=2, nnodes=1, output_path=str(tmp_path / "out"), dryrun=False,
+                      model_json=str(mj), strategy=Strategy(EP=False, CP=False, TP=False), profile_timeout=300,
+                      profile_port=29711)
+    ranked = taylor_search_tool(cfg, top_k=60)
+    out = tmp_path / "out"
+    summary = json.loads((out / "search_summary.json").read_text())
+    assert summary.get("profiled", "").startswith("profile_")
+    recs = [json.loads(l) for l in (out / "profile" / "profile_000.records.jsonl").read_text().splitlines()]
+    assert {r["module"] for r in recs} >= {"dense", "head", "embed"} and all(r["ms"] >= 0 for r in recs)
+    assert any(r["module"] == "dense" and r["ms"] > 0 for r in recs)
+    rows = list(csv.reader(open(out / "pipeline_output" / "ranked_configs.csv")))
+    assert rows[0][-3:] == ["sim_bubble", "sim_peak_gib", "check"] and len(rows) == len(ranked) + 1
+    piped = [e for e in ranked if e["pp"] > 1]
+    assert piped and all(e["check"] == "ok" and 0.0 <= e["sim_bubble"] < 1.0 for e in piped)
+    assert any(f.name.startswith("sim_") for f in (out / "pipeline_output").iterdir())
