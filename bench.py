@@ -35,7 +35,29 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--batch-per-gpu", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override the layer count")
+    ap.add_argument("--config", default="hsdp", choices=["hsdp", "tp_hsdp", "moe_ep", "pp"],
+                    help="hsdp: the headline (Llama-3-8B, hsdp level3); tp_hsdp: Llama-2-13B TP=4 (+SP) x hsdp 2, "
+                         "global batch 8; moe_ep: DeepSeek-V3 4 layers, 256 experts, EP over all ranks, fp8; "
+                         "pp: Llama-3-8B PP=4 x TP=2, 16 micro-batches")
+    ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"], help="--config pp only")
     return ap.parse_args()
+
+
+def other_config_argv(args, world):
+    """Command line of benchmarks/train_configs.py for the non-headline configurations, as the
+    benchmark specification names them (smaller world sizes shrink the parallel degrees, not the model)."""
+    base = ["--steps", str(args.steps), "--warmup", str(args.warmup), "--seq-len", str(args.seq_len)]
+    if args.layers is not None:
+        base += ["--layers", str(args.layers)]
+    if args.config == "tp_hsdp":
+        tp = min(4, world)
+        dp = max(world // tp, 1)
+        return ["--config", "tp_hsdp", "--tp", str(tp), "--batch", str(max(8 // dp, 1))] + base
+    if args.config == "moe_ep":
+        return ["--config", "moe_ep", "--batch", "1", "--fp8", "1"] + (base if args.layers else base + ["--layers", "4"])
+    tp = 2 if world >= 4 else 1
+    return ["--config", "pp", "--tp", str(tp), "--pp", str(max(world // tp, 1)), "--micro", "16", "--batch", "1",
+            "--schedule", args.schedule, "--vpp", "2"] + base
 
 
 def dist_env():
@@ -191,15 +213,30 @@ def run_ours(args):
 
 def main():
     args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         try:
             from reference_arm import run_reference
+            from reference_configs import run_reference_config
         except Exception as e:  # noqa: BLE001
             if int(os.environ.get("RANK", "0")) == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"reference harness failed to import: {e}"}))
             return
-        run_reference(args)
+        if args.config == "hsdp":
+            run_reference(args)
+        else:
+            run_reference_config(args, other_config_argv(args, world))
+        return
+    if args.config != "hsdp":
+        sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+        import train_configs
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29571")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("LOCAL_RANK", "0")
+        train_configs.main(other_config_argv(args, world))
         return
     run_ours(args)
 

@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 
-def parse():
+def parse(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", required=True, choices=["tp_hsdp", "moe_ep", "pp"])
     ap.add_argument("--steps", type=int, default=5)
@@ -43,10 +43,15 @@ def parse():
     ap.add_argument("--micro", type=int, default=8)
     ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"])
     ap.add_argument("--experts", type=int, default=None)
-    return ap.parse_args()
+    ap.add_argument("--fp8", type=int, default=1, help="moe_ep: fp8 block-scaled forward GEMMs (1) or bf16 (0)")
+    return ap.parse_args(argv)
 
 
-def timed_steps(step, args, dev):
+def timed_steps(step, args, dev, host=None):
+    """Device-timed loop over ``step(i)``; with ``host`` (pinned token batches) also the end-to-end loop
+    ``step(i, tokens copied from the host in this step)`` + a device->host read of the result.  Returns
+    ``(ms per step, last result, clocks, end-to-end ms per step or None)``."""
+    import time
     from hyper_parallel_b200.ops import native
     from hyper_parallel_b200.utils.clocks import ClockSampler
     for i in range(args.warmup):
@@ -63,9 +68,24 @@ def timed_steps(step, args, dev):
         dist.barrier()
         torch.cuda.synchronize()
     native.check_status()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    e2e = None
+    if host is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        f0.record()
+        for i in range(args.steps):
+            tok = host[args.warmup + i].to(dev, non_blocking=True)
+            _ = float(step(args.warmup + i, tok).detach())
+        f1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e2e = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3) / args.steps
+        native.check_status()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps, e2e or 0.0], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t.item(), out, clocks.summary()
+    return t[0].item(), out, clocks.summary(), (t[1].item() if host is not None else None)
 
 
 def run_tp_hsdp(args, rank, world, dev):
@@ -89,21 +109,25 @@ def run_tp_hsdp(args, rank, world, dev):
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
     dp_rank = rank // tp
     g = torch.Generator().manual_seed(dp_rank)
-    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1), generator=g).to(dev)
+    host = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1),
+                         generator=g).pin_memory()
+    toks = host.to(dev)
 
-    def step(i):
+    def step(i, tok=None):
+        tok = toks[i] if tok is None else tok
         model.zero_grads()
-        loss = model(toks[i, :, :-1], toks[i, :, 1:])
+        loss = model(tok[:, :-1], tok[:, 1:])
         loss.backward()
         hp.hsdp_sync_stream()
         opt.step()
         return loss
 
-    ms, loss, clocks = timed_steps(step, args, dev)
+    ms, loss, clocks, e2e = timed_steps(step, args, dev, host)
     tokens = dp * args.batch * args.seq_len
     return {"config": {"model": "llama2_13b", "layers": cfg.num_layers, "parallelism": f"tp{tp}(+sp) x hsdp{dp} level3",
-                       "global_batch": dp * args.batch, "seq_len": args.seq_len,
-                       "fused_tp": os.environ.get("HPB_FUSED_TP", "1") != "0"},
+                       "global_batch": dp * args.batch, "seq_len": args.seq_len},
+            "arm": {"fused_tp": os.environ.get("HPB_FUSED_TP", "1") != "0"},
+            "e2e_ms": e2e, "h2d_bytes": host[0].numel() * host.element_size(),
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(loss.detach()), "clocks": clocks,
             "mfu_flops_per_token": cfg.flops_per_token(args.seq_len)}
 
@@ -117,37 +141,45 @@ def run_moe_ep(args, rank, world, dev):
         cfg.num_layers = args.layers
     if args.experts:
         cfg.n_routed_experts = args.experts
+    cfg.fp8 = bool(args.fp8)
     model = DeepSeekV3(cfg, ep_group=dist.group.WORLD if world > 1 else None, device=dev)
     model.init_weights()
+    # the non-expert parameters are data parallel over the expert-parallel ranks: hsdp (level3, full
+    # shard) on them; the experts are owned by their rank and left alone (MoE marks them hsdp_ignore)
+    if world > 1:
+        kw = dict(shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=True, comm_async=True,
+                  grad_scale=1.0 / world)
+        for layer in model.layers:
+            hp.hsdp(layer, **kw)
+        hp.hsdp(model, **kw)
     opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
-    # non-expert parameters are replicated over the expert-parallel ranks: plain data parallelism
-    from hyper_parallel_b200.models.deepseek_v3 import MoE
-    experts = {id(p) for m in model.modules() if isinstance(m, MoE) for p in (m.w_gate_up, m.w_down)}
-    shared = [p for p in model.parameters() if id(p) not in experts]
+    if world > 1:
+        opt.fuse_into_backward(model)
     g = torch.Generator().manual_seed(rank)
-    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1), generator=g).to(dev)
+    host = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, args.batch, args.seq_len + 1),
+                         generator=g).pin_memory()
+    toks = host.to(dev)
 
-    def step(i):
+    def step(i, tok=None):
+        tok = toks[i] if tok is None else tok
+        if world > 1:
+            model.zero_grads()
         opt.zero_grad(set_to_none=True)
-        loss = model(toks[i, :, :-1], toks[i, :, 1:])
+        loss = model(tok[:, :-1], tok[:, 1:])
         loss.backward()
         if world > 1:
-            flat = torch.cat([p.grad.reshape(-1) for p in shared if p.grad is not None])
-            dist.all_reduce(flat)
-            flat.div_(world)
-            o = 0
-            for p in shared:
-                if p.grad is not None:
-                    p.grad.copy_(flat[o:o + p.numel()].view_as(p))
-                    o += p.numel()
+            hp.hsdp_sync_stream()
         opt.step()
         return loss
 
-    ms, loss, clocks = timed_steps(step, args, dev)
+    ms, loss, clocks, e2e = timed_steps(step, args, dev, host)
     tokens = world * args.batch * args.seq_len
     return {"config": {"model": "deepseek_v3", "layers": cfg.num_layers, "experts": cfg.n_routed_experts,
-                       "parallelism": f"ep{world} (+dp{world} on shared weights)", "global_batch": world * args.batch,
-                       "seq_len": args.seq_len},
+                       "parallelism": f"ep{world} + hsdp level3 x{world} on the non-expert parameters",
+                       "global_batch": world * args.batch, "seq_len": args.seq_len,
+                       "precision": "fp8 e4m3 block-scaled forward GEMMs (1x128 / 128x128), bf16 master weights"
+                       if cfg.fp8 else "bf16"},
+            "e2e_ms": e2e, "h2d_bytes": host[0].numel() * host.element_size(),
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(loss.detach()), "clocks": clocks,
             "mfu_flops_per_token": cfg.flops_per_token(args.seq_len)}
 
@@ -244,18 +276,20 @@ def run_pp(args, rank, world, dev):
     params = [p for m in mods for p in m.parameters()]
     opt = FusedAdamW(params, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
     g = torch.Generator().manual_seed(0)
-    toks = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, B * args.micro, S + 1), generator=g).to(dev)
+    host = torch.randint(0, cfg.vocab_size, (args.warmup + args.steps, B * args.micro, S + 1), generator=g).pin_memory()
+    toks = host.to(dev)
     last_mod = mods[-1] if mods[-1].last else None
 
-    def step(i):
+    def step(i, tok=None):
+        tok = toks[i] if tok is None else tok
         opt.zero_grad(set_to_none=True)
         if last_mod is not None:
-            last_mod.targets = list(toks[i, :, 1:].chunk(args.micro))
-        out = sched.run(toks[i]) if stage_rank == 0 else sched.run()
+            last_mod.targets = list(tok[:, 1:].chunk(args.micro))
+        out = sched.run(tok) if stage_rank == 0 else sched.run()
         opt.step()
         return torch.stack([o.detach() for o in out]).sum() if out is not None else torch.zeros((), device=dev)
 
-    ms, loss, clocks = timed_steps(step, args, dev)
+    ms, loss, clocks, e2e = timed_steps(step, args, dev, host)
     lt = loss.clone()
     dist.all_reduce(lt, op=dist.ReduceOp.MAX)
     tokens = B * args.micro * S
@@ -267,6 +301,7 @@ def run_pp(args, rank, world, dev):
     return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} x tp{tp} {args.schedule}"
                        + (f" x{chunks} chunks" if chunks > 1 else ""), "micro_batches": args.micro,
                        "global_batch": B * args.micro, "seq_len": S},
+            "e2e_ms": e2e, "h2d_bytes": host[0].numel() * host.element_size(),
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(lt.detach()), "clocks": clocks,
             "memory_max_over_ranks": {"peak_allocated_gib": round(float(mem[0]), 2),
                                       "peak_reserved_gib": round(float(mem[1]), 2),
@@ -274,8 +309,8 @@ def run_pp(args, rank, world, dev):
             "mfu_flops_per_token": cfg.flops_per_token(S)}
 
 
-def main():
-    args = parse()
+def main(argv=None):
+    args = parse(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -288,8 +323,17 @@ def main():
         peak = 1400.0
     fpt = res.pop("mfu_flops_per_token")
     res["mfu_of_measured_sustained_bf16"] = fpt * res["value"] / world / (peak * 1e12)
+    from hyper_parallel_b200.ops import native
+    e2e_ms, h2d = res.pop("e2e_ms", None), res.pop("h2d_bytes", 0)
+    tokens_per_step = res["value"] * res["ms_per_step"] / 1e3
     res.update({"metric": "train tokens/sec (device-timed, max over ranks)", "unit": "tokens/s", "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "data": "synthetic"})
+                "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "impl": "ours",
+                "data": "synthetic (uniform token ids, seed 0; random-init weights)",
+                "gpu_launches": native.launch_count})
+    if e2e_ms:
+        res["e2e"] = {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
     if rank == 0:
         print(json.dumps(res))
     dist.barrier()

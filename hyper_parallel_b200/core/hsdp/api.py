@@ -112,6 +112,10 @@ def hsdp(cell: nn.Module, shard_size: int = -1, threshold: int = 64, optimizer_l
     for name, p in cell.named_parameters():
         if id(p) in seen or getattr(p, "_hsdp_param", None) is not None:
             continue
+        if getattr(p, "hsdp_ignore", False):
+            # not data-parallel state at all (e.g. expert-parallel weights: every rank owns different
+            # experts): left alone -- no sharding, no gradient synchronisation
+            continue
         seen.add(id(p))
         params.append((name, p))
     cls = cell.__class__

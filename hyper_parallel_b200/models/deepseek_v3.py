@@ -175,6 +175,10 @@ class MoE(nn.Module):
         # expert weights are expert-parallel, not data-parallel replicas: HSDP must not shard them
         self.w_gate_up.hsdp_shard_size = 1
         self.w_down.hsdp_shard_size = 1
+        if self.ep_size > 1 and self.ep_size == cc.get_world_size():
+            # every rank owns different experts: there is no data-parallel replica to synchronise with
+            self.w_gate_up.hsdp_ignore = True
+            self.w_down.hsdp_ignore = True
 
     def reset_parameters(self):
         # every EP rank draws the full expert tensor and keeps its slice, so that the global
