@@ -147,8 +147,9 @@ ep_dispatch_kernel(const DispatchParams p) {
     }
     token = __shfl_sync(0xffffffffu, token, 0);
     scale = __shfl_sync(0xffffffffu, scale, 0);
-    if (!HPB_BOUNDS_OK(token >= 0 && token < p.T && j >= 0 && j < p.T * p.k && slot < p.cap_rows, p.status,
-                       0x100000 | slot))
+    // the pair list comes from the router: a token index outside [0, T) would turn into a wild peer read
+    if (!HPB_INPUT_OK(token >= 0 && token < p.T && j >= 0 && j < p.T * p.k && slot < p.cap_rows, p.status,
+                      0x100000 | (slot & 0xfffff)))
       continue;
     const uint4* src =
         reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x_stage.ptr[s]) +
@@ -190,6 +191,7 @@ ep_dispatch_kernel(const DispatchParams p) {
 
 struct CombineParams {
   int T, k, H, E, n, rank;
+  int cap_rows;                    // rows of every rank's expert-output matrix
   PeerTable out, pads;             // expert-output matrices [cap_rows, H] of every rank
   const int* counts_all;           // [n, E] local snapshot written by the dispatch kernel of this layer
   const long long* topk_idx;       // [T, k] global expert of each pair
@@ -249,13 +251,14 @@ ep_combine_kernel(const CombineParams p) {
     if (threadIdx.x < p.k) {
       const int pair = t * p.k + threadIdx.x;
       const int e = static_cast<int>(p.topk_idx[pair]);
-      const bool e_ok = HPB_BOUNDS_OK(e >= 0 && e < p.E, p.status, 0x200000 | pair);
+      // expert ids come from the router: anything outside [0, E) must not index the tables
+      const bool e_ok = HPB_INPUT_OK(e >= 0 && e < p.E, p.status, 0x200000 | (pair & 0xfffff));
       const int slot = e_ok ? s_dst[e] + (p.sorted_pos[pair] - s_myoff[e]) : -1;
-      if (e_ok && HPB_BOUNDS_OK(slot >= 0, p.status, 0x300000 | pair)) {
+      if (e_ok && HPB_INPUT_OK(slot >= 0 && slot < p.cap_rows, p.status, 0x300000 | (pair & 0xfffff))) {
         s_row[threadIdx.x] = reinterpret_cast<const uint4*>(
             reinterpret_cast<const __nv_bfloat16*>(p.out.ptr[e / El]) + static_cast<long long>(slot) * p.H);
         s_w[threadIdx.x] = p.weights ? p.weights[pair] : 1.f;
-      } else {        // only reachable in the debug build: the row is skipped (treated as zeros)
+      } else {        // bad routing entry: reported through the status word, the row counts as zeros
         s_row[threadIdx.x] = nullptr;
         s_w[threadIdx.x] = 0.f;
       }
@@ -339,11 +342,11 @@ extern "C" int hpb_ep_dispatch(void* const* x_stage, void* const* sorted_token, 
 // sorted_pos [T*k] int32, weights [T, k] fp32 or null; y [T, H]; rows_save [T*k, H] or null.
 extern "C" int hpb_ep_combine(void* const* out, const int* counts_all, void* const* pads, const void* topk_idx,
                               const int* sorted_pos, const float* weights, void* y, void* rows_save, int T, int k,
-                              int H, int E, int n, int rank, unsigned epoch, unsigned long long limit_ns,
+                              int H, int E, int n, int rank, int cap_rows, unsigned epoch, unsigned long long limit_ns,
                               int* status, int num_ctas, cudaStream_t stream) {
   if (n < 1 || n > ep::kMaxEp || E > ep::kMaxExperts || E % n || (H % 8) || k < 1 || k > 8) return -2;
   ep::CombineParams p;
-  p.T = T; p.k = k; p.H = H; p.E = E; p.n = n; p.rank = rank;
+  p.T = T; p.k = k; p.H = H; p.E = E; p.n = n; p.rank = rank; p.cap_rows = cap_rows;
   p.out = ep::table(out, n);
   p.counts_all = counts_all;
   p.pads = ep::table(pads, n);

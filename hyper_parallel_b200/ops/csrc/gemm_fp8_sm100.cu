@@ -41,11 +41,13 @@ struct Params {
   // scale tiles.  block_group == nullptr: plain GEMM.
   const int* block_group;
   int b_group_rows;
+  int num_groups;
 };
 
 // Expert of the row block (0 for a plain GEMM) and the number of K blocks the tile runs (0: skip).
 __device__ __forceinline__ int tile_group(const Params& p, int m_blk, int num_k, int& k_blocks) {
-  const int g = p.block_group != nullptr ? p.block_group[m_blk] : 0;
+  int g = p.block_group != nullptr ? p.block_group[m_blk] : 0;
+  if (!HPB_BOUNDS_OK(g < p.num_groups, p.status, 0x600000 | m_blk)) g = -1;      // debug build: skip the block
   k_blocks = g < 0 ? 0 : num_k;
   return g < 0 ? 0 : g;
 }
@@ -362,7 +364,7 @@ extern "C" int hpb_gemm_fp8_blockscale(const void* Aq, const float* sa, const vo
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, nullptr, 0};
+  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, nullptr, 0, 1};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   gemm_fp8_kernel<<<tiles < num_sms ? tiles : num_sms, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
@@ -393,7 +395,7 @@ extern "C" int hpb_gemm_fp8_blockscale_grouped(const void* Aq, const float* sa, 
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, block_group, N};
+  Params p{M, N, K, sa, sb, reinterpret_cast<__nv_bfloat16*>(C), ldc, status, block_group, N, num_experts};
   const int tiles = (M / BM) * (N / BN);
   gemm_fp8_kernel<<<tiles < num_sms ? tiles : num_sms, THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());

@@ -41,6 +41,11 @@ __device__ __forceinline__ void report(int* status, int code, int detail) {
 #endif
 #endif
 
+// Checks that stay on in every build: indices that come from tensors produced elsewhere (routing
+// tables).  A failed check records status code 6 with a detail word and evaluates to false; the
+// caller skips the access.
+#define HPB_INPUT_OK(cond, status, detail) ((cond) ? true : (::hpb::report((status), 6, static_cast<int>(detail)), false))
+
 // Signal every peer: "rank `rank` reached `epoch` on `slot`".
 __device__ __forceinline__ void signal_peers(const PeerTable& pads, int rank, int n, int slot,
                                              uint32_t epoch) {

@@ -41,7 +41,8 @@ def _lib():
         lib.hpb_ep_dispatch.argtypes = [pp, pp, pp, pp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cu, cull,
                                         vp, ci, vp]
         lib.hpb_ep_dispatch.restype = ci
-        lib.hpb_ep_combine.argtypes = [pp, vp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, cu, cull, vp, ci, vp]
+        lib.hpb_ep_combine.argtypes = [pp, vp, pp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, cu, cull, vp, ci,
+                                       vp]
         lib.hpb_ep_combine.restype = ci
         _bound = True
     return lib
@@ -117,8 +118,8 @@ class EPWorkspace:
         rows = torch.empty((self.T * self.k, self.H), dtype=torch.bfloat16, device=self.device) if save_rows else None
         rc = _lib().hpb_ep_combine(self.p_out, self.counts_all.data_ptr(), self.symm.pad_ptrs, topk_idx.data_ptr(),
                                    sorted_pos.data_ptr(), native.ptr(weights), y.data_ptr(), native.ptr(rows),
-                                   self.T, self.k, self.H, self.E, self.n, self.rank, self.symm.next_epoch(),
-                                   limit_ns, self.status.data_ptr(), self.ctas, native.stream(self.device))
+                                   self.T, self.k, self.H, self.E, self.n, self.rank, self.cap_rows,
+                                   self.symm.next_epoch(), limit_ns, self.status.data_ptr(), self.ctas, native.stream(self.device))
         native.check(rc, "hpb_ep_combine")
         return y, rows
 
@@ -147,6 +148,8 @@ class _FusedExperts(torch.autograd.Function):
         T, k = topk_idx.shape
         E, El, H, cap = ws.E, ws.e_local, ws.H, ws.cap_rows
         F2 = w_gate_up.shape[1]
+        # expert ids index device-side tables: keep them inside [0, E) whatever the router produced
+        topk_idx = topk_idx.clamp(0, E - 1)
         flat_e = topk_idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         sorted_token = (order // k).to(torch.int32)
