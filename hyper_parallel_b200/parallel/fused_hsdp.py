@@ -156,6 +156,14 @@ _RIDE_GBS = 500.0         # bytes a host GEMM is assumed to move per second of i
 _GEMM_TFLOPS = 1400.0
 
 
+_RIDE_STATS = [] if os.environ.get("HPB_RIDE_STATS", "0") == "1" else None
+
+
+def ride_stats():
+    """``[(parameter, is_dgrad, fraction gathered before the consumer started)]`` (HPB_RIDE_STATS=1)."""
+    return _RIDE_STATS
+
+
 def _queue(device) -> List[_Ticket]:
     return _RIDE_QUEUE.setdefault(device.index, [])
 
@@ -440,6 +448,13 @@ class SymmParamBuffer:
         t = self._close_ticket(i)
         spec = t.spec
         rows, cols = self.params[i].full_shape
+        if _RIDE_STATS is not None:
+            # diagnostic (HPB_RIDE_STATS=1, synchronises): how much of the weight the earlier GEMMs had
+            # brought in by the time its consumer is launched
+            torch.cuda.current_stream(self.device).synchronize()
+            items = (rows * cols // 8 + (2047 if cols % 128 == 0 else 1023)) // (2048 if cols % 128 == 0 else 1024)
+            done = int(self.panel_cnt[i][-2].item()) - (spec.seq - 1) * items
+            _RIDE_STATS.append((self.params[i].name, int(w_mn), done / max(items, 1)))
         ride = next_ride(self.device, 2.0 * a.shape[0] * rows * cols)
         with tracing.nvtx_range("hpb.hsdp.allgather_gemm"):
             rc = self.lib.hpb_gemm2_gather(
