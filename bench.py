@@ -40,6 +40,8 @@ def parse_args():
                          "global batch 8; moe_ep: DeepSeek-V3 4 layers, 256 experts, EP over all ranks, fp8; "
                          "pp: Llama-3-8B PP=4 x TP=2, 16 micro-batches")
     ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"], help="--config pp only")
+    ap.add_argument("--metrics-jsonl", default=os.environ.get("HPB_METRICS_JSONL"),
+                    help="also append the result (and the per-kernel-path switches) as one JSON line to this file")
     return ap.parse_args()
 
 
@@ -193,6 +195,15 @@ def run_ours(args):
         pass
     peak_tflops = peaks.get("bf16_tflops_sustained", 1400.0)
     mfu = flops / (ms_per_step / 1e3) / (peak_tflops * 1e12)
+    from hyper_parallel_b200.utils.logging import MetricsWriter, get_logger
+    log = get_logger("hyper_parallel_b200.bench")
+    log.info("llama %s x%d: %.1f ms/step device-timed, %.1f ms/step end to end, mfu %.3f", args.model, world,
+             ms_per_step, e2e_ms / args.steps, mfu)
+    MetricsWriter(args.metrics_jsonl).write(args.steps, tokens_per_s=value, ms_per_step=ms_per_step,
+                                            e2e_ms_per_step=e2e_ms / args.steps, mfu=mfu, loss=last_loss,
+                                            n_gpus=world, fused_comm=os.environ.get("HPB_FUSED_COMM", "1"),
+                                            fused_ag=os.environ.get("HPB_FUSED_AG", "1"),
+                                            ride=os.environ.get("HPB_RIDE", "1"), nvls=os.environ.get("HPB_NVLS", "1"))
     if rank == 0:
         print(json.dumps({
             "metric": "train tokens/sec (device-timed, max over ranks)", "value": value,

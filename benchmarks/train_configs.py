@@ -334,6 +334,11 @@ def main(argv=None):
     if e2e_ms:
         res["e2e"] = {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4}
+    from hyper_parallel_b200.utils.logging import MetricsWriter, get_logger
+    get_logger("hyper_parallel_b200.bench").info("%s x%d: %.1f ms/step", args.config, world, res["ms_per_step"])
+    MetricsWriter(os.environ.get("HPB_METRICS_JSONL")).write(args.steps, config=args.config,
+                                                             tokens_per_s=res["value"], ms_per_step=res["ms_per_step"],
+                                                             n_gpus=world, loss=res.get("loss", 0.0))
     if rank == 0:
         print(json.dumps(res))
     dist.barrier()

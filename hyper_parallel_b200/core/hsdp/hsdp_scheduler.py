@@ -128,6 +128,9 @@ class HSDPScheduler:
             buf.on_all_ready = (lambda b=buf: self._symm_ready(b))
             for i, hp in enumerate(buf.params):
                 hp.param._hpb_symm = (buf, i)
+                if hp.leaf is not hp.param:
+                    # tensor-parallel layers hand the local tensor of a DTensor parameter to the GEMMs
+                    hp.leaf._hpb_symm = (buf, i)
 
     def _symm_ready(self, buf) -> None:
         for hp in buf.params:

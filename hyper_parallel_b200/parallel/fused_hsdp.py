@@ -31,8 +31,9 @@ which has normally been published long before.  A shard is only rewritten after 
 gradients of that module have arrived, i.e. after every peer has finished reading it.
 
 The path is used when the group is a full-shard group of CUDA ranks on one node and the parameters
-are bf16; parameters of other kinds in the same module go through the ``torch.distributed``
-buffers.
+are bf16 -- plain parameters, or the local shards of tensor-parallel DTensor parameters (TP x HSDP:
+the HSDP group of such a parameter is the set of ranks that hold the same tensor-parallel slice);
+parameters of other kinds in the same module go through the ``torch.distributed`` buffers.
 """
 from __future__ import annotations
 
@@ -87,8 +88,13 @@ def group_ok(params) -> bool:
 
 
 def eligible(p) -> bool:
-    """One parameter: a plain CUDA bf16 tensor whose shard is a whole number of 16-byte vectors."""
-    return (not p.is_dtensor) and p.shard.dtype == torch.bfloat16 and p.shard.is_cuda and p.shard.numel() % 8 == 0
+    """One parameter: a CUDA bf16 tensor (a plain parameter, or the local shard of a tensor-parallel
+    DTensor parameter: HSDP shards dim 0 of the local tensor over the ranks that replicate it) whose
+    HSDP shard is a whole number of 16-byte vectors.  ``HPB_SYMM_DTENSOR=0`` keeps DTensor parameters
+    on the NCCL buffers."""
+    if p.is_dtensor and os.environ.get("HPB_SYMM_DTENSOR", "1") == "0":
+        return False
+    return p.shard.dtype == torch.bfloat16 and p.shard.is_cuda and p.shard.numel() % 8 == 0
 
 
 def split_eligible(params):
