@@ -109,6 +109,38 @@ def main():
     cases["flash_attn_fwd"] = lambda: attn_case(False)
     cases["flash_attn_bwd"] = lambda: attn_case(True)
 
+    def mla_case(bwd, lib=False):
+        """192 / 128 latent attention; ``lib``: the expanded form through the cuDNN graph (what the
+        model ran before the kernels existed), including its two concatenations."""
+        from hyper_parallel_b200.ops import mla_attention as mla
+        B, S, H = (1, 2048, 16) if args.small else (2, 4096, 32)
+        q = torch.randn(B, S, H, 192, device=dev, dtype=bf)
+        kv = torch.randn(B, S, H, 256, device=dev, dtype=bf)
+        kr = torch.randn(B, S, 64, device=dev, dtype=bf)
+        do = torch.randn(B, S, H, 128, device=dev, dtype=bf)
+        fl = 2.0 * B * H * S * S * (192 + 128) / 2
+        if lib:
+            import torch.nn.functional as F
+            from torch.nn.attention import SDPBackend, sdpa_kernel
+
+            def run():
+                qa, kva, kra = [t.detach().requires_grad_(bwd) for t in (q, kv, kr)]
+                kh = torch.cat([kva[..., :128], kra.view(B, S, 1, 64).expand(B, S, H, 64)], dim=-1)
+                with sdpa_kernel([SDPBackend.CUDNN_ATTENTION]):
+                    o = F.scaled_dot_product_attention(qa.transpose(1, 2), kh.transpose(1, 2),
+                                                       kva[..., 128:].transpose(1, 2), is_causal=True)
+                if bwd:
+                    o.backward(do.transpose(1, 2))
+            return run, (3.5 if bwd else 1.0) * fl, None
+        o, lse = mla.mla_forward(q, kv, kr)
+        if bwd:
+            return (lambda: mla.mla_backward(q, kv, kr, o, lse, do)), 2.5 * fl, None
+        return (lambda: mla.mla_forward(q, kv, kr)), fl, None
+    cases["mla_attn_fwd"] = lambda: mla_case(False)
+    cases["mla_attn_bwd"] = lambda: mla_case(True)
+    cases["mla_attn_fwd_cudnn_expanded"] = lambda: mla_case(False, lib=True)
+    cases["mla_attn_fwd_bwd_cudnn_expanded"] = lambda: mla_case(True, lib=True)
+
     def rms_case():
         x, w = torch.randn(TB, 4096, device=dev, dtype=bf), torch.ones(4096, device=dev, dtype=bf)
         r = torch.randn_like(x)

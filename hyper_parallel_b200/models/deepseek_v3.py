@@ -27,6 +27,7 @@ from torch import nn
 
 from .. import ops
 from ..collectives import cc
+from ..ops import mla_attention as mla_ops
 from ..ops import moe as moe_ops
 
 
@@ -119,19 +120,17 @@ class MLA(nn.Module):
         nh, dn, dr, dv = c.num_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
         T = x.shape[0]
         f8 = c.fp8
+        # q stays one tensor: RoPE rotates the rotary tail of every head in place; kv is read by the
+        # attention kernels as the up-projection left it (k_nope | v per head), the shared rotary key
+        # as one vector per token -- no concatenation or expansion on either pass
         q = _lin(ops.rmsnorm(_lin(x, self.wq_a, f8), self.q_norm, c.norm_eps), self.wq_b, f8)
-        q = q.view(T, nh, dn + dr)
-        q_nope, q_rope = q.split([dn, dr], dim=-1)
-        q_rope = _rope_last(q_rope.contiguous(), seq_len, c.rope_theta)
+        q = mla_ops.rope_tail_(q.view(T, nh, dn + dr), dr, seq_len, c.rope_theta)
         kv_a = _lin(x, self.wkv_a, f8)
         kv_c, k_rope = kv_a.split([c.kv_lora_rank, dr], dim=-1)
         k_rope = _rope_last(k_rope.contiguous().view(T, 1, dr), seq_len, c.rope_theta)
-        kv = _lin(ops.rmsnorm(kv_c.contiguous(), self.kv_norm, c.norm_eps), self.wkv_b, f8).view(T, nh, dn + dv)
-        k_nope, v = kv.split([dn, dv], dim=-1)
-        qh = torch.cat([q_nope, q_rope], dim=-1).view(batch, seq_len, nh, dn + dr)
-        kh = torch.cat([k_nope, k_rope.expand(T, nh, dr)], dim=-1).view(batch, seq_len, nh, dn + dr)
-        vh = v.reshape(batch, seq_len, nh, dv)
-        o = ops.attention.causal_attention(qh, kh, vh)          # [B, S, nh, dv]
+        kv = _lin(ops.rmsnorm(kv_c.contiguous(), self.kv_norm, c.norm_eps), self.wkv_b, f8)
+        o = mla_ops.mla_attention(q.view(batch, seq_len, nh, dn + dr), kv.view(batch, seq_len, nh, dn + dv),
+                                  k_rope.view(batch, seq_len, dr), dn, dv)          # [B, S, nh, dv]
         return _lin(o.reshape(T, nh * dv), self.wo, f8)
 
 
@@ -265,7 +264,7 @@ class DeepSeekV3(nn.Module):
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None,
                 loss_denominator: Optional[float] = None, loss_is_final: bool = True):
         B, S = tokens.shape
-        h = F.embedding(tokens.reshape(-1), self.embed)
+        h = ops.embedding(tokens.reshape(-1), self.embed)
         resid = None
         for layer in self.layers:
             h, resid = layer(h, resid, B, S)

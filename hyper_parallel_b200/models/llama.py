@@ -178,7 +178,7 @@ class Llama(nn.Module):
     def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor] = None,
                 loss_denominator: Optional[float] = None, loss_is_final: bool = True):
         B, S = tokens.shape
-        h = F.embedding(tokens.reshape(-1), self.embed)
+        h = ops.embedding(tokens.reshape(-1), self.embed)
         resid = None
         for layer in self.layers:
             h, resid = layer(h, resid, B, S)

@@ -321,7 +321,7 @@ __global__ void rope_table_init_kernel(float2* __restrict__ table, int S, int ha
 
 __global__ void rope_vec_kernel(bf16* __restrict__ x, const float2* __restrict__ table,
                                 const int* __restrict__ pos, int64_t T, int S, int NH, int D, int64_t ld,
-                                float sign) {
+                                int64_t head_stride, float sign) {
   const int half = D >> 1, hv = half >> 3;
   const int64_t total = T * NH * hv;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
@@ -331,7 +331,7 @@ __global__ void rope_vec_kernel(bf16* __restrict__ x, const float2* __restrict__
     const int h = static_cast<int>(th % NH);
     const int64_t t = th / NH;
     const int p = pos ? pos[t] : static_cast<int>(t % S);
-    bf16* base = x + t * ld + static_cast<int64_t>(h) * D + c * 8;
+    bf16* base = x + t * ld + h * head_stride + c * 8;
     const float4* tb = reinterpret_cast<const float4*>(table + static_cast<int64_t>(p) * half + c * 8);
     float a[8], b[8], oa[8], ob[8];
     unpack8(*reinterpret_cast<const uint4*>(base), a);
@@ -668,12 +668,18 @@ extern "C" int hpb_rope_table(float* table, int S, int D, float theta, cudaStrea
   return static_cast<int>(cudaGetLastError());
 }
 
-// In-place RoPE using a precomputed table; needs D % 16 == 0, ld % 8 == 0 and 16-byte aligned x.
-extern "C" int hpb_rope_vec(void* x, const float* table, const int* pos, int64_t T, int S, int NH, int D,
-                            int64_t ld, int backward, int num_sms, cudaStream_t s) {
-  if (D % 16 || ld % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
+// In-place RoPE using a precomputed table; needs D % 16 == 0, ld % 8 == 0, head_stride % 8 == 0 (elements
+// between the rotated D columns of consecutive heads; D when the heads are packed) and 16-byte aligned x.
+extern "C" int hpb_rope_vec_strided(void* x, const float* table, const int* pos, int64_t T, int S, int NH, int D,
+                                    int64_t ld, int64_t head_stride, int backward, int num_sms, cudaStream_t s) {
+  if (D % 16 || ld % 8 || head_stride % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -2;
   if (T == 0) return 0;
   rope_vec_kernel<<<grid_for(T * NH * (D / 16), 256, num_sms), 256, 0, s>>>(
-      (bf16*)x, reinterpret_cast<const float2*>(table), pos, T, S, NH, D, ld, backward ? -1.f : 1.f);
+      (bf16*)x, reinterpret_cast<const float2*>(table), pos, T, S, NH, D, ld, head_stride, backward ? -1.f : 1.f);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int hpb_rope_vec(void* x, const float* table, const int* pos, int64_t T, int S, int NH, int D,
+                            int64_t ld, int backward, int num_sms, cudaStream_t s) {
+  return hpb_rope_vec_strided(x, table, pos, T, S, NH, D, ld, D, backward, num_sms, s);
 }

@@ -17,7 +17,7 @@ from . import native
 
 __all__ = [
     "gemm", "linear", "matmul", "rmsnorm", "add_rmsnorm", "swiglu", "rope_", "apply_rope",
-    "cross_entropy_fwd_bwd", "fused_cross_entropy", "adamw_step_",
+    "cross_entropy_fwd_bwd", "fused_cross_entropy", "adamw_step_", "embedding",
 ]
 
 
@@ -342,12 +342,24 @@ def _rope_table(seq_len: int, D: int, theta: float, device) -> torch.Tensor:
 
 def rope_(x: torch.Tensor, seq_len: int, theta: float, positions: Optional[torch.Tensor] = None,
           inverse: bool = False) -> torch.Tensor:
-    """In-place rotary embedding of ``x[T, NH, D]`` (token stride may exceed ``NH*D``)."""
+    """In-place rotary embedding of ``x[T, NH, D]`` (token stride may exceed ``NH*D``; the heads may be
+    further apart than ``D``, e.g. the rotary tail of every head of a packed projection)."""
     T, NH, D = x.shape
     if not native.use_native(x):
         x.copy_(_rope_ref(x, seq_len, theta, positions, inverse))
         return x
-    assert x.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) == D
+    assert x.dtype == torch.bfloat16 and x.stride(2) == 1
+    if x.stride(1) != D:
+        if not (D % 16 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0
+                and positions is None):
+            x.copy_(_rope_ref(x, seq_len, theta, positions, inverse))
+            return x
+        table = _rope_table(seq_len, D, float(theta), x.device)
+        rc = native.lib().hpb_rope_vec_strided(x.data_ptr(), table.data_ptr(), None, T, seq_len, NH, D, x.stride(0),
+                                               x.stride(1), int(inverse), native.sm_count(x.device),
+                                               native.stream(x.device))
+        native.check(rc, "hpb_rope_vec_strided")
+        return x
     pos_ptr = None
     if positions is not None:
         positions = positions.to(torch.int32).contiguous()
@@ -384,6 +396,49 @@ def apply_rope(x: torch.Tensor, seq_len: int, theta: float) -> torch.Tensor:
     if native.use_native(x):
         return _RoPE.apply(x.contiguous(), seq_len, theta)
     return _rope_ref(x, seq_len, theta)
+
+
+# ---------------------------------------------------------------- embedding --
+class _Embedding(torch.autograd.Function):
+    """Row gather forward; deterministic dense weight gradient backward (``embedding.cu``)."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight):
+        T = tokens.numel()
+        V, H = weight.shape
+        idx = tokens.reshape(-1).to(torch.int64).contiguous()
+        out = torch.empty((T, H), dtype=weight.dtype, device=weight.device)
+        dev = weight.device
+        rc = native.lib().hpb_embedding_fwd(idx.data_ptr(), weight.data_ptr(), out.data_ptr(), T, V, H,
+                                            native.status_word(dev).data_ptr(), native.sm_count(dev), native.stream(dev))
+        native.check(rc, "hpb_embedding_fwd")
+        ctx.save_for_backward(idx)
+        ctx.shape = (V, H)
+        return out.view(*tokens.shape, H)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        V, H = ctx.shape
+        dy2 = dy.reshape(-1, H).contiguous()
+        dev = dy2.device
+        T = idx.numel()
+        dw = torch.empty((V, H), dtype=dy2.dtype, device=dev)
+        scratch = torch.empty(3 * V + T, dtype=torch.int32, device=dev)
+        rc = native.lib().hpb_embedding_bwd(idx.data_ptr(), dy2.data_ptr(), dw.data_ptr(), scratch.data_ptr(), T, V, H,
+                                            native.status_word(dev).data_ptr(), native.sm_count(dev), native.stream(dev))
+        native.check(rc, "hpb_embedding_bwd")
+        return None, dw
+
+
+def embedding(tokens: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``weight[tokens]`` -> ``[*tokens.shape, H]``.  bf16 CUDA weights with ``H % 8 == 0`` take this
+    library's kernels (the weight gradient is dense, written once per row, and bit-identical from
+    run to run); everything else takes ``torch.nn.functional.embedding``."""
+    if (native.use_native(weight) and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.is_contiguous()
+            and weight.shape[1] % 8 == 0 and type(weight) in (torch.Tensor, torch.nn.Parameter)):
+        return _Embedding.apply(tokens, weight)
+    return F.embedding(tokens, weight)
 
 
 # ------------------------------------------------------------ cross entropy --

@@ -38,6 +38,10 @@ _SIGNATURES = {
                  c_void_p],
     "hpb_rope_table": [c_void_p, c_int, c_int, c_float, c_void_p],
     "hpb_rope_vec": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_void_p],
+    "hpb_rope_vec_strided": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64, c_int64, c_int, c_int,
+                             c_void_p],
+    "hpb_embedding_fwd": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p],
+    "hpb_embedding_bwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p],
     "hpb_cross_entropy": [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_float, c_void_p],
     "hpb_adamw": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                   c_float, c_float, c_float, c_int, c_float, c_int, c_void_p],

@@ -543,3 +543,27 @@ def test_deepseek_tiny_fp8_gpu_matches_fp32_reference():
     assert abs(loss.item() - loss_ref.item()) < 5e-2 * abs(loss_ref.item()), (loss.item(), loss_ref.item())
     g = gpu.layers[1].ffn.w_down.grad
     assert g is not None and torch.isfinite(g.float()).all()
+
+
+@pytest.mark.parametrize("T,V,H,hot", [(1000, 512, 256, False), (4096, 3000, 128, True), (257, 100000, 64, False)])
+def test_embedding_forward_backward_deterministic(T, V, H, hot):
+    """Row gather and the dense weight gradient against index_add in fp32; the gradient is bit-identical
+    between runs (``hot``: most tokens name one row, a bucket far longer than a warp)."""
+    from hyper_parallel_b200 import ops
+    torch.manual_seed(31)
+    w = torch.randn(V, H, device=_dev(), dtype=torch.bfloat16).requires_grad_()
+    tok = torch.randint(0, V, (T,), device=_dev())
+    if hot:
+        tok[torch.rand(T, device=_dev()) < 0.6] = 7
+    dy = torch.randn(T, H, device=_dev(), dtype=torch.bfloat16)
+    out = ops.embedding(tok.view(1, T), w)
+    assert out.shape == (1, T, H) and torch.equal(out[0], w.detach()[tok])
+    out.backward(dy.view(1, T, H))
+    native.check_status()
+    ref = torch.zeros(V, H, device=_dev(), dtype=torch.float32).index_add_(0, tok, dy.float())
+    assert _rel_err(w.grad, ref) < 4e-3
+    assert torch.equal(w.grad[ref.abs().sum(1) == 0], torch.zeros_like(w.grad[ref.abs().sum(1) == 0]))
+    g1 = w.grad.clone()
+    w.grad = None
+    ops.embedding(tok, w).backward(dy)
+    assert torch.equal(g1, w.grad)
