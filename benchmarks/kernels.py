@@ -60,7 +60,19 @@ def main():
     ap.add_argument("--case", nargs="*", default=None)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--bwd-group", type=int, default=None,
+                    help="attention backward: (batch, head) pairs scheduled together (0 = all, key-tile major)")
+    ap.add_argument("--mla-probe", type=int, default=0,
+                    help="timing probe of the MLA backward (wrong results): 1 = no dQ reduce, 2 = no exponentials, "
+                         "4 / 8 / 16 = without the dQ / dK, dV / score products")
     args = ap.parse_args()
+    if os.environ.get("HPB_MLA_DQ_DIRECT") is not None:
+        native.lib().hpb_mla_attn_set_dq_direct(int(os.environ["HPB_MLA_DQ_DIRECT"]))
+    if args.mla_probe:
+        native.lib().hpb_mla_attn_set_probe(args.mla_probe)
+    if args.bwd_group is not None:
+        native.lib().hpb_flash_attn_set_head_group(args.bwd_group)
+        native.lib().hpb_mla_attn_set_head_group(args.bwd_group)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     tf, gbs, src = peaks()

@@ -5,28 +5,36 @@
 // tiles that see it.  Everything is computed transposed, so that the softmax threads (thread =
 // key row) write the A operands of the following products as plain 128-byte rows:
 //
-//   S^T  = K Q^T            [kv 128 x q 64]   contraction 192; tensor memory, double buffered
-//   dP^T = V dO^T           [kv 128 x q 64]   contraction 128; tensor memory, one buffer
+//   S^T  = K Q^T            [kv 128 x q 64]   contraction 192
+//   dP^T = V dO^T           [kv 128 x q 64]   contraction 128
 //   P^T  = exp2(S^T c - lse),  dS^T = P^T o (dP^T - D)        -> bf16, shared memory
-//   dV  += P^T dO           [kv 128 x 128]    tensor memory, accumulated over the whole walk
-//   dK  += dS^T Q           [kv 128 x 192]    tensor memory, accumulated over the whole walk
-//   dQ^T = K^T dS^T         [d 192 x q 64]    as two products of 128 rows: head elements 0..127
-//                                             into the S^T buffer just consumed, 64..191 into the
-//                                             dP^T buffer just consumed (its rows 64..127 = head
-//                                             elements 128..191 are the ones read out)
+//   dV  += P^T dO           [kv 128 x 128]    accumulated over the whole walk
+//   dK  += dS^T Q           [kv 128 x 192]    accumulated over the whole walk
+//   dQ^T = K^T dS^T         [d 192 x q 64]    as two products of 128 rows (head elements 0..127,
+//                                             then 64..191, of which rows 64..127 = elements
+//                                             128..191 are read out) through ONE buffer
 //
-// Tensor memory: S^T 2 x 64 | dP^T 64 | dV 128 | dK 192 = 512 columns.  dP^T of the next step can
-// only be formed once the upper dQ^T rows have been read out of its buffer, so the scores of step
-// i + 1 are issued behind the accumulations of step i: per step the tensor core runs dQ^T, dV, dK,
-// S^T(i + 1), dP^T(i + 1) back to back and the softmax of step i + 1 follows.
+// Tensor memory (512 columns): S^T 64 | dP^T 64 | dQ^T 64 | dV 128 | dK 192.  The two accumulators
+// leave room for three 64-column buffers only, so nothing is double buffered; instead every buffer
+// is handed back as early as possible and the products of neighbouring steps interleave:
 //
-//   warp 0       TMA producer: K, V once; (Q_i, dO_i) through a 2-stage ring
+//   * the softmax warps release S^T as soon as their scores are in registers, so S^T of step
+//     i + 2 is formed while step i + 1 is still being exponentiated;
+//   * P^T is written from S^T alone, before dP^T of the step is awaited;
+//   * per step the tensor core runs dP^T(i + 1) first (the softmax of step i + 1 waits for it),
+//     then dK(i), dV(i) (which free the Q / dO ring slots), the lower dQ^T(i), S^T(i + 2) while
+//     that tile is read out, and the upper dQ^T(i).
+//
+//   warp 0       TMA producer: K, V once; Q_i and dO_i through two 2-slot rings
 //   warp 1       MMA issuer
 //   warps 2-9    softmax / dS: two groups of four warps, each owning 32 of the 64 query columns;
 //                they also write dV / dK at the end
-//   warps 10-13  dQ read-out: fp32 tiles staged in shared memory and added to global memory by TMA
+//   warps 10-13  dQ read-out: fp32 tiles staged in shared memory (over P^T for the lower product,
+//                over dS^T for the upper one, once their readers have retired) and added to the
+//                fp32 dQ in global memory by TMA reduces
 //
 // dK of the rotary columns is written per head; the caller sums it over the heads.
+// Every wait is bounded; on expiry a status code is recorded and all roles unwind.
 #include "attention_common.cuh"
 
 namespace hpb {
@@ -44,11 +52,10 @@ constexpr int UNIT_BYTES = 128 * 64 * 2;        // 16 KB: [128 key rows x 64 col
 constexpr int QSUB_BYTES = BQ * 64 * 2;         // 8 KB:  [64 query rows x 64 columns]
 constexpr int Q_BYTES = 3 * QSUB_BYTES;         // 24 KB
 constexpr int DO_BYTES = 2 * QSUB_BYTES;        // 16 KB
-constexpr int STAGE_BYTES = Q_BYTES + DO_BYTES; // 40 KB
-constexpr int QDO_STAGES = 2;
+constexpr int RING = 2;
 constexpr int PT_BYTES = BN * BQ * 2;           // 16 KB
 constexpr int BWD_THREADS = 448;
-constexpr int BWD_SMEM = 3 * UNIT_BYTES + 2 * UNIT_BYTES + QDO_STAGES * STAGE_BYTES + 2 * 2 * PT_BYTES +
+constexpr int BWD_SMEM = 3 * UNIT_BYTES + 2 * UNIT_BYTES + RING * (Q_BYTES + DO_BYTES) + 2 * 2 * PT_BYTES +
                          2 * 2 * BQ * 4 + 1024 + 256;
 static_assert(BWD_SMEM <= 227 * 1024, "shared memory budget");
 
@@ -56,35 +63,50 @@ struct BwdParams {
   int B, S, H;
   float scale, scale_log2;
   int causal;
+  int head_group;        // (batch, head) pairs scheduled together
+  int probe;             // timing probes (results are wrong): 1 = no dQ staging / reduce, 2 = no exponentials,
+                         // 4 / 8 / 16 = the dQ^T / dK, dV / S^T, dP^T products are not issued
   const float* lse;      // [B, H, S]
   const float* delta;    // [B, H, S]  rowsum(dO o O)
+  float* dQ;             // [B, S, H, 192] fp32, zero-initialised (DQ_DIRECT)
   __nv_bfloat16* dKV;    // [B, S, H, 256]: dK nope | dV
   __nv_bfloat16* dKR;    // [B, S, H, 64]: dK of the rotary columns, per head
   int* status;
+  long long* prof;       // optional [16]: cycles that one softmax thread of CTA 0 spent per phase, summed over its walk
 };
 
+// DQ_DIRECT: the dQ warps add their registers to the fp32 dQ with coalesced red.global instructions
+// (lane = head element) instead of staging tiles for TMA reduces; the P^T / dS^T buffers are then
+// handed back by the tensor core alone.
+template <bool DQ_DIRECT>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_kr,
-               const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ CUtensorMap tmap_dq32,
+               const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;                                         // 3 units: nope 0..63, nope 64..127, rope
   uint8_t* sV = sK + 3 * UNIT_BYTES;                          // 2 units: columns 0..63, 64..127
-  uint8_t* sQdO = sV + 2 * UNIT_BYTES;                        // per stage: Q (3 x 8 KB) | dO (2 x 8 KB)
-  uint8_t* sPT = sQdO + QDO_STAGES * STAGE_BYTES;             // per buffer: P^T (16 KB) | dS^T (16 KB)
+  uint8_t* sQ = sV + 2 * UNIT_BYTES;                          // ring of Q tiles (3 x 8 KB each)
+  uint8_t* sDO = sQ + RING * Q_BYTES;                         // ring of dO tiles (2 x 8 KB each)
+  uint8_t* sPT = sDO + RING * DO_BYTES;                       // per buffer: P^T (16 KB) | dS^T (16 KB)
   float* sStat = reinterpret_cast<float*>(sPT + 2 * 2 * PT_BYTES);   // [2][2][64]: lse * log2e, delta
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(sStat + 2 * 2 * BQ);
-  uint64_t* qdo_full = kv_full + 1;              // [2]
-  uint64_t* qdo_empty = qdo_full + QDO_STAGES;   // [2]
-  uint64_t* st_full = qdo_empty + QDO_STAGES;    // [2]  S^T of a step complete
-  uint64_t* dpt_full = st_full + 2;              // [1]  dP^T of a step complete
-  uint64_t* ds_full = dpt_full + 1;              // [2]  P^T / dS^T written (8 warp arrivals)
+  uint64_t* q_full = kv_full + 1;                // [2]
+  uint64_t* q_empty = q_full + RING;             // [2]
+  uint64_t* do_full = q_empty + RING;            // [2]
+  uint64_t* do_empty = do_full + RING;           // [2]
+  uint64_t* st_full = do_empty + RING;           // [1]  S^T of a step complete
+  uint64_t* st_consumed = st_full + 1;           // [1]  S^T of a step is in registers (8 warp arrivals)
+  uint64_t* dpt_full = st_consumed + 1;          // [1]  dP^T of a step complete
+  uint64_t* ds_full = dpt_full + 1;              // [2]  P^T / dS^T written, dP^T read (8 warp arrivals)
   uint64_t* pt_free = ds_full + 2;               // [2]  dQ staging over P^T / dS^T has been read (4 warp arrivals)
-  uint64_t* dq_full = pt_free + 2;               // [2]  both dQ^T products of a step complete
-  uint64_t* dq_lo_drained = dq_full + 2;         // [2]  (4 warp arrivals)
-  uint64_t* dq_hi_drained = dq_lo_drained + 2;   // [1]  (2 warp arrivals)
+  uint64_t* dq_lo_full = pt_free + 2;            // [1]
+  uint64_t* dq_hi_full = dq_lo_full + 1;         // [1]
+  uint64_t* dq_lo_drained = dq_hi_full + 1;      // [1]  (4 warp arrivals)
+  uint64_t* dq_hi_drained = dq_lo_drained + 1;   // [1]  (2 warp arrivals)
   uint64_t* stat_full = dq_hi_drained + 1;       // [2]  lse / delta of a step staged (4 warp arrivals)
   uint64_t* acc_full = stat_full + 2;            // [1]
   uint64_t* drain_bar = acc_full + 1;            // [1]
@@ -93,8 +115,20 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int hb = static_cast<int>(blockIdx.x) % (p.H * p.B);
-  const int jt = static_cast<int>(blockIdx.x) / (p.H * p.B);   // causal: low tiles have the longest walk
+  // (batch, head) pairs are processed in groups of `head_group`: the CTAs that run at the same time
+  // then add into a few MB of the fp32 dQ (and re-read the same Q / dO), which stays in L2; inside
+  // a group the key tiles go in ascending order (causal: low tiles have the longest walk)
+  int hb, jt;
+  {
+    const int n_tiles = (p.S + BN - 1) / BN;
+    const int pairs = p.H * p.B;
+    const int hg = max(1, min(p.head_group, pairs));
+    const int g0 = static_cast<int>(blockIdx.x) / (hg * n_tiles) * hg;
+    const int gsz = min(hg, pairs - g0);
+    const int r = static_cast<int>(blockIdx.x) - g0 * n_tiles;
+    jt = r / gsz;
+    hb = g0 + r % gsz;
+  }
   const int head = hb % p.H;
   const int batch = hb / p.H;
   const int k0 = jt * BN;
@@ -104,19 +138,23 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < QDO_STAGES; ++s) {
-      mbar_init(&qdo_full[s], 1);
-      mbar_init(&qdo_empty[s], 1);
+    for (int s = 0; s < RING; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&do_full[s], 1);
+      mbar_init(&do_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&st_full[b], 1);
       mbar_init(&ds_full[b], 8);
-      mbar_init(&pt_free[b], 4);
-      mbar_init(&dq_full[b], 1);
-      mbar_init(&dq_lo_drained[b], 4);
+      mbar_init(&pt_free[b], DQ_DIRECT ? 1 : 4);
       mbar_init(&stat_full[b], 4);
     }
+    mbar_init(st_full, 1);
+    mbar_init(st_consumed, 8);
     mbar_init(dpt_full, 1);
+    mbar_init(dq_lo_full, 1);
+    mbar_init(dq_hi_full, 1);
+    mbar_init(dq_lo_drained, 4);
     mbar_init(dq_hi_drained, 2);
     mbar_init(acc_full, 1);
     mbar_init(drain_bar, 1);
@@ -127,6 +165,7 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tma_prefetch_desc(&tmap_kv);
     tma_prefetch_desc(&tmap_kr);
     tma_prefetch_desc(&tmap_dq);
+    tma_prefetch_desc(&tmap_dq32);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, 512);
@@ -137,8 +176,9 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   // tensor-memory columns
-  constexpr uint32_t COL_ST = 0;      // 2 x 64   (S^T, later dQ^T of head elements 0..127)
-  constexpr uint32_t COL_DPT = 128;   // 64       (dP^T, later dQ^T of head elements 64..191)
+  constexpr uint32_t COL_ST = 0;      // 64
+  constexpr uint32_t COL_DPT = 64;    // 64
+  constexpr uint32_t COL_DQ = 128;    // 64
   constexpr uint32_t COL_DV = 192;    // 128
   constexpr uint32_t COL_DK = 320;    // 192
 
@@ -152,33 +192,40 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tma_load_3d(sV + h * UNIT_BYTES, &tmap_kv, kv_full, head * DKV + DV + h * 64, k0, batch);
       }
       tma_load_3d(sK + 2 * UNIT_BYTES, &tmap_kr, kv_full, 0, k0, batch);
-      int issued = 0;
+      int q_issued = 0, do_issued = 0;
       bool ok = true;
       for (int it = 0; it < n_it && ok; ++it) {
-        const int stage = it % QDO_STAGES;
-        const uint32_t phase = (it / QDO_STAGES) & 1;
-        ok = mbar_wait_bounded(&qdo_empty[stage], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier,
-                               blockIdx.x);
-        if (!ok) break;
+        const int slot = it % RING;
+        const uint32_t phase = (it / RING) & 1;
         const int q0 = (i_start + it) * BQ;
-        uint8_t* dq = sQdO + stage * STAGE_BYTES;
-        mbar_arrive_expect_tx(&qdo_full[stage], STAGE_BYTES);
+        ok = mbar_wait_bounded(&q_empty[slot], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier, blockIdx.x);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&q_full[slot], Q_BYTES);
 #pragma unroll
         for (int h = 0; h < 3; ++h)
-          tma_load_3d(dq + h * QSUB_BYTES, &tmap_q, &qdo_full[stage], head * DQK + h * 64, q0, batch);
+          tma_load_3d(sQ + slot * Q_BYTES + h * QSUB_BYTES, &tmap_q, &q_full[slot], head * DQK + h * 64, q0, batch);
+        ++q_issued;
+        ok = mbar_wait_bounded(&do_empty[slot], phase ^ 1, abort_flag, p.status, kTimeoutEmptyBarrier, blockIdx.x);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&do_full[slot], DO_BYTES);
 #pragma unroll
         for (int h = 0; h < 2; ++h)
-          tma_load_3d(dq + Q_BYTES + h * QSUB_BYTES, &tmap_do, &qdo_full[stage], head * DV + h * 64, q0, batch);
-        ++issued;
+          tma_load_3d(sDO + slot * DO_BYTES + h * QSUB_BYTES, &tmap_do, &do_full[slot], head * DV + h * 64, q0, batch);
+        ++do_issued;
       }
       if (!ok) {
+        // wait (bounded) for the copies already issued, so that none lands after the CTA exits
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(kv_full, 0) && globaltimer_ns() - t0 < 100000000ull) {}
-        for (int b = 1; b <= min(issued, QDO_STAGES); ++b) {
-          const int it = issued - b;
+        for (int b = 1; b <= min(q_issued, RING); ++b) {
+          const int it = q_issued - b;
           const uint64_t t1 = globaltimer_ns();
-          while (!mbar_try_wait(&qdo_full[it % QDO_STAGES], (it / QDO_STAGES) & 1) &&
-                 globaltimer_ns() - t1 < 100000000ull) {}
+          while (!mbar_try_wait(&q_full[it % RING], (it / RING) & 1) && globaltimer_ns() - t1 < 100000000ull) {}
+        }
+        for (int b = 1; b <= min(do_issued, RING); ++b) {
+          const int it = do_issued - b;
+          const uint64_t t1 = globaltimer_ns();
+          while (!mbar_try_wait(&do_full[it % RING], (it / RING) & 1) && globaltimer_ns() - t1 < 100000000ull) {}
         }
       }
     }
@@ -189,29 +236,39 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       constexpr uint32_t idesc_dv = make_idesc(1, 1, 0, 1, BN, DV);    // P^T (K-major) x dO (MN-major)
       constexpr uint32_t idesc_dk = make_idesc(1, 1, 0, 1, BN, DQK);   // dS^T (K-major) x Q (MN-major)
       constexpr uint32_t idesc_dq = make_idesc(1, 1, 1, 1, 128, BQ);   // K^T (MN-major) x dS^T (MN-major)
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdO),
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
                      pt_addr = smem_u32(sPT);
       bool ok = true;
       const uint64_t k_desc = make_smem_desc_sw128(k_addr, 0, 1024);               // K as K-major A
       const uint64_t v_desc = make_smem_desc_sw128(v_addr, 0, 1024);               // V as K-major A
       const uint64_t kt_desc = make_smem_desc_sw128(k_addr, UNIT_BYTES, 1024);     // K^T as MN-major A
-      const uint64_t qk_desc = make_smem_desc_sw128(qdo_addr, 0, 1024);            // Q / dO as K-major B
-      const uint64_t qm_desc = make_smem_desc_sw128(qdo_addr, QSUB_BYTES, 1024);   // Q / dO as MN-major B
+      const uint64_t qk_desc = make_smem_desc_sw128(q_addr, 0, 1024);              // Q as K-major B
+      const uint64_t qm_desc = make_smem_desc_sw128(q_addr, QSUB_BYTES, 1024);     // Q as MN-major B
+      const uint64_t dok_desc = make_smem_desc_sw128(do_addr, 0, 1024);            // dO as K-major B
+      const uint64_t dom_desc = make_smem_desc_sw128(do_addr, QSUB_BYTES, 1024);   // dO as MN-major B
       const uint64_t ptk_desc = make_smem_desc_sw128(pt_addr, 0, 1024);            // P^T / dS^T as K-major A
       const uint64_t ptm_desc = make_smem_desc_sw128(pt_addr, PT_BYTES, 1024);     // dS^T as MN-major B
+      auto wait_on = [&](uint64_t* bar, uint32_t parity, int code) {
+        return mbar_wait_bounded(bar, parity, abort_flag, p.status, code, blockIdx.x);
+      };
+      auto q_ready = [&](int it) { return wait_on(&q_full[it % RING], (it / RING) & 1, kTimeoutFullBarrier); };
+      auto do_ready = [&](int it) { return wait_on(&do_full[it % RING], (it / RING) & 1, kTimeoutFullBarrier); };
+      // S^T(it) = K Q^T: 3 units of 64 columns, 4 steps of 16 columns (32 bytes) each
       auto issue_st = [&](int it) {
-        const int b = it & 1;
-        const uint64_t qa = desc_at(qk_desc, (it % QDO_STAGES) * STAGE_BYTES);
+        const uint64_t qa = desc_at(qk_desc, (it % RING) * Q_BYTES);
+        if (!(p.probe & 16))
 #pragma unroll
         for (int kb = 0; kb < 3; ++kb)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_f16(tmem_base + COL_ST + b * BQ, desc_at(k_desc, kb * UNIT_BYTES + kk * 32),
+            umma_f16(tmem_base + COL_ST, desc_at(k_desc, kb * UNIT_BYTES + kk * 32),
                      desc_at(qa, kb * QSUB_BYTES + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
-        umma_commit(&st_full[b]);
+        umma_commit(st_full);
       };
+      // dP^T(it) = V dO^T
       auto issue_dpt = [&](int it) {
-        const uint64_t doa = desc_at(qk_desc, (it % QDO_STAGES) * STAGE_BYTES + Q_BYTES);
+        const uint64_t doa = desc_at(dok_desc, (it % RING) * DO_BYTES);
+        if (!(p.probe & 16))
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
@@ -220,61 +277,94 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                      desc_at(doa, kb * QSUB_BYTES + kk * 32), idesc_st, (kb | kk) ? 1u : 0u);
         umma_commit(dpt_full);
       };
-      auto wait_qdo = [&](int it) {
-        return mbar_wait_bounded(&qdo_full[it % QDO_STAGES], (it / QDO_STAGES) & 1, abort_flag, p.status,
-                                 kTimeoutFullBarrier, blockIdx.x);
-      };
-      ok = mbar_wait_bounded(kv_full, 0, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
-      if (ok) ok = wait_qdo(0);
+      ok = wait_on(kv_full, 0, kTimeoutFullBarrier);
+      if (ok) ok = q_ready(0);
       if (ok) {
         tc_fence_after();
         issue_st(0);
+        ok = do_ready(0);
+      }
+      if (ok) {
+        tc_fence_after();
         issue_dpt(0);
+      }
+      if (ok && n_it > 1) {
+        ok = wait_on(st_consumed, 0, kTimeoutTmemEmpty);
+        if (ok) ok = q_ready(1);
+        if (ok) {
+          tc_fence_after();
+          issue_st(1);
+        }
       }
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
-        const uint32_t par = (it >> 1) & 1;
-        ok = mbar_wait_bounded(&ds_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        ok = wait_on(&ds_full[b], (it >> 1) & 1, kTimeoutTmemFull);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t qa = desc_at(qm_desc, (it % QDO_STAGES) * STAGE_BYTES);
-        const uint64_t doa = desc_at(qa, Q_BYTES);
+        // dP^T of the next step first: its softmax is waiting for nothing else
+        if (it + 1 < n_it) {
+          ok = do_ready(it + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dpt(it + 1);
+        }
+        const uint64_t qa = desc_at(qm_desc, (it % RING) * Q_BYTES);
+        const uint64_t doa = desc_at(dom_desc, (it % RING) * DO_BYTES);
         const uint64_t pta = desc_at(ptk_desc, b * 2 * PT_BYTES);
         const uint64_t dsa = desc_at(pta, PT_BYTES);
         const uint64_t dsm = desc_at(ptm_desc, b * 2 * PT_BYTES + PT_BYTES);
         const uint32_t first = it ? 1u : 0u;
-        // dQ^T = K^T dS^T (contraction over the 128 key rows: 8 steps of 16): head elements 0..127
-        // from units 0, 1 of K into the S^T buffer, 64..191 from units 1, 2 into the dP^T buffer
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + COL_ST + b * BQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
-                   kk ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + COL_DPT, desc_at(kt_desc, UNIT_BYTES + kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
-                   kk ? 1u : 0u);
-        umma_commit(&dq_full[b]);
-        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem_base + COL_DV, desc_at(pta, kk * 32), desc_at(doa, kk * 2048), idesc_dv, kk ? 1u : first);
+        // dK += dS^T Q ; dV += P^T dO   (contraction over the 64 query rows: 4 steps of 16); each
+        // frees its ring slot, so that the loads of step it + 2 start as early as possible
+        if (!(p.probe & 8))
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_f16(tmem_base + COL_DK, desc_at(dsa, kk * 32), desc_at(qa, kk * 2048), idesc_dk, kk ? 1u : first);
-        umma_commit(&qdo_empty[it % QDO_STAGES]);
-        if (it + 1 < n_it) {
-          ok = wait_qdo(it + 1);
-          // the other S^T buffer holds the lower dQ^T tile of the step before this one
-          if (ok && it >= 1)
-            ok = mbar_wait_bounded(&dq_lo_drained[b ^ 1], ((it - 1) >> 1) & 1, abort_flag, p.status, kTimeoutTmemEmpty,
-                                   blockIdx.x);
+        umma_commit(&q_empty[it % RING]);
+        if (!(p.probe & 8))
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16(tmem_base + COL_DV, desc_at(pta, kk * 32), desc_at(doa, kk * 2048), idesc_dv, kk ? 1u : first);
+        umma_commit(&do_empty[it % RING]);
+        // dQ^T = K^T dS^T (contraction over the 128 key rows: 8 steps of 16), head elements 0..127
+        // from units 0, 1 of K; the buffer still holds the upper tile of the step before until
+        // that has been read out
+        if (it > 0) {
+          ok = wait_on(dq_hi_drained, (it - 1) & 1, kTimeoutTmemEmpty);
           if (!ok) break;
           tc_fence_after();
-          issue_st(it + 1);
-          ok = mbar_wait_bounded(dq_hi_drained, it & 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
+        }
+        if (!(p.probe & 4))
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + COL_DQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq, kk ? 1u : 0u);
+        umma_commit(dq_lo_full);
+        // S^T of step it + 2 while the lower dQ^T tile is read out -- if the scores of step it + 1
+        // are already in registers and Q(it + 2) has landed; otherwise after the upper tile
+        bool st_issued = it + 2 >= n_it;
+        if (!st_issued && mbar_try_wait(st_consumed, (it + 1) & 1) &&
+            mbar_try_wait(&q_full[(it + 2) % RING], ((it + 2) / RING) & 1)) {
+          tc_fence_after();
+          issue_st(it + 2);
+          st_issued = true;
+        }
+        ok = wait_on(dq_lo_drained, it & 1, kTimeoutTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        // head elements 64..191 from units 1, 2 of K
+        if (!(p.probe & 4))
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + COL_DQ, desc_at(kt_desc, UNIT_BYTES + kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
+                   kk ? 1u : 0u);
+        umma_commit(dq_hi_full);
+        if constexpr (DQ_DIRECT) umma_commit(&pt_free[b]);     // every reader of P^T / dS^T of this step was issued
+        if (!st_issued) {
+          ok = wait_on(st_consumed, (it + 1) & 1, kTimeoutTmemEmpty);
+          if (ok) ok = q_ready(it + 2);
           if (!ok) break;
           tc_fence_after();
-          issue_dpt(it + 1);
+          issue_st(it + 2);
         }
       }
       if (ok) umma_commit(acc_full);
@@ -296,15 +386,26 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const int kv_row = k0 + row;
       const bool row_live = kv_row < p.S;
       const int sw = row & 7;
+      const int c = wg;                       // this group's 32 query columns
       auto load_stat = [&](int it) -> float {
         // threads 0..63 fetch lse (scaled to log2), 64..127 fetch delta, of step `it`
         if (it >= n_it || tid >= 128) return 0.f;
         const int q = (i_start + it) * BQ + (tid & 63);
         if (q >= p.S) return tid < 64 ? INFINITY : 0.f;
         const int64_t off = (static_cast<int64_t>(batch) * p.H + head) * p.S + q;
-        return tid < 64 ? p.lse[off] * 1.4426950408889634f : p.delta[off];
+        return tid < 64 ? p.lse[off] : p.delta[off];     // raw: scaled when staged, a step later
       };
       float stat_next = load_stat(0);
+      const bool prof = p.prof != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
+      long long acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      long long tp = prof ? clock64() : 0;
+      auto tick = [&](int i) {
+        if (prof) {
+          const long long t = clock64();
+          acc[i] += t - tp;
+          tp = t;
+        }
+      };
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -314,15 +415,25 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         // b can be rewritten
         ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
-        if (tid < 128) stat[tid] = stat_next;
+        tick(0);
+        if (tid < 128) stat[tid] = tid < 64 ? stat_next * 1.4426950408889634f : stat_next;
         stat_next = load_stat(it + 1);
         __syncwarp();
         if (lane == 0 && wg == 0) mbar_arrive(&stat_full[b]);
         ok = mbar_wait_bounded(&stat_full[b], par, abort_flag, p.status, kTimeoutFullBarrier, blockIdx.x);
-        if (ok) ok = mbar_wait_bounded(&st_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
-        if (ok) ok = mbar_wait_bounded(dpt_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        tick(1);
+        if (ok) ok = mbar_wait_bounded(st_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
         if (!ok) break;
+        tick(2);
         tc_fence_after();
+        uint32_t rs[32];
+        tmem_ld_32x32b_x32(tmem_base + COL_ST + c * 32 + lane_off, rs);
+        tmem_ld_wait();
+        // the scores are in registers: the tensor core may form S^T of the next step but one
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(st_consumed);
+        tick(3);
         const int q0 = (i_start + it) * BQ;
         // visible iff key <= query:  column c >= kv_row - q0
         const int cmin = p.causal ? kv_row - q0 : 0;
@@ -330,106 +441,161 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const bool masked = (k0 + quarter * 32 + 32 > p.S) || (p.causal && k0 + quarter * 32 + 31 - q0 > 0);
         uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
         uint8_t* ds_row = pt_row + PT_BYTES;
+        float2 ev[16];
         {
-          const int c = wg;                    // this group's 32 query columns
-          uint32_t rs[32], rp[32];
-          tmem_ld_32x32b_x32(tmem_base + COL_ST + b * BQ + c * 32 + lane_off, rs);
-          tmem_ld_32x32b_x32(tmem_base + COL_DPT + c * 32 + lane_off, rp);
-          tmem_ld_wait();
-          uint32_t pk[16], dk[16];
+          uint32_t pk[16];
           const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
           for (int i2 = 0; i2 < 16; ++i2) {
             const float2 ls = *reinterpret_cast<const float2*>(stat + c * 32 + 2 * i2);
-            const float2 dl = *reinterpret_cast<const float2*>(stat + BQ + c * 32 + 2 * i2);
             float2 e = fma2(make_float2(__uint_as_float(rs[2 * i2]), __uint_as_float(rs[2 * i2 + 1])), sc2,
                             make_float2(-ls.x, -ls.y));
-            e.x = fast_exp2(e.x);
-            e.y = fast_exp2(e.y);
+            if (!(p.probe & 2)) {
+              e.x = fast_exp2(e.x);
+              e.y = fast_exp2(e.y);
+            }
             if (masked) {
               const int col = c * 32 + 2 * i2;
               if (!row_live || col < cmin) e.x = 0.f;
               if (!row_live || col + 1 < cmin) e.y = 0.f;
             }
-            const float2 d = mul2(e, add2(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])),
-                                          make_float2(-dl.x, -dl.y)));
-            const __nv_bfloat162 eb = __floats2bfloat162_rn(e.x, e.y), db = __floats2bfloat162_rn(d.x, d.y);
+            ev[i2] = e;
+            const __nv_bfloat162 eb = __floats2bfloat162_rn(e.x, e.y);
             pk[i2] = *reinterpret_cast<const uint32_t*>(&eb);
-            dk[i2] = *reinterpret_cast<const uint32_t*>(&db);
           }
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             const int chunk = c * 4 + q4;
             *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) =
                 make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+          }
+        }
+        tick(4);
+        ok = mbar_wait_bounded(dpt_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        if (!ok) break;
+        tick(5);
+        tc_fence_after();
+        {
+          uint32_t rp[32], dk[16];
+          tmem_ld_32x32b_x32(tmem_base + COL_DPT + c * 32 + lane_off, rp);
+          tmem_ld_wait();
+          tick(6);
+#pragma unroll
+          for (int i2 = 0; i2 < 16; ++i2) {
+            const float2 dl = *reinterpret_cast<const float2*>(stat + BQ + c * 32 + 2 * i2);
+            const float2 d = mul2(ev[i2], add2(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])),
+                                               make_float2(-dl.x, -dl.y)));
+            const __nv_bfloat162 db = __floats2bfloat162_rn(d.x, d.y);
+            dk[i2] = *reinterpret_cast<const uint32_t*>(&db);
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = c * 4 + q4;
             *reinterpret_cast<uint4*>(ds_row + ((chunk ^ sw) << 4)) =
                 make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
           }
         }
+        tick(7);
         fence_proxy_async();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ds_full[b]);
+        tick(8);
+      }
+      if (prof) {
+        for (int i = 0; i < 9; ++i) p.prof[i] = acc[i];
+        p.prof[9] = n_it;
       }
     } else {
       // ------------------------------------------------------ dQ reduction --
-      // dQ^T (lane = head element, column = query row) is transposed through the P^T / dS^T
-      // buffer of the same step -- free once the products of the step have retired -- as dense
-      // fp32 [64 query rows x 32] tiles of 8 KB, one per warp, which TMA reduces add to the fp32
-      // dQ in global memory.  Warps 2 and 3 own lanes 64..127, where the second product left the
-      // head elements 128..191: they read those out first (the next dP^T waits for that buffer),
-      // then their share of the first product through the same staging tile.
+      // dQ^T (lane = head element, column = query row) is transposed through shared memory as
+      // dense fp32 tiles with 32 head elements per row, which TMA reduces add to the fp32 dQ in
+      // global memory.  The lower product is read out first; its staging tiles ([32 query rows x
+      // 32], two rounds per warp) lie over P^T of this step, whose only reader (the dV product)
+      // was issued before it.  Warps 2 and 3 own lanes 64..127, where the upper product leaves
+      // the head elements 128..191: their tiles ([64 query rows x 32]) lie over dS^T, free once
+      // that product -- the last reader -- has retired.
       const bool has_hi = quarter >= 2;
+      const bool staged = !(p.probe & 1);
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
-        const uint32_t par = (it >> 1) & 1;
-        ok = mbar_wait_bounded(&dq_full[b], par, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        ok = mbar_wait_bounded(dq_lo_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
         if (!ok) break;
         tc_fence_after();
         const int q0 = (i_start + it) * BQ;
-        uint8_t* tile = sPT + b * 2 * PT_BYTES + quarter * (BQ * 32 * 4);
-        float* stage = reinterpret_cast<float*>(tile) + lane;
+        uint8_t* lo_tile = sPT + b * 2 * PT_BYTES + quarter * (32 * 32 * 4);
+        uint8_t* hi_tile = sPT + b * 2 * PT_BYTES + PT_BYTES + (quarter & 1) * (BQ * 32 * 4);
         uint32_t r[64];
-        if (has_hi) {
-          tmem_ld32(tmem_base + COL_DPT + lane_off, r);
-          tmem_ld32(tmem_base + COL_DPT + 32 + lane_off, r + 32);
-          tmem_ld_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(dq_hi_drained);    // the dP^T buffer may be overwritten
-        }
-        // the staging tiles lie over P^T / dS^T of this step: the dV / dK products, issued after
-        // the dQ^T products, must have retired as well (their commit frees the Q / dO stage)
-        ok = mbar_wait_bounded(&qdo_empty[it % QDO_STAGES], (it / QDO_STAGES) & 1, abort_flag, p.status,
-                               kTimeoutEmptyBarrier, blockIdx.x);
-        if (!ok) break;
-        if (has_hi) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) {
-            tma_reduce_add_3d(&tmap_dq, tile, head * DQK + 128 + (quarter - 2) * 32, q0, batch);
-            tma_store_commit();
-            tma_store_wait_read<0>();
-          }
-          __syncwarp();
-        }
-        tmem_ld32(tmem_base + COL_ST + b * BQ + lane_off, r);
-        tmem_ld32(tmem_base + COL_ST + b * BQ + 32 + lane_off, r + 32);
+        tmem_ld32(tmem_base + COL_DQ + lane_off, r);
+        tmem_ld32(tmem_base + COL_DQ + 32 + lane_off, r + 32);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&dq_lo_drained[b]);   // the S^T buffer may be overwritten
+        if (lane == 0) mbar_arrive(dq_lo_drained);       // the upper product may overwrite the buffer
+        float* dq_row = p.dQ + ((static_cast<int64_t>(batch) * p.S + q0) * p.H + head) * DQK + quarter * 32 + lane;
+        const int64_t dq_stride = static_cast<int64_t>(p.H) * DQK;
+        const int q_live = min(BQ, p.S - q0);
+        if constexpr (DQ_DIRECT) {
+          if (staged) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_3d(&tmap_dq, tile, head * DQK + quarter * 32, q0, batch);
-          tma_store_commit();
-          tma_store_wait_read<0>();
-          mbar_arrive(&pt_free[b]);                   // 4 arrivals: the softmax groups may write P^T / dS^T again
+            for (int i = 0; i < 64; ++i)
+              if (i < q_live) atomicAdd(dq_row + i * dq_stride, __uint_as_float(r[i]) * p.scale);
+          }
+        } else if (staged) {
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            float* stage = reinterpret_cast<float*>(lo_tile) + lane;
+            if (h == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
+            } else {
+              if (lane == 0) tma_store_wait_read<0>();   // round 0 has left the tile
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) stage[i * 32] = __uint_as_float(r[32 + i]) * p.scale;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tmap_dq32, lo_tile, head * DQK + quarter * 32, q0 + h * 32, batch);
+              tma_store_commit();
+            }
+          }
+        }
+        if (has_hi) {
+          ok = mbar_wait_bounded(dq_hi_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+          if (!ok) break;
+          tc_fence_after();
+          tmem_ld32(tmem_base + COL_DQ + lane_off, r);
+          tmem_ld32(tmem_base + COL_DQ + 32 + lane_off, r + 32);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dq_hi_drained);     // the next lower product may overwrite the buffer
+          if constexpr (DQ_DIRECT) {
+            if (staged) {
+#pragma unroll
+              for (int i = 0; i < 64; ++i)
+                if (i < q_live) atomicAdd(dq_row + 64 + i * dq_stride, __uint_as_float(r[i]) * p.scale);
+            }
+          } else if (staged) {
+            float* stage = reinterpret_cast<float*>(hi_tile) + lane;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tmap_dq, hi_tile, head * DQK + 128 + (quarter - 2) * 32, q0, batch);
+              tma_store_commit();
+            }
+          }
+        }
+        if constexpr (!DQ_DIRECT) {
+          if (lane == 0) {
+            tma_store_wait_read<0>();
+            mbar_arrive(&pt_free[b]);                 // 4 arrivals: the softmax groups may write P^T / dS^T again
+          }
+          __syncwarp();
         }
       }
       if (lane == 0) tma_store_wait<0>();
@@ -502,6 +668,20 @@ __global__ void mla_sum_heads_kernel(const __nv_bfloat16* __restrict__ in, __nv_
 
 using namespace hpb;
 
+// Backward schedule: (batch, head) pairs per group; <= 0 = all pairs in one group (key-tile major).
+static int g_mla_bwd_head_group = 16;
+extern "C" void hpb_mla_attn_set_head_group(int pairs) { g_mla_bwd_head_group = pairs; }
+// Timing probes for the benchmarks (the gradients are wrong while one is set): see BwdParams::probe.
+static long long* g_mla_bwd_prof = nullptr;
+// Device buffer of 16 int64 that receives the phase timings of one softmax thread (nullptr = off).
+extern "C" void hpb_mla_attn_set_prof(long long* buf) { g_mla_bwd_prof = buf; }
+// dQ accumulation: 1 = red.global from registers (measured 2x slower: the 384 reductions per step back up the
+// load/store unit), 0 = staged tiles and TMA reduces (default).
+static int g_mla_bwd_dq_direct = 0;
+extern "C" void hpb_mla_attn_set_dq_direct(int on) { g_mla_bwd_dq_direct = on; }
+static int g_mla_bwd_probe = 0;
+extern "C" void hpb_mla_attn_set_probe(int mask) { g_mla_bwd_probe = mask; }
+
 // Backward.  q [B, S, H, 192], kv [B, S, H, 256] (k_nope | v), kr [B, S, 64], O / dO [B, S, H, 128] bf16
 // with the innermost dimension contiguous and row (token) / batch strides in elements; lse from the
 // forward.  Outputs (contiguous bf16): dQ [B, S, H, 192], dKV [B, S, H, 256] (dK nope | dV), dKR
@@ -524,7 +704,7 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
        reinterpret_cast<uintptr_t>(dkr_heads)) & 15)
     return -2;
   cudaFree(nullptr);
-  CUtensorMap tq, tdo, tkv, tkr, tdq;
+  CUtensorMap tq, tdo, tkv, tkr, tdq, tdq32;
   int r = make_tmap_bsd(&tq, q, B, S, H * mla::DQK, q_batch_stride, q_row_stride, mla::BQ);
   if (r) return r;
   r = make_tmap_bsd(&tdo, dO, B, S, H * mla::DV, do_batch_stride, do_row_stride, mla::BQ);
@@ -545,13 +725,21 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return static_cast<int>(cr);
+    box[1] = 32;      // the lower dQ tile is reduced in two rounds of 32 query rows
+    cr = enc(&tdq32, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return static_cast<int>(cr);
   }
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mla::mla_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(mla::mla_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          mla::BWD_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(mla::mla_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               mla::BWD_SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
@@ -571,13 +759,20 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.causal = causal;
+  p.head_group = g_mla_bwd_head_group > 0 ? g_mla_bwd_head_group : (1 << 30);
+  p.probe = g_mla_bwd_probe;
+  p.prof = g_mla_bwd_prof;
   p.lse = lse;
   p.delta = delta;
   p.dKV = reinterpret_cast<__nv_bfloat16*>(dKV);
   p.dKR = reinterpret_cast<__nv_bfloat16*>(dkr_heads);
   p.status = status;
   dim3 grid(((S + mla::BN - 1) / mla::BN) * H * B);
-  mla::mla_bwd_kernel<<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, p);
+  p.dQ = dq_acc;
+  if (g_mla_bwd_dq_direct)
+    mla::mla_bwd_kernel<true><<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, tdq32, p);
+  else
+    mla::mla_bwd_kernel<false><<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, tdq32, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   {

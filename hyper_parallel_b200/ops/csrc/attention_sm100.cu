@@ -424,6 +424,7 @@ struct BwdParams {
   int B, S, Hq, Hkv;
   float scale, scale_log2;
   int causal;
+  int head_group;      // (batch, kv head) pairs scheduled together
   const float* lse;    // [B, Hq, S]
   const float* delta;  // [B, Hq, S]  rowsum(dO o O)
   float* dQ;           // [B, S, Hq, 128] fp32, zero-initialised
@@ -461,8 +462,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int hb = static_cast<int>(blockIdx.x) % (p.Hkv * p.B);
-  const int jt = static_cast<int>(blockIdx.x) / (p.Hkv * p.B);   // causal: low tiles have the longest walk
+  // (batch, kv head) pairs are processed in groups of `head_group`: the CTAs that run at the same
+  // time then add into a few MB of the fp32 dQ (and re-read the same Q / dO), which stays in L2;
+  // inside a group the key tiles go in ascending order (causal: low tiles have the longest walk)
+  int hb, jt;
+  {
+    const int n_tiles = (p.S + BN - 1) / BN;
+    const int pairs = p.Hkv * p.B;
+    const int hg = max(1, min(p.head_group, pairs));
+    const int g0 = static_cast<int>(blockIdx.x) / (hg * n_tiles) * hg;
+    const int gsz = min(hg, pairs - g0);
+    const int r = static_cast<int>(blockIdx.x) - g0 * n_tiles;
+    jt = r / gsz;
+    hb = g0 + r % gsz;
+  }
   const int kv_head = hb % p.Hkv;
   const int batch = hb / p.Hkv;
   const int group = p.Hq / p.Hkv;
@@ -670,7 +683,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int q = (i_start + it % per_head) * BQ + (tid & 63);
         if (q >= p.S) return tid < 64 ? INFINITY : 0.f;
         const int64_t off = (static_cast<int64_t>(batch) * p.Hq + head) * p.S + q;
-        return tid < 64 ? p.lse[off] * 1.4426950408889634f : p.delta[off];
+        return tid < 64 ? p.lse[off] : p.delta[off];     // raw: scaled when staged, a step later
       };
       float stat_next = load_stat(0);
       for (int it = 0; it < n_it && ok; ++it) {
@@ -682,7 +695,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // b can be rewritten
         ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
-        if (tid < 128) stat[tid] = stat_next;
+        if (tid < 128) stat[tid] = tid < 64 ? stat_next * 1.4426950408889634f : stat_next;
         stat_next = load_stat(it + 1);
         __syncwarp();
         if (lane == 0 && wg == 0) mbar_arrive(&stat_full[b]);
@@ -827,6 +840,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
 using namespace hpb;
 
+// Backward schedule: (batch, kv head) pairs per group; <= 0 = all pairs in one group (key-tile major).
+static int g_bwd_head_group = 8;
+extern "C" void hpb_flash_attn_set_head_group(int pairs) { g_bwd_head_group = pairs; }
+
 // Forward variant: 1 = P stays in tensor memory (default), 0 = P goes through shared memory.
 static int g_fwd_p_in_tmem = 1;
 extern "C" void hpb_flash_attn_set_variant(int p_in_tmem) { g_fwd_p_in_tmem = p_in_tmem; }
@@ -936,6 +953,7 @@ extern "C" int hpb_flash_attn_bwd(const void* q, long long q_batch_stride, long 
   p.scale = softmax_scale;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.causal = causal;
+  p.head_group = g_bwd_head_group > 0 ? g_bwd_head_group : (1 << 30);
   p.lse = lse;
   p.delta = delta;
   p.dQ = dq_acc;
