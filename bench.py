@@ -40,6 +40,10 @@ def parse_args():
                          "global batch 8; moe_ep: DeepSeek-V3 4 layers, 256 experts, EP over all ranks, fp8; "
                          "pp: Llama-3-8B PP=4 x TP=2, 16 micro-batches")
     ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"], help="--config pp only")
+    ap.add_argument("--check", action="store_true",
+                    help="after the timed runs, rebuild the model on the NCCL path (HPB_FUSED_COMM=0) and compare "
+                         "the losses of the first two steps with those of the symmetric-memory kernels; the "
+                         "result goes into the JSON line (N > 1 only)")
     ap.add_argument("--metrics-jsonl", default=os.environ.get("HPB_METRICS_JSONL"),
                     help="also append the result (and the per-kernel-path switches) as one JSON line to this file")
     return ap.parse_args()
@@ -108,23 +112,26 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     cfg = model_config(args)
 
-    # public API: build on meta, shard with hsdp (full shard, level3), deferred init
-    model = Llama(cfg, device="meta")
-    for layer in model.layers:
-        hp.hsdp(layer, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
+    def build():
+        """Public API: build on meta, shard with hsdp (full shard, level3), deferred init."""
+        model = Llama(cfg, device="meta")
+        for layer in model.layers:
+            hp.hsdp(layer, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
+                    comm_async=world > 1)
+        hp.hsdp(model, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
                 comm_async=world > 1)
-    hp.hsdp(model, shard_size=world, threshold=0, optimizer_level="level3", comm_fusion=world > 1,
-            comm_async=world > 1)
-    for i, layer in enumerate(model.layers):
-        if i + 1 < len(model.layers):
-            layer.set_forward_prefetch_cells([model.layers[i + 1]])
-        if i > 0:
-            layer.set_backward_prefetch_cells([model.layers[i - 1]])
-    hp.init_parameters(model, device=dev, seed=0)
-    opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
-    opt.fuse_into_backward(model)       # optimizer update runs inside backward, per wrapped module
-    opt.init_state()
+        for i, layer in enumerate(model.layers):
+            if i + 1 < len(model.layers):
+                layer.set_forward_prefetch_cells([model.layers[i + 1]])
+            if i > 0:
+                layer.set_backward_prefetch_cells([model.layers[i - 1]])
+        hp.init_parameters(model, device=dev, seed=0)
+        opt = FusedAdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+        opt.fuse_into_backward(model)       # optimizer update runs inside backward, per wrapped module
+        opt.init_state()
+        return model, opt
 
+    model, opt = build()
     n_total = args.warmup + args.steps
     host = make_batches(cfg, args, rank, n_total)
     tokens_per_step = world * args.batch_per_gpu * args.seq_len
@@ -152,8 +159,11 @@ def run_ours(args):
 
     # ---- device-timed loop (inputs resident) --------------------------------
     dev_batches = host.to(dev)
+    first_losses = []
     for i in range(args.warmup):
-        step(dev_batches[i])
+        loss = step(dev_batches[i])
+        if args.check and i < 2:
+            first_losses.append(loss.item())
     native.check_status()
     barrier()
     launches0 = native.launch_count
@@ -195,6 +205,32 @@ def run_ours(args):
         pass
     peak_tflops = peaks.get("bf16_tflops_sustained", 1400.0)
     mfu = flops / (ms_per_step / 1e3) / (peak_tflops * 1e12)
+    check = None
+    if args.check and world > 1 and len(first_losses) == 2:
+        # the same two steps on NCCL collectives + separate kernels: step 0 checks the gathered weights,
+        # step 1 the reduced gradients and the sharded optimizer update
+        import gc
+        from hyper_parallel_b200.core.hsdp.hsdp_scheduler import reset_hsdp_registry
+        del model, opt
+        reset_hsdp_registry()
+        gc.collect()
+        torch.cuda.empty_cache()
+        prev = os.environ.get("HPB_FUSED_COMM")
+        os.environ["HPB_FUSED_COMM"] = "0"
+        try:
+            model, opt = build()
+            ref_losses = [step(dev_batches[i]).item() for i in range(2)]
+            native.check_status()
+            diff = max(abs(a - b) / max(abs(b), 1e-6) for a, b in zip(first_losses, ref_losses))
+            check = {"loss_fused": first_losses, "loss_nccl": ref_losses, "max_rel_diff": diff, "ok": diff < 2e-3}
+        except Exception as e:  # noqa: BLE001  (the benchmark line must still be printed)
+            check = {"error": repr(e)[:200], "ok": False}
+        finally:
+            if prev is None:
+                os.environ.pop("HPB_FUSED_COMM", None)
+            else:
+                os.environ["HPB_FUSED_COMM"] = prev
+        barrier()
     from hyper_parallel_b200.utils.logging import MetricsWriter, get_logger
     log = get_logger("hyper_parallel_b200.bench")
     log.info("llama %s x%d: %.1f ms/step device-timed, %.1f ms/step end to end, mfu %.3f", args.model, world,
@@ -217,6 +253,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            **({"check": check} if check is not None else {}),
         }))
     if world > 1:
         dist.destroy_process_group()
