@@ -66,8 +66,6 @@ def main():
                     help="timing probe of the MLA backward (wrong results): 1 = no dQ reduce, 2 = no exponentials, "
                          "4 / 8 / 16 = without the dQ / dK, dV / score products")
     args = ap.parse_args()
-    if os.environ.get("HPB_MLA_DQ_DIRECT") is not None:
-        native.lib().hpb_mla_attn_set_dq_direct(int(os.environ["HPB_MLA_DQ_DIRECT"]))
     if args.mla_probe:
         native.lib().hpb_mla_attn_set_probe(args.mla_probe)
     if args.bwd_group is not None:

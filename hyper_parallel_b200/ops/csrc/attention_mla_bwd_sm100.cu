@@ -10,9 +10,10 @@
 //   P^T  = exp2(S^T c - lse),  dS^T = P^T o (dP^T - D)        -> bf16, shared memory
 //   dV  += P^T dO           [kv 128 x 128]    accumulated over the whole walk
 //   dK  += dS^T Q           [kv 128 x 192]    accumulated over the whole walk
-//   dQ^T = K^T dS^T         [d 192 x q 64]    as two products of 128 rows (head elements 0..127,
-//                                             then 64..191, of which rows 64..127 = elements
-//                                             128..191 are read out) through ONE buffer
+//   dQ^T = K^T dS^T         [d 192 x q 64]    as two products of 128 rows: head elements 0..127 into
+//                                             a buffer of their own, 64..191 (of which rows 64..127 =
+//                                             elements 128..191 are read out) into the S^T buffer
+//                                             between two score tiles
 //
 // Tensor memory (512 columns): S^T 64 | dP^T 64 | dQ^T 64 | dV 128 | dK 192.  The two accumulators
 // leave room for three 64-column buffers only, so nothing is double buffered; instead every buffer
@@ -20,18 +21,21 @@
 //
 //   * the softmax warps release S^T as soon as their scores are in registers, so S^T of step
 //     i + 2 is formed while step i + 1 is still being exponentiated;
-//   * P^T is written from S^T alone, before dP^T of the step is awaited;
-//   * per step the tensor core runs dP^T(i + 1) first (the softmax of step i + 1 waits for it),
-//     then dK(i), dV(i) (which free the Q / dO ring slots), the lower dQ^T(i), S^T(i + 2) while
-//     that tile is read out, and the upper dQ^T(i).
+//   * P^T (bf16 pairs) goes back into tensor memory, over the dP^T columns that the same thread has
+//     just read, and is the A operand of the dV product from there; only dS^T goes through shared
+//     memory (it is also a B operand), double buffered and handed back by the tensor core;
+//   * per step the tensor core runs dV(i), dP^T(i + 1) (the softmax of step i + 1 waits for it;
+//     in-order execution keeps it behind the read of P^T), dK(i), the upper dQ^T(i) into the S^T
+//     buffer (the scores of step i + 1 are in registers by then), the lower dQ^T(i) while that
+//     tile is read out, and then S^T(i + 2).
 //
 //   warp 0       TMA producer: K, V once; Q_i and dO_i through two 2-slot rings
 //   warp 1       MMA issuer
 //   warps 2-9    softmax / dS: two groups of four warps, each owning 32 of the 64 query columns;
 //                they also write dV / dK at the end
-//   warps 10-13  dQ read-out: fp32 tiles staged in shared memory (over P^T for the lower product,
-//                over dS^T for the upper one, once their readers have retired) and added to the
-//                fp32 dQ in global memory by TMA reduces
+//   warps 10-13  dQ read-out: fp32 tiles staged in a buffer of their own (32 KB) and added to the
+//                fp32 dQ in global memory by TMA reduces, so the read-out never holds back the
+//                softmax warps
 //
 // dK of the rotary columns is written per head; the caller sums it over the heads.
 // Every wait is bounded; on expiry a status code is recorded and all roles unwind.
@@ -55,8 +59,9 @@ constexpr int DO_BYTES = 2 * QSUB_BYTES;        // 16 KB
 constexpr int RING = 2;
 constexpr int PT_BYTES = BN * BQ * 2;           // 16 KB
 constexpr int BWD_THREADS = 448;
-constexpr int BWD_SMEM = 3 * UNIT_BYTES + 2 * UNIT_BYTES + RING * (Q_BYTES + DO_BYTES) + 2 * 2 * PT_BYTES +
-                         2 * 2 * BQ * 4 + 1024 + 256;
+constexpr int STAGE_TILE = BQ * 32 * 4;          // 8 KB: [64 query rows x 32 head elements] fp32
+constexpr int BWD_SMEM = 3 * UNIT_BYTES + 2 * UNIT_BYTES + RING * (Q_BYTES + DO_BYTES) + 2 * PT_BYTES +
+                         4 * STAGE_TILE + 2 * 2 * BQ * 4 + 1024 + 256;
 static_assert(BWD_SMEM <= 227 * 1024, "shared memory budget");
 
 struct BwdParams {
@@ -68,22 +73,16 @@ struct BwdParams {
                          // 4 / 8 / 16 = the dQ^T / dK, dV / S^T, dP^T products are not issued
   const float* lse;      // [B, H, S]
   const float* delta;    // [B, H, S]  rowsum(dO o O)
-  float* dQ;             // [B, S, H, 192] fp32, zero-initialised (DQ_DIRECT)
   __nv_bfloat16* dKV;    // [B, S, H, 256]: dK nope | dV
   __nv_bfloat16* dKR;    // [B, S, H, 64]: dK of the rotary columns, per head
   int* status;
   long long* prof;       // optional [16]: cycles that one softmax thread of CTA 0 spent per phase, summed over its walk
 };
 
-// DQ_DIRECT: the dQ warps add their registers to the fp32 dQ with coalesced red.global instructions
-// (lane = head element) instead of staging tiles for TMA reduces; the P^T / dS^T buffers are then
-// handed back by the tensor core alone.
-template <bool DQ_DIRECT>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_kr,
-               const __grid_constant__ CUtensorMap tmap_dq, const __grid_constant__ CUtensorMap tmap_dq32,
-               const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -91,8 +90,9 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint8_t* sV = sK + 3 * UNIT_BYTES;                          // 2 units: columns 0..63, 64..127
   uint8_t* sQ = sV + 2 * UNIT_BYTES;                          // ring of Q tiles (3 x 8 KB each)
   uint8_t* sDO = sQ + RING * Q_BYTES;                         // ring of dO tiles (2 x 8 KB each)
-  uint8_t* sPT = sDO + RING * DO_BYTES;                       // per buffer: P^T (16 KB) | dS^T (16 KB)
-  float* sStat = reinterpret_cast<float*>(sPT + 2 * 2 * PT_BYTES);   // [2][2][64]: lse * log2e, delta
+  uint8_t* sDS = sDO + RING * DO_BYTES;                       // dS^T, two buffers of 16 KB
+  uint8_t* sStage = sDS + 2 * PT_BYTES;                       // dQ staging: one 8 KB tile per dQ warp
+  float* sStat = reinterpret_cast<float*>(sStage + 4 * STAGE_TILE);  // [2][2][64]: lse * log2e, delta
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(sStat + 2 * 2 * BQ);
   uint64_t* q_full = kv_full + 1;                // [2]
   uint64_t* q_empty = q_full + RING;             // [2]
@@ -102,7 +102,7 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint64_t* st_consumed = st_full + 1;           // [1]  S^T of a step is in registers (8 warp arrivals)
   uint64_t* dpt_full = st_consumed + 1;          // [1]  dP^T of a step complete
   uint64_t* ds_full = dpt_full + 1;              // [2]  P^T / dS^T written, dP^T read (8 warp arrivals)
-  uint64_t* pt_free = ds_full + 2;               // [2]  dQ staging over P^T / dS^T has been read (4 warp arrivals)
+  uint64_t* pt_free = ds_full + 2;               // [2]  every product reading dS^T buffer b has retired
   uint64_t* dq_lo_full = pt_free + 2;            // [1]
   uint64_t* dq_hi_full = dq_lo_full + 1;         // [1]
   uint64_t* dq_lo_drained = dq_hi_full + 1;      // [1]  (4 warp arrivals)
@@ -146,7 +146,7 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ds_full[b], 8);
-      mbar_init(&pt_free[b], DQ_DIRECT ? 1 : 4);
+      mbar_init(&pt_free[b], 1);
       mbar_init(&stat_full[b], 4);
     }
     mbar_init(st_full, 1);
@@ -165,7 +165,6 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tma_prefetch_desc(&tmap_kv);
     tma_prefetch_desc(&tmap_kr);
     tma_prefetch_desc(&tmap_dq);
-    tma_prefetch_desc(&tmap_dq32);
   }
   if (warp == 1) {
     tmem_alloc(tmem_base_slot, 512);
@@ -237,7 +236,7 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       constexpr uint32_t idesc_dk = make_idesc(1, 1, 0, 1, BN, DQK);   // dS^T (K-major) x Q (MN-major)
       constexpr uint32_t idesc_dq = make_idesc(1, 1, 1, 1, 128, BQ);   // K^T (MN-major) x dS^T (MN-major)
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
-                     pt_addr = smem_u32(sPT);
+                     ds_addr = smem_u32(sDS);
       bool ok = true;
       const uint64_t k_desc = make_smem_desc_sw128(k_addr, 0, 1024);               // K as K-major A
       const uint64_t v_desc = make_smem_desc_sw128(v_addr, 0, 1024);               // V as K-major A
@@ -246,8 +245,8 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const uint64_t qm_desc = make_smem_desc_sw128(q_addr, QSUB_BYTES, 1024);     // Q as MN-major B
       const uint64_t dok_desc = make_smem_desc_sw128(do_addr, 0, 1024);            // dO as K-major B
       const uint64_t dom_desc = make_smem_desc_sw128(do_addr, QSUB_BYTES, 1024);   // dO as MN-major B
-      const uint64_t ptk_desc = make_smem_desc_sw128(pt_addr, 0, 1024);            // P^T / dS^T as K-major A
-      const uint64_t ptm_desc = make_smem_desc_sw128(pt_addr, PT_BYTES, 1024);     // dS^T as MN-major B
+      const uint64_t dsk_desc = make_smem_desc_sw128(ds_addr, 0, 1024);            // dS^T as K-major A
+      const uint64_t dsm_desc = make_smem_desc_sw128(ds_addr, PT_BYTES, 1024);     // dS^T as MN-major B
       auto wait_on = [&](uint64_t* bar, uint32_t parity, int code) {
         return mbar_wait_bounded(bar, parity, abort_flag, p.status, code, blockIdx.x);
       };
@@ -296,41 +295,69 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           issue_st(1);
         }
       }
+      const bool prof = p.prof != nullptr && blockIdx.x == 0;
+      long long acc[5] = {0, 0, 0, 0, 0};
+      long long tp = prof ? clock64() : 0;
+      auto tick = [&](int i) {
+        if (prof) {
+          const long long t = clock64();
+          acc[i] += t - tp;
+          tp = t;
+        }
+      };
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         ok = wait_on(&ds_full[b], (it >> 1) & 1, kTimeoutTmemFull);
         if (!ok) break;
+        tick(0);
         tc_fence_after();
-        // dP^T of the next step first: its softmax is waiting for nothing else
+        const uint64_t qa = desc_at(qm_desc, (it % RING) * Q_BYTES);
+        const uint64_t doa = desc_at(dom_desc, (it % RING) * DO_BYTES);
+        const uint64_t dsa = desc_at(dsk_desc, b * PT_BYTES);
+        const uint64_t dsm = desc_at(dsm_desc, b * PT_BYTES);
+        const uint32_t first = it ? 1u : 0u;
+        // dV += P^T dO (contraction over the 64 query rows: 4 steps of 16).  P^T lies in the dP^T
+        // buffer: query rows 0..31 in columns 0..15, 32..63 in columns 32..47 (8 columns per step)
+        if (!(p.probe & 8))
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_DPT + (kk >> 1) * 32 + (kk & 1) * 8, desc_at(doa, kk * 2048),
+                      idesc_dv, kk ? 1u : first);
+        umma_commit(&do_empty[it % RING]);
+        // dP^T of the next step: its softmax is waiting for nothing else (executes behind dV, which
+        // reads the buffer it overwrites)
         if (it + 1 < n_it) {
           ok = do_ready(it + 1);
           if (!ok) break;
           tc_fence_after();
           issue_dpt(it + 1);
         }
-        const uint64_t qa = desc_at(qm_desc, (it % RING) * Q_BYTES);
-        const uint64_t doa = desc_at(dom_desc, (it % RING) * DO_BYTES);
-        const uint64_t pta = desc_at(ptk_desc, b * 2 * PT_BYTES);
-        const uint64_t dsa = desc_at(pta, PT_BYTES);
-        const uint64_t dsm = desc_at(ptm_desc, b * 2 * PT_BYTES + PT_BYTES);
-        const uint32_t first = it ? 1u : 0u;
-        // dK += dS^T Q ; dV += P^T dO   (contraction over the 64 query rows: 4 steps of 16); each
-        // frees its ring slot, so that the loads of step it + 2 start as early as possible
+        // dK += dS^T Q; frees the Q slot, so that the load of step it + 2 starts early
         if (!(p.probe & 8))
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           umma_f16(tmem_base + COL_DK, desc_at(dsa, kk * 32), desc_at(qa, kk * 2048), idesc_dk, kk ? 1u : first);
         umma_commit(&q_empty[it % RING]);
-        if (!(p.probe & 8))
+        tick(1);
+        // dQ^T = K^T dS^T (contraction over the 128 key rows: 8 steps of 16).  Head elements 64..191
+        // (units 1, 2 of K) go into the S^T buffer, free once the scores of step it + 1 are in
+        // registers (the three products above have kept the tensor core busy meanwhile)
+        if (it + 1 < n_it) {
+          ok = wait_on(st_consumed, (it + 1) & 1, kTimeoutTmemEmpty);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        tick(2);
+        if (!(p.probe & 4))
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16(tmem_base + COL_DV, desc_at(pta, kk * 32), desc_at(doa, kk * 2048), idesc_dv, kk ? 1u : first);
-        umma_commit(&do_empty[it % RING]);
-        // dQ^T = K^T dS^T (contraction over the 128 key rows: 8 steps of 16), head elements 0..127
-        // from units 0, 1 of K; the buffer still holds the upper tile of the step before until
-        // that has been read out
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16(tmem_base + COL_ST, desc_at(kt_desc, UNIT_BYTES + kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
+                   kk ? 1u : 0u);
+        umma_commit(dq_hi_full);
+        // head elements 0..127 (units 0, 1 of K) go into the dQ^T buffer, free once the tile of the
+        // step before was read; this product runs while the upper tile is read out
         if (it > 0) {
-          ok = wait_on(dq_hi_drained, (it - 1) & 1, kTimeoutTmemEmpty);
+          ok = wait_on(dq_lo_drained, (it - 1) & 1, kTimeoutTmemEmpty);
           if (!ok) break;
           tc_fence_after();
         }
@@ -339,34 +366,19 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int kk = 0; kk < 8; ++kk)
           umma_f16(tmem_base + COL_DQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq, kk ? 1u : 0u);
         umma_commit(dq_lo_full);
-        // S^T of step it + 2 while the lower dQ^T tile is read out -- if the scores of step it + 1
-        // are already in registers and Q(it + 2) has landed; otherwise after the upper tile
-        bool st_issued = it + 2 >= n_it;
-        if (!st_issued && mbar_try_wait(st_consumed, (it + 1) & 1) &&
-            mbar_try_wait(&q_full[(it + 2) % RING], ((it + 2) / RING) & 1)) {
-          tc_fence_after();
-          issue_st(it + 2);
-          st_issued = true;
-        }
-        ok = wait_on(dq_lo_drained, it & 1, kTimeoutTmemEmpty);
-        if (!ok) break;
-        tc_fence_after();
-        // head elements 64..191 from units 1, 2 of K
-        if (!(p.probe & 4))
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16(tmem_base + COL_DQ, desc_at(kt_desc, UNIT_BYTES + kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
-                   kk ? 1u : 0u);
-        umma_commit(dq_hi_full);
-        if constexpr (DQ_DIRECT) umma_commit(&pt_free[b]);     // every reader of P^T / dS^T of this step was issued
-        if (!st_issued) {
-          ok = wait_on(st_consumed, (it + 1) & 1, kTimeoutTmemEmpty);
+        umma_commit(&pt_free[b]);     // every reader of dS^T of this step has been issued
+        tick(3);
+        if (it + 2 < n_it) {
+          ok = wait_on(dq_hi_drained, it & 1, kTimeoutTmemEmpty);
           if (ok) ok = q_ready(it + 2);
           if (!ok) break;
           tc_fence_after();
           issue_st(it + 2);
         }
+        tick(4);
       }
+      if (prof)
+        for (int i = 0; i < 5; ++i) p.prof[10 + i] = acc[i];
       if (ok) umma_commit(acc_full);
       if (!ok) {
         umma_commit(drain_bar);
@@ -410,9 +422,9 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
         float* stat = sStat + b * 2 * BQ;
-        // P^T / dS^T buffer b is free again (the dQ tiles staged in it have been read); this also
-        // means that all eight softmax warps have finished step it - 2, so the statistics buffer
-        // b can be rewritten
+        // dS^T buffer b is free again (the products of step it - 2 that read it have retired); this
+        // also means that all eight softmax warps have finished step it - 2, so the statistics
+        // buffer b can be rewritten
         ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
         tick(0);
@@ -439,11 +451,10 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int cmin = p.causal ? kv_row - q0 : 0;
         // warp-uniform: does any row of this warp hide any column of this step?
         const bool masked = (k0 + quarter * 32 + 32 > p.S) || (p.causal && k0 + quarter * 32 + 31 - q0 > 0);
-        uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
-        uint8_t* ds_row = pt_row + PT_BYTES;
+        uint8_t* ds_row = sDS + b * PT_BYTES + row * 128;
         float2 ev[16];
+        uint32_t pk[16];
         {
-          uint32_t pk[16];
           const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
           for (int i2 = 0; i2 < 16; ++i2) {
@@ -463,12 +474,6 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             const __nv_bfloat162 eb = __floats2bfloat162_rn(e.x, e.y);
             pk[i2] = *reinterpret_cast<const uint32_t*>(&eb);
           }
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int chunk = c * 4 + q4;
-            *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) =
-                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-          }
         }
         tick(4);
         ok = mbar_wait_bounded(dpt_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
@@ -479,6 +484,8 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           uint32_t rp[32], dk[16];
           tmem_ld_32x32b_x32(tmem_base + COL_DPT + c * 32 + lane_off, rp);
           tmem_ld_wait();
+          // P^T over the first 16 of the 32 columns just read (this thread's own)
+          tmem_st_32x32b_x16(tmem_base + COL_DPT + c * 32 + lane_off, pk);
           tick(6);
 #pragma unroll
           for (int i2 = 0; i2 < 16; ++i2) {
@@ -496,6 +503,7 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           }
         }
         tick(7);
+        tmem_st_wait();
         fence_proxy_async();
         tc_fence_before();
         __syncwarp();
@@ -508,94 +516,66 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
     } else {
       // ------------------------------------------------------ dQ reduction --
-      // dQ^T (lane = head element, column = query row) is transposed through shared memory as
-      // dense fp32 tiles with 32 head elements per row, which TMA reduces add to the fp32 dQ in
-      // global memory.  The lower product is read out first; its staging tiles ([32 query rows x
-      // 32], two rounds per warp) lie over P^T of this step, whose only reader (the dV product)
-      // was issued before it.  Warps 2 and 3 own lanes 64..127, where the upper product leaves
-      // the head elements 128..191: their tiles ([64 query rows x 32]) lie over dS^T, free once
-      // that product -- the last reader -- has retired.
+      // dQ^T (lane = head element, column = query row) is transposed through this warp's staging
+      // tile as a dense fp32 [64 query rows x 32 head elements] tile, which one TMA reduce adds to
+      // the fp32 dQ in global memory.  Warps 2 and 3 own lanes 64..127, where the upper product
+      // leaves the head elements 128..191: they pass a second tile per step through the same
+      // staging memory.
       const bool has_hi = quarter >= 2;
       const bool staged = !(p.probe & 1);
+      uint8_t* tile = sStage + quarter * STAGE_TILE;
+      float* stage = reinterpret_cast<float*>(tile) + lane;
       for (int it = 0; it < n_it && ok; ++it) {
-        const int b = it & 1;
-        ok = mbar_wait_bounded(dq_lo_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
-        if (!ok) break;
-        tc_fence_after();
         const int q0 = (i_start + it) * BQ;
-        uint8_t* lo_tile = sPT + b * 2 * PT_BYTES + quarter * (32 * 32 * 4);
-        uint8_t* hi_tile = sPT + b * 2 * PT_BYTES + PT_BYTES + (quarter & 1) * (BQ * 32 * 4);
         uint32_t r[64];
-        tmem_ld32(tmem_base + COL_DQ + lane_off, r);
-        tmem_ld32(tmem_base + COL_DQ + 32 + lane_off, r + 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(dq_lo_drained);       // the upper product may overwrite the buffer
-        float* dq_row = p.dQ + ((static_cast<int64_t>(batch) * p.S + q0) * p.H + head) * DQK + quarter * 32 + lane;
-        const int64_t dq_stride = static_cast<int64_t>(p.H) * DQK;
-        const int q_live = min(BQ, p.S - q0);
-        if constexpr (DQ_DIRECT) {
-          if (staged) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (i < q_live) atomicAdd(dq_row + i * dq_stride, __uint_as_float(r[i]) * p.scale);
-          }
-        } else if (staged) {
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            float* stage = reinterpret_cast<float*>(lo_tile) + lane;
-            if (h == 0) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
-            } else {
-              if (lane == 0) tma_store_wait_read<0>();   // round 0 has left the tile
-              __syncwarp();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) stage[i * 32] = __uint_as_float(r[32 + i]) * p.scale;
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_3d(&tmap_dq32, lo_tile, head * DQK + quarter * 32, q0 + h * 32, batch);
-              tma_store_commit();
-            }
-          }
-        }
         if (has_hi) {
+          // the upper tile first: the next score tile waits for its buffer
           ok = mbar_wait_bounded(dq_hi_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
           if (!ok) break;
           tc_fence_after();
-          tmem_ld32(tmem_base + COL_DQ + lane_off, r);
-          tmem_ld32(tmem_base + COL_DQ + 32 + lane_off, r + 32);
+          tmem_ld32(tmem_base + COL_ST + lane_off, r);
+          tmem_ld32(tmem_base + COL_ST + 32 + lane_off, r + 32);
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(dq_hi_drained);     // the next lower product may overwrite the buffer
-          if constexpr (DQ_DIRECT) {
-            if (staged) {
-#pragma unroll
-              for (int i = 0; i < 64; ++i)
-                if (i < q_live) atomicAdd(dq_row + 64 + i * dq_stride, __uint_as_float(r[i]) * p.scale);
-            }
-          } else if (staged) {
-            float* stage = reinterpret_cast<float*>(hi_tile) + lane;
+          if (lane == 0) {
+            mbar_arrive(dq_hi_drained);                // S^T of the step after next may overwrite the buffer
+            tma_store_wait_read<0>();                  // the tile of the step before has left the staging memory
+          }
+          __syncwarp();
+          if (staged) {
 #pragma unroll
             for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-              tma_reduce_add_3d(&tmap_dq, hi_tile, head * DQK + 128 + (quarter - 2) * 32, q0, batch);
+              tma_reduce_add_3d(&tmap_dq, tile, head * DQK + 128 + (quarter - 2) * 32, q0, batch);
               tma_store_commit();
             }
           }
         }
-        if constexpr (!DQ_DIRECT) {
-          if (lane == 0) {
-            tma_store_wait_read<0>();
-            mbar_arrive(&pt_free[b]);                 // 4 arrivals: the softmax groups may write P^T / dS^T again
-          }
+        ok = mbar_wait_bounded(dq_lo_full, it & 1, abort_flag, p.status, kTimeoutTmemFull, blockIdx.x);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tmem_base + COL_DQ + lane_off, r);
+        tmem_ld32(tmem_base + COL_DQ + 32 + lane_off, r + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(dq_lo_drained);                  // the lower product of the next step may overwrite the buffer
+          tma_store_wait_read<0>();
+        }
+        __syncwarp();
+        if (staged) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
+          fence_proxy_async();
           __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_3d(&tmap_dq, tile, head * DQK + quarter * 32, q0, batch);
+            tma_store_commit();
+          }
         }
       }
       if (lane == 0) tma_store_wait<0>();
@@ -675,10 +655,6 @@ extern "C" void hpb_mla_attn_set_head_group(int pairs) { g_mla_bwd_head_group = 
 static long long* g_mla_bwd_prof = nullptr;
 // Device buffer of 16 int64 that receives the phase timings of one softmax thread (nullptr = off).
 extern "C" void hpb_mla_attn_set_prof(long long* buf) { g_mla_bwd_prof = buf; }
-// dQ accumulation: 1 = red.global from registers (measured 2x slower: the 384 reductions per step back up the
-// load/store unit), 0 = staged tiles and TMA reduces (default).
-static int g_mla_bwd_dq_direct = 0;
-extern "C" void hpb_mla_attn_set_dq_direct(int on) { g_mla_bwd_dq_direct = on; }
 static int g_mla_bwd_probe = 0;
 extern "C" void hpb_mla_attn_set_probe(int mask) { g_mla_bwd_probe = mask; }
 
@@ -704,7 +680,7 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
        reinterpret_cast<uintptr_t>(dkr_heads)) & 15)
     return -2;
   cudaFree(nullptr);
-  CUtensorMap tq, tdo, tkv, tkr, tdq, tdq32;
+  CUtensorMap tq, tdo, tkv, tkr, tdq;
   int r = make_tmap_bsd(&tq, q, B, S, H * mla::DQK, q_batch_stride, q_row_stride, mla::BQ);
   if (r) return r;
   r = make_tmap_bsd(&tdo, dO, B, S, H * mla::DV, do_batch_stride, do_row_stride, mla::BQ);
@@ -725,21 +701,13 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return static_cast<int>(cr);
-    box[1] = 32;      // the lower dQ tile is reduced in two rounds of 32 query rows
-    cr = enc(&tdq32, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (cr != CUDA_SUCCESS) return static_cast<int>(cr);
   }
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mla::mla_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(mla::mla_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          mla::BWD_SMEM);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(mla::mla_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               mla::BWD_SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
@@ -768,11 +736,7 @@ extern "C" int hpb_mla_attn_bwd(const void* q, long long q_batch_stride, long lo
   p.dKR = reinterpret_cast<__nv_bfloat16*>(dkr_heads);
   p.status = status;
   dim3 grid(((S + mla::BN - 1) / mla::BN) * H * B);
-  p.dQ = dq_acc;
-  if (g_mla_bwd_dq_direct)
-    mla::mla_bwd_kernel<true><<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, tdq32, p);
-  else
-    mla::mla_bwd_kernel<false><<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, tdq32, p);
+  mla::mla_bwd_kernel<<<grid, mla::BWD_THREADS, mla::BWD_SMEM, stream>>>(tq, tdo, tkv, tkr, tdq, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   {

@@ -401,7 +401,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 //
 //   S^T  = K Q^T            [kv 128 x q 64]   tensor memory (double buffered)
 //   dP^T = V dO^T           [kv 128 x q 64]   tensor memory (double buffered)
-//   P^T  = exp2(S^T * c - lse),  dS^T = P^T o (dP^T - D)      -> bf16, shared memory
+//   P^T  = exp2(S^T * c - lse)                                 -> bf16 pairs, back into tensor memory over
+//                                                                 the dP^T columns the thread has read
+//   dS^T = P^T o (dP^T - D)                                    -> bf16, shared memory
 //   dV  += P^T dO           [kv 128 x d 128]  tensor memory, accumulated over the whole walk
 //   dK  += dS^T Q           [kv 128 x d 128]  tensor memory, accumulated over the whole walk
 //   dQ^T = K^T dS^T         [d 128 x q 64]    tensor memory (in the S^T buffer just consumed),
@@ -412,13 +414,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 //   warp 1       MMA issuer
 //   warps 2-9    softmax / dS: two groups of four warps, each owning 32 of the 64 query columns;
 //                they also write dV / dK at the end
-//   warps 10-13  dQ read-out and TMA reduce
+//   warps 10-13  dQ read-out: fp32 tiles staged in a buffer of their own and added to global
+//                memory by TMA reduces, so the read-out never holds back the softmax warps
 constexpr int BQ = 64;                        // query rows per step
 constexpr int QDO_STAGES = 3;
 constexpr int QTILE_BYTES = BQ * HD * 2;      // 16 KB
 constexpr int PT_BYTES = BN * BQ * 2;         // 16 KB
 constexpr int BWD_THREADS = 448;
-constexpr int BWD_SMEM = 2 * TILE_BYTES + QDO_STAGES * 2 * QTILE_BYTES + 2 * 2 * PT_BYTES + 2 * 2 * BQ * 4 + 1024 + 256;
+constexpr int STAGE_TILE = BQ * 32 * 4;       // 8 KB: [64 query rows x 32 head elements] fp32
+constexpr int BWD_SMEM = 2 * TILE_BYTES + QDO_STAGES * 2 * QTILE_BYTES + 2 * PT_BYTES + 4 * STAGE_TILE +
+                         2 * 2 * BQ * 4 + 1024 + 256;
 
 struct BwdParams {
   int B, S, Hq, Hkv;
@@ -444,14 +449,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sK = smem;
   uint8_t* sV = smem + TILE_BYTES;
   uint8_t* sQdO = sV + TILE_BYTES;                            // per stage: Q (16 KB) | dO (16 KB)
-  uint8_t* sPT = sQdO + QDO_STAGES * 2 * QTILE_BYTES;         // per buffer: P^T (16 KB) | dS^T (16 KB)
-  float* sStat = reinterpret_cast<float*>(sPT + 2 * 2 * PT_BYTES);   // [2][2][64]: lse*log2e, delta
+  uint8_t* sDS = sQdO + QDO_STAGES * 2 * QTILE_BYTES;         // dS^T, two buffers of 16 KB
+  uint8_t* sStage = sDS + 2 * PT_BYTES;                       // dQ staging: one 8 KB tile per dQ warp
+  float* sStat = reinterpret_cast<float*>(sStage + 4 * STAGE_TILE);  // [2][2][64]: lse*log2e, delta
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(sStat + 2 * 2 * BQ);
   uint64_t* qdo_full = kv_full + 1;              // [QDO_STAGES]
   uint64_t* qdo_empty = qdo_full + QDO_STAGES;   // [QDO_STAGES]
   uint64_t* st_full = qdo_empty + QDO_STAGES;    // [2]  S^T and dP^T of a step are complete
   uint64_t* ds_full = st_full + 2;               // [2]  P^T / dS^T written (4 warp arrivals)
-  uint64_t* pt_free = ds_full + 2;               // [2]  products reading P^T / dS^T retired
+  uint64_t* pt_free = ds_full + 2;               // [2]  products reading dS^T buffer b retired
   uint64_t* dq_full = pt_free + 2;               // [2]
   uint64_t* dq_drained = dq_full + 2;            // [2]  (4 warp arrivals)
   uint64_t* stat_full = dq_drained + 2;          // [2]  lse / delta of a step staged (4 warp arrivals)
@@ -494,7 +500,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int b = 0; b < 2; ++b) {
       mbar_init(&st_full[b], 1);
       mbar_init(&ds_full[b], 8);
-      mbar_init(&pt_free[b], 4);     // one arrival per dQ warp once its TMA reduce has read the buffer
+      mbar_init(&pt_free[b], 1);     // committed by the MMA issuer behind the last reader of dS^T
       mbar_init(&dq_full[b], 1);
       mbar_init(&dq_drained[b], 4);
       mbar_init(&stat_full[b], 4);
@@ -570,15 +576,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       constexpr uint32_t idesc_acc = make_idesc(1, 1, 0, 1, BN, HD);   // P^T (K-major) x dO (MN-major)
       constexpr uint32_t idesc_dq = make_idesc(1, 1, 1, 1, HD, BQ);    // K^T (MN-major) x dS^T (MN-major)
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), qdo_addr = smem_u32(sQdO),
-                     pt_addr = smem_u32(sPT);
+                     ds_addr = smem_u32(sDS);
       bool ok = true;
       const uint64_t k_desc = make_smem_desc_sw128(k_addr, 0, 1024);              // K as K-major A
       const uint64_t v_desc = make_smem_desc_sw128(v_addr, 0, 1024);              // V as K-major A
       const uint64_t kt_desc = make_smem_desc_sw128(k_addr, HALF_BYTES, 1024);    // K^T as MN-major A
       const uint64_t qk_desc = make_smem_desc_sw128(qdo_addr, 0, 1024);           // Q / dO as K-major B
       const uint64_t qm_desc = make_smem_desc_sw128(qdo_addr, QTILE_BYTES / 2, 1024);   // Q / dO as MN-major B
-      const uint64_t ptk_desc = make_smem_desc_sw128(pt_addr, 0, 1024);           // P^T / dS^T as K-major A
-      const uint64_t ptm_desc = make_smem_desc_sw128(pt_addr, PT_BYTES, 1024);    // dS^T as MN-major B
+      const uint64_t dsk_desc = make_smem_desc_sw128(ds_addr, 0, 1024);           // dS^T as K-major A
+      const uint64_t dsm_desc = make_smem_desc_sw128(ds_addr, PT_BYTES, 1024);    // dS^T as MN-major B
       // S^T(it) and dP^T(it) into buffer it & 1 (st_full follows the S^T product, issued last)
       auto issue_dpt = [&](int it) {
         const int b = it & 1;
@@ -626,9 +632,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         const uint64_t qa = desc_at(qm_desc, (it % QDO_STAGES) * 2 * QTILE_BYTES);
         const uint64_t doa = desc_at(qa, QTILE_BYTES);
-        const uint64_t pta = desc_at(ptk_desc, b * 2 * PT_BYTES);
-        const uint64_t dsa = desc_at(pta, PT_BYTES);
-        const uint64_t dsm = desc_at(ptm_desc, b * 2 * PT_BYTES + PT_BYTES);
+        const uint64_t dsa = desc_at(dsk_desc, b * PT_BYTES);
+        const uint64_t dsm = desc_at(dsm_desc, b * PT_BYTES);
         const uint32_t first = it ? 1u : 0u;
         // dQ^T = K^T dS^T  (contraction over the 128 key rows: 8 steps of 16) into the S^T buffer
 #pragma unroll
@@ -636,16 +641,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           umma_f16(tmem_base + COL_ST + b * BQ, desc_at(kt_desc, kk * 2048), desc_at(dsm, kk * 2048), idesc_dq,
                    kk ? 1u : 0u);
         umma_commit(&dq_full[b]);
-        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16)
-        umma_f16(tmem_base + COL_DV, pta, doa, idesc_acc, first);
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows: 4 steps of 16).  P^T lies
+        // in the dP^T buffer of the step: query rows 0..31 in columns 0..15, 32..63 in columns 32..47
 #pragma unroll
-        for (int kk = 1; kk < 4; ++kk)
-          umma_f16(tmem_base + COL_DV, desc_at(pta, kk * 32), desc_at(doa, kk * 2048), idesc_acc, 1u);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_DPT + b * BQ + (kk >> 1) * 32 + (kk & 1) * 8,
+                      desc_at(doa, kk * 2048), idesc_acc, kk ? 1u : first);
         umma_f16(tmem_base + COL_DK, dsa, qa, idesc_acc, first);
 #pragma unroll
         for (int kk = 1; kk < 4; ++kk)
           umma_f16(tmem_base + COL_DK, desc_at(dsa, kk * 32), desc_at(qa, kk * 2048), idesc_acc, 1u);
         umma_commit(&qdo_empty[it % QDO_STAGES]);
+        umma_commit(&pt_free[b]);      // every reader of dS^T of this step has been issued
         if (it + 2 < n_it) {
           ok = wait_qdo(it + 2);
           if (!ok) break;
@@ -690,9 +697,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
         float* stat = sStat + b * 2 * BQ;
-        // P^T / dS^T buffer b is free again (the dQ tile staged in it has been read); this also
-        // means that all eight softmax warps have finished step it - 2, so the statistics buffer
-        // b can be rewritten
+        // dS^T buffer b is free again (the products of step it - 2 that read it have retired); this
+        // also means that all eight softmax warps have finished step it - 2, so the statistics
+        // buffer b can be rewritten
         ok = mbar_wait_bounded(&pt_free[b], par ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, blockIdx.x);
         if (!ok) break;
         if (tid < 128) stat[tid] = tid < 64 ? stat_next * 1.4426950408889634f : stat_next;
@@ -708,8 +715,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int cmin = p.causal ? kv_row - q0 : 0;
         // warp-uniform: does any row of this warp hide any column of this step?
         const bool masked = (k0 + quarter * 32 + 32 > p.S) || (p.causal && k0 + quarter * 32 + 31 - q0 > 0);
-        uint8_t* pt_row = sPT + b * 2 * PT_BYTES + row * 128;
-        uint8_t* ds_row = pt_row + PT_BYTES;
+        uint8_t* ds_row = sDS + b * PT_BYTES + row * 128;
         {
           const int c = wg;                    // this group's 32 query columns
           uint32_t rs[32], rp[32];
@@ -737,14 +743,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             pk[i2] = *reinterpret_cast<const uint32_t*>(&eb);
             dk[i2] = *reinterpret_cast<const uint32_t*>(&db);
           }
+          // P^T over the first 16 of the 32 dP^T columns just read (this thread's own)
+          tmem_st_32x32b_x16(tmem_base + COL_DPT + b * BQ + c * 32 + lane_off, pk);
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             const int chunk = c * 4 + q4;
-            *reinterpret_cast<uint4*>(pt_row + ((chunk ^ sw) << 4)) =
-                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
             *reinterpret_cast<uint4*>(ds_row + ((chunk ^ sw) << 4)) =
                 make_uint4(dk[4 * q4], dk[4 * q4 + 1], dk[4 * q4 + 2], dk[4 * q4 + 3]);
           }
+          tmem_st_wait();
         }
         fence_proxy_async();
         tc_fence_before();
@@ -753,9 +760,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
     } else {
       // ------------------------------------------------------ dQ reduction --
-      // dQ^T (lane = head element, column = query row) is transposed through the P^T / dS^T
-      // buffer of the same step -- free once the dQ product has retired -- as a dense fp32
-      // [64 query rows x 128] tile, which one TMA reduce adds to the fp32 dQ in global memory.
+      // dQ^T (lane = head element, column = query row) is transposed through this warp's staging
+      // tile as a dense fp32 [64 query rows x 32 head elements] tile of 8 KB, which one TMA
+      // reduce adds to the fp32 dQ in global memory.
+      uint8_t* tile = sStage + quarter * STAGE_TILE;
+      float* stage = reinterpret_cast<float*>(tile) + lane;
       for (int it = 0; it < n_it && ok; ++it) {
         const int b = it & 1;
         const uint32_t par = (it >> 1) & 1;
@@ -764,31 +773,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
         const int head = kv_head * group + it / per_head;
         const int q0 = (i_start + it % per_head) * BQ;
-        // every warp stages and reduces its own 32 head elements: a dense [64 query rows x 32]
-        // fp32 tile of 8 KB, added to global memory by one TMA reduce per warp
-        float* stage = reinterpret_cast<float*>(sPT + b * 2 * PT_BYTES + quarter * (BQ * 32 * 4)) + lane;
         uint32_t r[64];
         tmem_ld32(tmem_base + COL_ST + b * BQ + lane_off, r);
         tmem_ld32(tmem_base + COL_ST + b * BQ + 32 + lane_off, r + 32);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&dq_drained[b]);   // the S^T buffer may be overwritten
-        // the staging tile lies over P^T / dS^T of this step: the dV / dK products, issued after
-        // the dQ^T product, must have retired as well (their commit frees the Q / dO stage)
-        ok = mbar_wait_bounded(&qdo_empty[it % QDO_STAGES], (it / QDO_STAGES) & 1, abort_flag, p.status,
-                               kTimeoutEmptyBarrier, blockIdx.x);
-        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive(&dq_drained[b]);                 // the S^T buffer may be overwritten
+          tma_store_wait_read<0>();                    // the tile of the step before has left the staging memory
+        }
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < 64; ++i) stage[i * 32] = __uint_as_float(r[i]) * p.scale;
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          tma_reduce_add_3d(&tmap_dq, sPT + b * 2 * PT_BYTES + quarter * (BQ * 32 * 4), head * HD + quarter * 32, q0,
-                            batch);
+          tma_reduce_add_3d(&tmap_dq, tile, head * HD + quarter * 32, q0, batch);
           tma_store_commit();
-          tma_store_wait_read<0>();
-          mbar_arrive(&pt_free[b]);                   // 4 arrivals: the softmax groups may write P^T / dS^T again
         }
       }
       if (lane == 0) tma_store_wait<0>();

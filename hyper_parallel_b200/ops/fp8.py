@@ -127,20 +127,21 @@ def gemm_fp8_grouped(aq, sa, bq, sb, block_group, num_experts: int, out=None) ->
 
 
 class _Fp8Linear(torch.autograd.Function):
+    """2-D in, 2-D out: nothing it returns is a view created inside the Function, so callers may
+    modify (part of) the result in place."""
+
     @staticmethod
-    def forward(ctx, x, w):
-        x2 = x.reshape(-1, x.shape[-1])
+    def forward(ctx, x2, w):
         ctx.save_for_backward(x2, w)
-        ctx.x_shape = x.shape
         aq, sa = quantize_act_1x128(x2)
         bq, sb = quantize_weight_128x128(w)
-        return gemm_fp8(aq, sa, bq, sb).view(*x.shape[:-1], w.shape[0])
+        return gemm_fp8(aq, sa, bq, sb)
 
     @staticmethod
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        dx = Fn.gemm(dy2, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dy2 = dy.contiguous()
+        dx = Fn.gemm(dy2, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw = Fn.gemm(dy2, x2, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
         return dx, dw
 
@@ -149,4 +150,5 @@ def fp8_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``x @ w.T`` with an fp8 block-scaled forward GEMM (K must be a multiple of 128)."""
     if x.shape[-1] % 128:
         return Fn.linear(x, w)
-    return _Fp8Linear.apply(x, w)
+    y = _Fp8Linear.apply(x.reshape(-1, x.shape[-1]), w)
+    return y if x.dim() == 2 else y.view(*x.shape[:-1], w.shape[0])
