@@ -210,9 +210,9 @@ def run_ours(args):
         # the same two steps on NCCL collectives + separate kernels: step 0 checks the gathered weights,
         # step 1 the reduced gradients and the sharded optimizer update
         import gc
-        from hyper_parallel_b200.core.hsdp.hsdp_scheduler import reset_hsdp_registry
-        del model, opt
-        reset_hsdp_registry()
+        from hyper_parallel_b200.core.hsdp.hsdp_scheduler import teardown_hsdp
+        teardown_hsdp(model)
+        del model, opt, loss
         gc.collect()
         torch.cuda.empty_cache()
         prev = os.environ.get("HPB_FUSED_COMM")
@@ -238,7 +238,7 @@ def run_ours(args):
     MetricsWriter(args.metrics_jsonl).write(args.steps, tokens_per_s=value, ms_per_step=ms_per_step,
                                             e2e_ms_per_step=e2e_ms / args.steps, mfu=mfu, loss=last_loss,
                                             n_gpus=world, fused_comm=os.environ.get("HPB_FUSED_COMM", "1"),
-                                            fused_ag=os.environ.get("HPB_FUSED_AG", "1"),
+                                            fused_ag=os.environ.get("HPB_FUSED_AG", "0"),
                                             ride=os.environ.get("HPB_RIDE", "1"), nvls=os.environ.get("HPB_NVLS", "1"))
     if rank == 0:
         print(json.dumps({

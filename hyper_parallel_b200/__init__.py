@@ -14,7 +14,7 @@ from .core.layout import Layout
 from .core.dtensor import (DTensor, SkipDTensorDispatch, distribute_tensor, empty, full, ones, zeros)
 from .core.shard import (ShardingPlan, custom_shard, parallelize_value_and_grad, shard, shard_module)
 from .core.shard.ops.parallel_ops import DistributedOp
-from .core.hsdp import HSDPCell, hsdp, hsdp_sync_stream
+from .core.hsdp import HSDPCell, hsdp, hsdp_sync_stream, teardown_hsdp
 from .core.parameter_init import init_parameters
 from .core.pipeline_parallel import (BatchDimSpec, MetaStep, MetaStepType, PipelineStage, Schedule1F1B,
                                      ScheduleGPipe, ScheduleInterleaved1F1B, SharedParameterInfo,
@@ -25,7 +25,7 @@ from .core import function_override as _function_override
 _function_override.install()
 
 __all__ = [
-    "get_platform", "hsdp", "hsdp_sync_stream", "HSDPCell", "Layout", "DTensor", "DeviceMesh",
+    "get_platform", "hsdp", "hsdp_sync_stream", "teardown_hsdp", "HSDPCell", "Layout", "DTensor", "DeviceMesh",
     "init_device_mesh", "init_parameters", "shard_module", "shard", "custom_shard",
     "parallelize_value_and_grad", "SkipDTensorDispatch", "ShardingPlan", "DistributedOp",
     "Shard", "Replicate", "Partial", "Placement", "distribute_tensor", "ones", "zeros", "empty", "full",

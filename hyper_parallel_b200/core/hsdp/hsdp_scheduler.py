@@ -244,3 +244,25 @@ def reset_hsdp_registry() -> None:
     """Forget every scheduler (tests build many models in one process)."""
     _ALL_SCHEDULERS.clear()
     _PENDING.clear()
+
+
+def teardown_hsdp(root) -> None:
+    """Give back what ``hsdp()`` allocated outside the caching allocator for the modules below
+    ``root``: the symmetric-memory regions (flat shards and gradient buffers, mapped by the peers)
+    are closed, the staging buffers and the queue of pending weight gathers dropped, the registry
+    forgotten.  Collective -- every rank calls it, with no kernel of the model in flight -- and the
+    model must not be used afterwards."""
+    import torch
+    from ...parallel import fused_hsdp
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    for mod in root.modules():
+        sch = mod.__dict__.get("hsdp_scheduler")
+        if sch is None:
+            continue
+        for buf in list(getattr(sch.hsdp_state, "symm_buffers", [])):
+            buf.close()
+        sch.hsdp_state.symm_buffers = []
+    fused_hsdp._RIDE_QUEUE.clear()
+    fused_hsdp._POOL.free.clear()
+    reset_hsdp_registry()

@@ -73,8 +73,13 @@ def symm_path_enabled() -> bool:
 
 
 def fused_gather_enabled() -> bool:
-    """``HPB_FUSED_AG=0`` gathers every weight with the stand-alone copy kernel instead."""
-    return os.environ.get("HPB_FUSED_AG", "1") != "0"
+    """``HPB_FUSED_AG=1`` gathers GEMM-only weights inside the GEMMs (own gather in the consumer,
+    riding gathers on the GEMMs before it).  Default off: end to end the stand-alone peer-pull copy
+    kernel on its side stream was faster on the Llama-3-8B step (2 GPUs: 402.8 against 414.9 ms,
+    4 GPUs: 424.7 against 437.6 ms) -- the copy hides completely behind the compute of the layer
+    before, while a GEMM that carries a gather gives four warps per CTA and part of its L2 / HBM
+    bandwidth to it.  Kernel against kernel the fused GEMM beats NCCL all-gather + GEMM."""
+    return os.environ.get("HPB_FUSED_AG", "0") != "0"
 
 
 def group_ok(params) -> bool:
@@ -301,6 +306,7 @@ class SymmParamBuffer:
         self._fused_step_done = False
         for i, p in enumerate(params):
             p._symm = (self, i)
+        self.closed = False
         _LIVE.add(self)
         _install_step_hook()
         from ..ops import functional as _fn
@@ -562,10 +568,25 @@ class SymmParamBuffer:
             self.reduce_event = None
 
     # --------------------------------------------------------------- versions --
+    def close(self) -> None:
+        """Give the symmetric region back (collective over the shard group; see
+        ``SymmetricMemory.close``).  The buffer leaves the set that the optimizer post-step hook
+        walks, so no later optimizer step -- of this or of any other model -- signals through pads
+        that are no longer mapped."""
+        if self.closed:
+            return
+        self.closed = True
+        _LIVE.discard(self)
+        self.release_staging()
+        self.tickets = [None] * len(self.params)
+        self.symm.close()
+
     def after_optimizer_step(self) -> None:
         """Runs after every optimizer step.  If the fused kernel rewrote the shards in this step it
         has published the new version itself; otherwise (an optimizer that writes the shards with
         its own kernels) publish it now, ordered after those kernels on the current stream."""
+        if self.closed:
+            return
         if self._fused_step_done:
             self._fused_step_done = False
             return
@@ -574,6 +595,8 @@ class SymmParamBuffer:
     def params_written(self) -> None:
         """The shards of this buffer were rewritten on the current stream (optimizer step, state-dict
         load): publish a new version.  Every rank must call it the same number of times."""
+        if self.closed:
+            raise RuntimeError("this HSDP buffer was closed (teardown_hsdp); its model cannot be stepped any more")
         self.version += 1
         if self.n > 1:
             self.symm.signal(SLOT_SHARD_VERSION, self.version)

@@ -371,6 +371,8 @@ class SymmetricMemory:
 
     def signal(self, slot: int, value: int) -> None:
         """Publish ``value`` on ``slot`` of every peer's pad (current stream, no wait)."""
+        if not getattr(self, "_base", 0):
+            raise RuntimeError("symmetric memory region is closed")
         native.check(self.lib.hpb_symm_signal(self.pad_ptrs, self.rank, self.world, slot, value,
                                               native.stream(self.device)), "hpb_symm_signal")
 

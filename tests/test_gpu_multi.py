@@ -78,6 +78,12 @@ def _worker(rank, world, port, tmp):
     _train(rank, world, True, 3, os.path.join(tmp, "fused.pt"))
     reset_hsdp_registry()
     _train(rank, world, True, 3, os.path.join(tmp, "fused2.pt"))      # second identical run: determinism
+    reset_hsdp_registry()
+    os.environ["HPB_FUSED_AG"] = "1"           # weight gathers inside the consumer GEMMs (and riding ahead)
+    try:
+        _train(rank, world, True, 3, os.path.join(tmp, "fused_ag.pt"))
+    finally:
+        os.environ.pop("HPB_FUSED_AG", None)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -99,6 +105,12 @@ def test_symmetric_hsdp_matches_nccl_path(tmp_path, world):
     # the fused path run twice from the same seeds gives the same bits (no race shows up as noise)
     c = torch.load(tmp_path / "fused2.pt")
     assert b["losses"] == c["losses"] and torch.equal(b["w"], c["w"])
+    # gathering the weights inside the GEMMs moves the same bytes; the input-gradient product then
+    # walks its K blocks in arrival order, so the sums agree to rounding, not to the bit
+    d = torch.load(tmp_path / "fused_ag.pt")
+    for x, y in zip(b["losses"], d["losses"]):
+        assert abs(x - y) < 2e-3 * abs(x), (b["losses"], d["losses"])
+    assert (b["w"] - d["w"]).norm() / b["w"].norm() < 2e-3
 
 
 def test_peer_wait_times_out_with_status_not_a_hang():
