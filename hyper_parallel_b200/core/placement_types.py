@@ -36,6 +36,10 @@ class Shard(Placement):
     def __setattr__(self, key, value):
         raise AttributeError("Shard is immutable")
 
+    def __reduce__(self):
+        # immutable slots: pickling (placements travel between pipeline stages) goes through __init__
+        return (Shard, (self.dim,))
+
     def is_shard(self, dim=None) -> bool:
         return dim is None or dim == self.dim
 
@@ -83,6 +87,9 @@ class Partial(Placement):
 
     def __setattr__(self, key, value):
         raise AttributeError("Partial is immutable")
+
+    def __reduce__(self):
+        return (Partial, (self.reduce_op,))
 
     def is_partial(self, reduce_op=None) -> bool:
         return reduce_op is None or reduce_op == self.reduce_op
