@@ -368,12 +368,18 @@ mla_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         umma_commit(dq_lo_full);
         umma_commit(&pt_free[b]);     // every reader of dS^T of this step has been issued
         tick(3);
-        if (it + 2 < n_it) {
+        // The upper tile must have left the S^T buffer before anything else is written there: S^T of
+        // step it + 2, or -- in the last two steps, where no score tile follows -- the upper tile of
+        // the next step (this wait also keeps the phase of dq_hi_full at most one ahead of its readers)
+        if (it + 1 < n_it) {
           ok = wait_on(dq_hi_drained, it & 1, kTimeoutTmemEmpty);
-          if (ok) ok = q_ready(it + 2);
           if (!ok) break;
-          tc_fence_after();
-          issue_st(it + 2);
+          if (it + 2 < n_it) {
+            ok = q_ready(it + 2);
+            if (!ok) break;
+            tc_fence_after();
+            issue_st(it + 2);
+          }
         }
         tick(4);
       }
