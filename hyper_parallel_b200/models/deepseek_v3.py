@@ -58,6 +58,10 @@ class DeepSeekV3Config:
     # the attention / dense / shared-expert projections and of the routed experts; master weights,
     # the backward GEMMs, the router and the lm head stay bf16 / fp32
     fp8: bool = False
+    # receive capacity of the expert-parallel dispatch, in multiples of the balanced load; 0 = as large
+    # as any routing can need (the expert-parallel size), capped at 4: group-limited routing of
+    # correlated tokens can legitimately send most pairs to the ranks of a few groups
+    ep_capacity: float = 0.0
 
     @staticmethod
     def tiny() -> "DeepSeekV3Config":
@@ -203,8 +207,9 @@ class MoE(nn.Module):
         from ..parallel import ep_fused
         if ep_fused.usable(x, topk_idx, self.w_gate_up, c.n_routed_experts, self.ep_group):
             # dispatch / combine kernels over NVLink peer memory around the grouped expert GEMMs
+            cap = c.ep_capacity if c.ep_capacity > 0 else float(min(max(self.ep_size, 2), 4))
             y = ep_fused.fused_expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down,
-                                                   c.n_routed_experts, self.ep_group, fp8=c.fp8)
+                                                   c.n_routed_experts, self.ep_group, capacity=cap, fp8=c.fp8)
         else:
             y = moe_ops.expert_parallel_ffn(x, topk_idx, topk_w, self.w_gate_up, self.w_down, c.n_routed_experts,
                                             self.ep_group)

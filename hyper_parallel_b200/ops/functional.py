@@ -348,7 +348,9 @@ def rope_(x: torch.Tensor, seq_len: int, theta: float, positions: Optional[torch
     if not native.use_native(x):
         x.copy_(_rope_ref(x, seq_len, theta, positions, inverse))
         return x
-    assert x.dtype == torch.bfloat16 and x.stride(2) == 1
+    if x.dtype != torch.bfloat16 or x.stride(2) != 1:
+        x.copy_(_rope_ref(x, seq_len, theta, positions, inverse))     # other dtypes / layouts: reference math
+        return x
     if x.stride(1) != D:
         if not (D % 16 == 0 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0
                 and positions is None):
@@ -386,7 +388,7 @@ class _RoPE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        dx = dy.clone()
+        dx = dy.clone(memory_format=torch.contiguous_format)
         rope_(dx, ctx.seq_len, ctx.theta, inverse=True)
         return dx, None, None
 

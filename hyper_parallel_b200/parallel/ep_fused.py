@@ -13,7 +13,11 @@ receive matrix of a dispatch is an ordinary tensor sized for ``capacity`` x the 
 GEMM kernel through a device-side block table, so no size ever returns to the host.  A router so
 imbalanced that one rank receives more than ``capacity`` x the balanced load is an ERROR: the
 dispatch kernel records status code 6, leaves empty tables (the expert GEMMs then do nothing) and
-``native.check_status()`` raises at the end of the step; raise ``capacity`` in that case.
+``native.check_status()`` raises at the end of the step; raise ``capacity`` in that case.  The
+DeepSeek-V3 model passes the expert-parallel size (capped at 4) unless told otherwise: with
+group-limited routing, correlated tokens all prefer the same few groups and the ranks that host
+them receive far more than twice the balanced load -- seen after a handful of steps on random
+tokens (2.4 x at EP = 4), which is why 2.0 is only the default of the bare function.
 """
 from __future__ import annotations
 
