@@ -290,6 +290,14 @@ def run_pp(args, rank, world, dev):
         return torch.stack([o.detach() for o in out]).sum() if out is not None else torch.zeros((), device=dev)
 
     ms, loss, clocks, e2e = timed_steps(step, args, dev, host)
+    trace = sched.trace_report()        # HPB_PP_TRACE=1: mean device time and count per kind of step, per rank
+    if trace:
+        print(f"[pp trace] rank {rank} stage {stage_rank} {args.schedule}: " +
+              "  ".join(f"{k} {v[0]:.2f} ms x{v[1]}" for k, v in sorted(trace.items())), flush=True)
+    tl = sched.trace_timeline()         # HPB_PP_TRACE=2: the compute steps of the last step on this rank's stream
+    if tl:
+        print(f"[pp timeline] rank {rank} {args.schedule}: " +
+              " ".join(f"{lab}{m}:{a:.0f}-{b:.0f}" for lab, m, a, b in tl), flush=True)
     lt = loss.clone()
     dist.all_reduce(lt, op=dist.ReduceOp.MAX)
     tokens = B * args.micro * S

@@ -21,6 +21,7 @@ unmatched pairs or a deadlock.
 from __future__ import annotations
 
 import logging
+import os
 from enum import Enum, auto
 from typing import Dict, List, Optional, Tuple
 
@@ -229,6 +230,27 @@ class PipelineScheduleRuntime:
         self.real_stage_index = s0.real_stage_index
         self.stage_by_index = {st.stage_index: st for st in self.stages}
         self.exec_order: Dict[int, List[MetaStep]] = {}
+        # Receives are posted ahead of the compute steps, so an NCCL receive kernel sits on a few SMs
+        # and spins until its peer sends -- for most of a backward step in 1F1B.  The persistent GEMMs
+        # stride their tiles over one CTA per SM and cannot share an SM with it: the CTAs meant for
+        # those SMs start when others finish and the GEMM takes far longer (measured on the last
+        # stage of PP=2: backward 88 ms with a receive pending, 73 ms without).  Leaving 16 SMs out of
+        # the persistent grids (8 were not enough) removes that and costs next to nothing under the
+        # power cap; HPB_PP_RESERVE_SMS overrides the number (0 = off).
+        if overlap_p2p and torch.cuda.is_available():
+            from ...ops import native as _native
+            want = int(os.environ.get("HPB_PP_RESERVE_SMS", "16"))
+            if want > _native._sm_reserve:
+                _native.reserve_sms(want)
+        # HPB_PP_TRACE=1: CUDA-event timers on the compute stream around every compute step, split
+        # into the wait for its received operand and the compute itself (``trace_report()``)
+        self.tracer = None
+        self.timeline = None              # HPB_PP_TRACE=2: (label, micro, start event, end event) of the last run
+        if os.environ.get("HPB_PP_TRACE", "0") == "1":
+            from ...utils.tracing import CudaTimer
+            self.tracer = CudaTimer()
+        elif os.environ.get("HPB_PP_TRACE", "0") == "2" and torch.cuda.is_available():
+            self.timeline = []
         self.build_exec_order()
 
     # subclasses fill self.exec_order = {real_stage: [MetaStep]}
@@ -244,6 +266,22 @@ class PipelineScheduleRuntime:
             ([()] * self.micro_batch_num, [{}] * self.micro_batch_num)
         return self.run_microbatches(micro_args, micro_kwargs)
 
+    def trace_report(self) -> Dict[str, tuple]:
+        """``{key: (mean ms, count)}`` of the traced steps so far (synchronises); empty without HPB_PP_TRACE=1."""
+        if self.tracer is None:
+            return {}
+        means = self.tracer.resolve()
+        return {k: (means[k], self.tracer.counts[k]) for k in means}
+
+    def trace_timeline(self) -> List[tuple]:
+        """``[(label, micro, start ms, end ms)]`` of the compute steps of the last run on this rank's
+        compute stream, relative to its first step (synchronises); empty without HPB_PP_TRACE=2."""
+        if not self.timeline:
+            return []
+        torch.cuda.synchronize()
+        t0 = self.timeline[0][2]
+        return [(lab, m, t0.elapsed_time(s), t0.elapsed_time(e)) for lab, m, s, e in self.timeline if e is not None]
+
     def run_microbatches(self, micro_args, micro_kwargs):
         prog = self.exec_order[self.real_stage_index]
         T = MetaStepType
@@ -254,6 +292,22 @@ class PipelineScheduleRuntime:
         for st in self.stages:
             st.fwd_cache.clear()
             st.input_grads.clear()
+        if self.timeline is not None:
+            self.timeline = []
+
+        def mark(label, micro):
+            if self.timeline is None:
+                return None
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.timeline.append([label, micro, ev, None])
+            return self.timeline[-1]
+
+        def done(rec):
+            if rec is not None:
+                rec[3] = torch.cuda.Event(enable_timing=True)
+                rec[3].record()
+
         for step in prog:
             stage = self.stage_by_index[step.stage_index]
             m = step.micro_index
@@ -266,8 +320,16 @@ class PipelineScheduleRuntime:
                 if stage.is_first:
                     a, k = micro_args[m], micro_kwargs[m]
                 else:
+                    tok = self.tracer.start("fwd_recv_wait") if self.tracer else None
                     a, k = stage.finish_forward_recv(recv_f.pop((step.stage_index, m))), {}
+                    if tok:
+                        self.tracer.stop(tok)
+                tok = self.tracer.start("fwd") if self.tracer else None
+                rec = mark("F", m)
                 out = stage.forward_one_chunk(m, a, k)
+                done(rec)
+                if tok:
+                    self.tracer.stop(tok)
                 if stage.is_last:
                     losses[m] = out
             elif step.type == T.FWD_SEND:
@@ -282,12 +344,20 @@ class PipelineScheduleRuntime:
             elif step.type == T.BWD:
                 grads = None
                 if not stage.is_last:
+                    tok = self.tracer.start("bwd_recv_wait") if self.tracer else None
                     p = recv_b.pop((step.stage_index, m))
                     p.wait()
+                    if tok:
+                        self.tracer.stop(tok)
                     grads = [stage._rebuild(b, meta) for b, meta in zip(p.buffers, p.metas)]
                 n = bwd_seen.get(step.stage_index, 0) + 1
                 bwd_seen[step.stage_index] = n
+                tok = self.tracer.start("bwd") if self.tracer else None
+                rec = mark("B", m)
                 stage.backward_one_chunk(m, grads, last_micro=(n == self.micro_batch_num))
+                done(rec)
+                if tok:
+                    self.tracer.stop(tok)
             elif step.type == T.BWD_SEND:
                 stage.send_backward(m)
                 if not self.overlap_p2p:

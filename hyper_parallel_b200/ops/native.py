@@ -103,7 +103,22 @@ def stream(device=None):
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_sm_reserve = 0
+
+
+def reserve_sms(n: int) -> None:
+    """Leave ``n`` SMs (an even number: the GEMMs run CTA pairs) out of the grids of the persistent
+    kernels.  A persistent kernel strides its tiles over ``gridDim`` CTAs, one per SM; when another
+    kernel holds an SM for a long time -- an NCCL receive posted ahead that spins until its peer
+    sends, inside a pipeline stage -- the CTA meant for that SM starts only when another CTA has
+    finished, and the kernel takes up to twice as long.  Reserving the SMs that such kernels take
+    costs n / 148 of the peak and removes the tail.  ``HPB_RESERVE_SMS`` sets the initial value."""
+    global _sm_reserve
+    _sm_reserve = max(0, int(n)) // 2 * 2
+
+
 def sm_count(device) -> int:
+    """SMs that a persistent kernel may fill on ``device`` (all of them minus ``reserve_sms``)."""
     idx = torch.device(device).index
     if idx is None:
         idx = torch.cuda.current_device()
@@ -111,7 +126,10 @@ def sm_count(device) -> int:
     if n is None:
         n = torch.cuda.get_device_properties(idx).multi_processor_count
         _sm_count[idx] = n
-    return n
+    return max(n - _sm_reserve, 2)
+
+
+reserve_sms(int(os.environ.get("HPB_RESERVE_SMS", "0")))
 
 
 def status_word(device) -> torch.Tensor:
