@@ -200,7 +200,8 @@ def all_reduce_(t: torch.Tensor, op: str, group, async_op: bool = False):
     n = group_size(group)
     if n == 1:
         return None
-    if op == "all":
+    if op == "all" or t.dtype == torch.bool:
+        # logical reductions go through integers: all = MIN, any = MAX over {0, 1}
         buf = t.to(torch.int32)
         dist.all_reduce(buf, _reduce_op(op), group=group)
         t.copy_(buf.to(t.dtype))

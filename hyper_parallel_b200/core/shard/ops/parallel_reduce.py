@@ -2,7 +2,8 @@
 
 As in hyper_parallel/core/shard/ops/parallel_reduce.py:31-311 of the reference: a
 reduced dim that is sharded turns into a pending reduction (``Partial``) on its
-mesh axes (``sum``, ``avg`` for mean, ``prod``, ``all``, ``max``, ``min``);
+mesh axes (``sum``, ``avg`` for mean, ``prod``, ``all``, ``max``, ``min``; ``any`` is a ``max`` over
+booleans);
 ``max/min`` with a ``dim`` return ``(values, indices)`` and need that dim unsharded,
 as do ``argmax/argmin``.
 """
@@ -12,7 +13,7 @@ from ._common import make, norm_dims, require_unsharded
 from .parallel_ops import DistributedOp
 
 _PARTIAL_OF = {"sum": "sum", "mean": "avg", "prod": "prod", "all": "all", "max": "max", "min": "min",
-               "amax": "max", "amin": "min", "any": None, "nansum": "sum"}
+               "amax": "max", "amin": "min", "any": "max", "nansum": "sum"}
 
 
 def _parse_dim_keepdim(extra_args, ndim):
