@@ -222,6 +222,42 @@ def main():
     else:
         out.append({"path": "hsdp_fused_rs_adamw[multimem.ld_reduce]", "n_gpus": n,
                     "unavailable": f"no multicast mapping (transport {symm.transport})"})
+    # ---- (4) expert-parallel dispatch / combine: DeepSeek-V3 shapes, uniform random routing ------------------
+    from hyper_parallel_b200.parallel.ep_fused import EPWorkspace
+    T, k, H = 4096, 8, 7168
+    E = min(256, 64 * n)                      # the kernels hold at most 64 local experts per rank
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, generator=g)
+    topk_idx = torch.stack([torch.randperm(E, device=dev, generator=g)[:k] for _ in range(64)]).repeat(T // 64, 1)
+    topk_idx = topk_idx[torch.randperm(T, device=dev, generator=g)].contiguous()
+    flat_e = topk_idx.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    sorted_token = (order // k).to(torch.int32)
+    counts = torch.bincount(flat_e, minlength=E).to(torch.int32)
+    sorted_pos = torch.empty(T * k, dtype=torch.int32, device=dev)
+    sorted_pos[order] = torch.arange(T * k, dtype=torch.int32, device=dev)
+    w = torch.rand(T, k, device=dev)
+    ws = EPWorkspace.get(dist.group.WORLD, T, k, H, E, 2.0)
+    ws.dispatch(x, sorted_token, counts)
+    ws.out.normal_()
+    rows_remote = T * k * (n - 1) / n
+    roof = max(rows_remote * H * 2 / (LINK_GBS * 1e9), (T * k * H * 2 * 2) / (hbm_gbs * 1e9)) * 1e3
+    send = torch.empty(T * k, H, device=dev, dtype=torch.bfloat16)
+    recv_nccl = torch.empty_like(send)
+
+    def a2a():
+        dist.all_to_all_single(recv_nccl, send)
+
+    t_a2a = timed(a2a)
+    t = timed(lambda: ws.dispatch(x, sorted_token, counts))
+    out.append({"path": "ep_dispatch", "n_gpus": n, "tokens": T, "top_k": k, "hidden": H, "experts": E, "fused_ms": t,
+                "nccl_all_to_all_ms": t_a2a, "roofline_ms": roof, "fraction_of_roofline": roof / t, "peaks": src,
+                "note": "fused = stage + peer pull into the padded expert layout + grouped-GEMM tables; NCCL = one "
+                        "all_to_all_single of the same rows (equal splits, no permutation, no tables)"})
+    t = timed(lambda: ws.combine(topk_idx, sorted_pos, w, save_rows=False))
+    out.append({"path": "ep_combine", "n_gpus": n, "tokens": T, "top_k": k, "hidden": H, "experts": E, "fused_ms": t,
+                "nccl_all_to_all_ms": t_a2a, "roofline_ms": roof, "fraction_of_roofline": roof / t, "peaks": src,
+                "note": "fused = peer pull of the k expert rows of every token + weighted sum"})
     native.check_status(dev)
     if rank == 0:
         for o in out:
