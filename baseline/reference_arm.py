@@ -222,7 +222,8 @@ def run_reference(args):
 
     def probe(mode, tok, steps=2):
         """Seconds per step of one mode over a few steps, or None (and the traceback on rank 0's
-        stderr and in gpurun_out/) when the reference raises in that mode."""
+        stderr and in the directory that ``HPB_LOG_DIR`` names, default ``bench_logs``) when the
+        reference raises in that mode."""
         import gc
         import traceback
         try:
@@ -239,8 +240,9 @@ def run_reference(args):
                 text = traceback.format_exc()
                 sys.stderr.write(f"[reference arm] mode comm_async={mode[0]} comm_fusion={mode[1]} failed:\n{text}")
                 try:
-                    os.makedirs(os.path.join(os.path.dirname(HERE), "gpurun_out"), exist_ok=True)
-                    with open(os.path.join(os.path.dirname(HERE), "gpurun_out",
+                    log_dir = os.path.join(os.path.dirname(HERE), os.environ.get("HPB_LOG_DIR", "bench_logs"))
+                    os.makedirs(log_dir, exist_ok=True)
+                    with open(os.path.join(log_dir,
                                            f"reference_mode_async{int(mode[0])}_fusion{int(mode[1])}_N{world}.txt"),
                               "w") as f:
                         f.write(text)
