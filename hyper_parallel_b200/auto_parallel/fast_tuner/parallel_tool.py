@@ -22,7 +22,7 @@ from .memory_model import (GIB, activation_memory, compute_weight_and_optimizer_
 from .pipeline_balance import LayerProfile, balance_pipeline
 from .profiling import (launch_profile, parse_layer_records, select_profile_candidates,
                         write_profile_config)
-from .pp_simulator import compute_order, render_text, simulate
+from .pp_simulator import compute_order, render_svg, render_text, simulate
 from .space import (Config, build_initial_spaces, dp_of, ep_of, expert_filter_configs, mbs_of, op_of, pp_of,
                     sp_of, tp_of, vp_of)
 
@@ -140,6 +140,7 @@ def _recheck(spec: ModelSpec, c: Config, e: dict, lp: LayerProfile, cfg: TunerCo
     name = f"sim_dp{e['dp']}_tp{e['tp']}_pp{pp}_vp{vp}_mbs{e['mbs']}.txt"
     with open(os.path.join(out_dir, name), "w") as f:
         f.write(render_text(res) + "\n")
+    render_svg(res, os.path.join(out_dir, name[:-4] + ".svg"))
     return {"sim_bubble": round(res.bubble_ratio, 4), "sim_peak_gib": round(peak, 1),
             "check": "ok" if peak <= cfg.max_mem_gib else "over budget"}
 

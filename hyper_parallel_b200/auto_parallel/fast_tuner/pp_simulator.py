@@ -17,7 +17,7 @@ rows for a CSV file.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 from ...core.pipeline_parallel.scheduler import (MetaStep, MetaStepType, Schedule1F1B, ScheduleGPipe,
                                                 ScheduleInterleaved1F1B)
@@ -152,3 +152,65 @@ def render_text(res: SimResult, width: int = 100) -> str:
         out.append("peak bytes per stage: " + ", ".join(f"{b:.3g}" for b in res.peak_bytes))
     out.append(f"makespan {res.makespan:.4g}, bubble {res.bubble_ratio:.3f}")
     return "\n".join(out)
+
+
+def render_svg(res: SimResult, path: Optional[str] = None, width: int = 1200, lane_h: int = 22) -> str:
+    """The schedule as a self-contained SVG drawing (no plotting library needed): per stage one compute
+    lane (forward blocks light, backward blocks dark, labelled with the micro-batch), one p2p lane, and
+    below them the live-activation memory of every stage as a step line.  Returns the SVG text and
+    writes it to ``path`` when given.  Counterpart of the matplotlib timelines of the reference's
+    simulator (fast_tuner/pipeline_conductor/pp_simulator.py:820-1397)."""
+    if res.makespan <= 0:
+        return ""
+    stages = sorted(res.timeline)
+    has_comm = bool(res.comm) and any(res.comm.get(s) for s in stages)
+    rows_per_stage = 2 if has_comm else 1
+    left, top = 70, 24
+    sx = (width - left - 10) / res.makespan
+    lanes_h = len(stages) * rows_per_stage * (lane_h + 4)
+    mem_h = 90 if res.mem_timeline and any(res.mem_timeline.get(s) for s in stages) else 0
+    height = top + lanes_h + mem_h + 40
+    palette = ["#4e79a7", "#f28e2b", "#59a14f", "#e15759", "#76b7b2", "#edc948", "#b07aa1", "#9c755f"]
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="monospace" '
+           f'font-size="10">',
+           f'<text x="{left}" y="14">makespan {res.makespan:.4g}, bubble {res.bubble_ratio:.3f}</text>']
+    y = top
+    for s in stages:
+        out.append(f'<text x="4" y="{y + lane_h - 7}">stage {s}</text>')
+        for a, b, k, m, v in res.timeline[s]:
+            x, w = left + a * sx, max((b - a) * sx, 0.5)
+            fill = "#cfe2f3" if k == "FWD" else "#3d6b99"
+            ink = "#000" if k == "FWD" else "#fff"
+            out.append(f'<rect x="{x:.1f}" y="{y}" width="{w:.1f}" height="{lane_h}" fill="{fill}" stroke="#222" '
+                       f'stroke-width="0.4"><title>{k} micro {m} virtual stage {v}: {a:.4g} - {b:.4g}</title></rect>')
+            if w > 12:
+                out.append(f'<text x="{x + 2:.1f}" y="{y + lane_h - 7}" fill="{ink}">{m}</text>')
+        y += lane_h + 4
+        if has_comm:
+            out.append(f'<text x="4" y="{y + lane_h - 7}">p2p {s}</text>')
+            for a, b, k, m, v, dst in res.comm.get(s, []):
+                x, w = left + a * sx, max((b - a) * sx, 0.5)
+                fill = "#a8d08d" if k == "F" else "#c27ba0"
+                out.append(f'<rect x="{x:.1f}" y="{y + 4}" width="{w:.1f}" height="{lane_h - 8}" fill="{fill}">'
+                           f'<title>{"activation" if k == "F" else "gradient"} micro {m} of virtual stage {v} -> stage '
+                           f'{dst}</title></rect>')
+            y += lane_h + 4
+    if mem_h:
+        peak = max(max((b for _t, b in res.mem_timeline.get(s, [])), default=0.0) for s in stages) or 1.0
+        base = y + mem_h - 6
+        out.append(f'<text x="4" y="{y + 12}">live activations</text>')
+        for i, s in enumerate(stages):
+            pts, last = [], 0.0
+            for t, b in res.mem_timeline.get(s, []):
+                pts.append(f"{left + t * sx:.1f},{base - last / peak * (mem_h - 20):.1f}")
+                pts.append(f"{left + t * sx:.1f},{base - b / peak * (mem_h - 20):.1f}")
+                last = b
+            if pts:
+                out.append(f'<polyline fill="none" stroke="{palette[i % len(palette)]}" stroke-width="1.2" '
+                           f'points="{" ".join(pts)}"><title>stage {s}</title></polyline>')
+    out.append("</svg>")
+    text = "\n".join(out)
+    if path:
+        with open(path, "w") as f:
+            f.write(text)
+    return text

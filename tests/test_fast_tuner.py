@@ -119,3 +119,20 @@ def test_search_profile_balance_csv_end_to_end(tmp_path):
     piped = [e for e in ranked if e["pp"] > 1]
     assert piped and all(e["check"] == "ok" and 0.0 <= e["sim_bubble"] < 1.0 for e in piped)
     assert any(f.name.startswith("sim_") for f in (out / "pipeline_output").iterdir())
+
+
+def test_simulator_svg_rendering(tmp_path):
+    """The SVG drawing holds one block per compute step and per transfer, and the memory lines."""
+    from hyper_parallel_b200.auto_parallel.fast_tuner import pp_simulator as sim
+    order = sim.compute_order("vpp", 8, 4, 2)
+    res = sim.simulate(order, [1.0] * 8, [2.0] * 8, 4, p2p=0.1, act_bytes=[1e9] * 8, static_bytes=[2e9] * 4)
+    path = tmp_path / "schedule.svg"
+    text = sim.render_svg(res, str(path))
+    assert path.read_text() == text and text.startswith("<svg") and text.rstrip().endswith("</svg>")
+    n_compute = sum(len(v) for v in res.timeline.values())
+    n_comm = sum(len(v) for v in res.comm.values())
+    assert n_compute == 2 * 8 * 8 and n_comm > 0
+    assert text.count("<rect") == n_compute + n_comm
+    assert text.count("<polyline") == 4 and "bubble" in text
+    import xml.dom.minidom
+    xml.dom.minidom.parseString(text)                  # well-formed
