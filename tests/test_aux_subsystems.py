@@ -162,3 +162,21 @@ def test_metrics_writer_and_layer_timer(tmp_path):
         torch.randn(64, 64) @ torch.randn(64, 64)
     assert t.resolve()["x"] >= 0.0
     assert lt is not None
+
+
+def test_reserved_sms_shrink_the_persistent_grids(monkeypatch):
+    """``native.reserve_sms`` leaves an even number of SMs out of what persistent kernels may fill."""
+    from hyper_parallel_b200.ops import native
+    monkeypatch.setitem(native._sm_count, 0, 148)
+    monkeypatch.setattr(native, "_sm_reserve", 0)
+    import torch
+    dev = torch.device("cuda", 0)
+    assert native.sm_count(dev) == 148
+    native.reserve_sms(16)
+    assert native.sm_count(dev) == 132
+    native.reserve_sms(7)                       # CTA pairs: rounded down to an even number
+    assert native.sm_count(dev) == 142
+    native.reserve_sms(1000)
+    assert native.sm_count(dev) == 2            # never below one CTA pair
+    native.reserve_sms(0)
+    assert native.sm_count(dev) == 148
