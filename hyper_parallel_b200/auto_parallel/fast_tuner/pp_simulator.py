@@ -80,21 +80,19 @@ def simulate(order: Dict[int, List[MetaStep]], fwd: Sequence[float], bwd: Sequen
                     break
                 ready = 0.0
                 for d in deps:
-                    src = d[2] % stages
-                    if src == s or p2p <= 0.0 or d[2] == v:
-                        ready = max(ready, finish[d])
-                        continue
-                    if d not in arrive:
-                        # the transfer is a block on the sender's p2p lane, issued when the data exists
-                        t0 = max(finish[d], lane_free[src])
-                        lane_free[src] = t0 + p2p
-                        arrive[d] = t0 + p2p
-                        comm[src].append((t0, t0 + p2p, d[0].name[0], d[1], d[2], s))
-                    ready = max(ready, arrive[d])
+                    ready = max(ready, arrive.get(d, finish[d]))
                 start = max(clock[s], ready)
                 dur = fwd[v] if st.type == F else bwd[v]
                 clock[s] = start + dur
                 finish[(st.type, m, v)] = clock[s]
+                # the transfer of the result is a block on this stage's p2p lane, issued the moment
+                # the data exists (steps of a stage finish in time order, so the lane stays ordered)
+                nxt = v + 1 if st.type == F else v - 1
+                if p2p > 0.0 and 0 <= nxt < n_virtual and nxt % stages != s:
+                    t0 = max(clock[s], lane_free[s])
+                    lane_free[s] = t0 + p2p
+                    arrive[(st.type, m, v)] = t0 + p2p
+                    comm[s].append((t0, t0 + p2p, st.type.name[0], m, v, nxt % stages))
                 if st.type == F:
                     mem[s] += act[v]
                     mem_tl[s].append((start, mem[s]))
