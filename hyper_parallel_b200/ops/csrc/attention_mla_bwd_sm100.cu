@@ -7,7 +7,8 @@
 //
 //   S^T  = K Q^T            [kv 128 x q 64]   contraction 192
 //   dP^T = V dO^T           [kv 128 x q 64]   contraction 128
-//   P^T  = exp2(S^T c - lse),  dS^T = P^T o (dP^T - D)        -> bf16, shared memory
+//   P^T  = exp2(S^T c - lse)                                  -> bf16 pairs, tensor memory
+//   dS^T = P^T o (dP^T - D)                                   -> bf16, shared memory
 //   dV  += P^T dO           [kv 128 x 128]    accumulated over the whole walk
 //   dK  += dS^T Q           [kv 128 x 192]    accumulated over the whole walk
 //   dQ^T = K^T dS^T         [d 192 x q 64]    as two products of 128 rows: head elements 0..127 into
