@@ -9,7 +9,9 @@
 * ``moe_ep``   DeepSeek-V3 (``--layers``, ``--experts``) with expert parallelism over all ranks.
 * ``pp``       Llama-3-8B split into ``--pp`` pipeline stages (x ``--vpp`` chunks per rank), each stage
   ``--tp`` wide tensor parallel,
-  schedule ``--schedule {gpipe,1f1b,vpp}``, ``--micro`` micro-batches.
+  schedule ``--schedule {gpipe,1f1b,vpp}``, ``--micro`` micro-batches; ``--balance 1`` lets the
+  Fast-Tuner's balancer choose the layers of each virtual stage (the output head of a 128k
+  vocabulary costs more than two layers, so the last stage gets fewer).
 
 Timing rules are those of ``bench.py``: warm-up, CUDA events around exactly ``--steps`` steps,
 barrier + synchronize on both sides, max over ranks; the step includes the optimizer.  Rank 0
@@ -42,6 +44,9 @@ def parse(argv=None):
     ap.add_argument("--vpp", type=int, default=2)
     ap.add_argument("--micro", type=int, default=8)
     ap.add_argument("--schedule", default="1f1b", choices=["gpipe", "1f1b", "vpp"])
+    ap.add_argument("--balance", type=int, default=0,
+                    help="pp: 1 = split the layers with the Fast-Tuner's pipeline balancer (fewer layers beside "
+                         "the output head) instead of evenly")
     ap.add_argument("--experts", type=int, default=None)
     ap.add_argument("--fp8", type=int, default=1, help="moe_ep: fp8 block-scaled forward GEMMs (1) or bf16 (0)")
     return ap.parse_args(argv)
@@ -201,6 +206,14 @@ def run_pp(args, rank, world, dev):
     chunks = args.vpp if args.schedule == "vpp" else 1
     n_virtual = pp * chunks
     per = cfg.num_layers // n_virtual
+    ranges = [(i * per, (i + 1) * per) for i in range(n_virtual)]
+    if args.balance:
+        from hyper_parallel_b200.auto_parallel.fast_tuner.pipeline_balance import (
+            balance_pipeline, dense_transformer_profile, layer_ranges)
+        prof = dense_transformer_profile(cfg.hidden_size, cfg.ffn_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
+                                         cfg.vocab_size, args.seq_len)
+        ranges = layer_ranges(balance_pipeline(cfg.num_layers, cfg.num_layers, pp, chunks, args.micro, prof,
+                                               max_offset=3).layers)
     S, B = args.seq_len, args.batch
     stage_rank = rank // tp                      # ranks [s * tp, (s + 1) * tp) form pipeline stage s
 
@@ -267,7 +280,7 @@ def run_pp(args, rank, world, dev):
         # scheduled.  Inside pipeline stages tensor parallelism therefore uses NCCL + GEMM.
         os.environ["HPB_FUSED_TP"] = "0"
     idx = [stage_rank + c * pp for c in range(chunks)]
-    mods = [Chunk(i * per, (i + 1) * per, i == 0, i == n_virtual - 1) for i in idx]
+    mods = [Chunk(ranges[i][0], ranges[i][1], i == 0, i == n_virtual - 1) for i in idx]
     stages = [PipelineStage(m, i, n_virtual, device=dev) for m, i in zip(mods, idx)]
     if args.schedule == "vpp":
         sched = ScheduleInterleaved1F1B(stages, args.micro)
@@ -308,7 +321,8 @@ def run_pp(args, rank, world, dev):
     dist.all_reduce(mem, op=dist.ReduceOp.MAX)
     return {"config": {"model": "llama3_8b", "layers": cfg.num_layers, "parallelism": f"pp{pp} x tp{tp} {args.schedule}"
                        + (f" x{chunks} chunks" if chunks > 1 else ""), "micro_batches": args.micro,
-                       "global_batch": B * args.micro, "seq_len": S},
+                       "global_batch": B * args.micro, "seq_len": S,
+                       "layers_per_virtual_stage": [hi - lo for lo, hi in ranges]},
             "e2e_ms": e2e, "h2d_bytes": host[0].numel() * host.element_size(),
             "ms_per_step": ms, "value": tokens / (ms / 1e3), "loss": float(lt.detach()), "clocks": clocks,
             "memory_max_over_ranks": {"peak_allocated_gib": round(float(mem[0]), 2),

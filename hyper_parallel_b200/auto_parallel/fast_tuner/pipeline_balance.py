@@ -15,7 +15,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
-from .pp_simulator import compute_order, simulate
+from .pp_simulator import CompiledOrder, compute_order, simulate
 
 
 @dataclass
@@ -95,6 +95,14 @@ def balance_pipeline(num_layers: int, num_dense: int, stages: int, chunks: int, 
     even = [base + (1 if i < rem else 0) for i in range(slots)]
     best = {"t": float("inf"), "x": None}
     nodes = [0]
+    fast = CompiledOrder(order, slots, S)        # the search only needs the makespan
+    zero = [[0] * S for _ in range(V)]
+
+    def objective(flat: Sequence[int]) -> float:
+        layers = [[flat[c * S + s] for s in range(S)] for c in range(V)]
+        dense, moe = _split_types(layers, num_dense)
+        fwd, bwd = _slot_times(dense, moe, zero, prof, S, V)
+        return fast.makespan(fwd, bwd, p2p)
 
     def evaluate(flat: Sequence[int]):
         layers = [[flat[c * S + s] for s in range(S)] for c in range(V)]
@@ -114,9 +122,9 @@ def balance_pipeline(num_layers: int, num_dense: int, stages: int, chunks: int, 
                 return
             cand = flat + [left]
             nodes[0] += 1
-            res, *_ = evaluate(cand)
-            if res.makespan < best["t"]:
-                best["t"], best["x"] = res.makespan, cand
+            t = objective(cand)
+            if t < best["t"]:
+                best["t"], best["x"] = t, cand
             return
         for delta in sorted(range(-max_offset, max_offset + 1), key=abs):
             n = even[i] + delta
@@ -163,3 +171,27 @@ def _stage_memory(layers, rec, peak_live, prof: LayerProfile, S: int, V: int) ->
         static = prof.static_mem + n * prof.layer_mem + (prof.lm_head_mem if s == S - 1 else 0.0)
         out.append(static + act)
     return out
+
+
+def layer_ranges(layers: Sequence[Sequence[int]]) -> List[tuple]:
+    """``[chunk][stage]`` layer counts -> ``(first, end)`` layer range of every virtual stage, in model
+    order (virtual stage ``v = chunk * stages + stage``): what a pipeline runtime needs to build
+    the module of each virtual stage from a :class:`BalanceResult`."""
+    out, lo = [], 0
+    for row in layers:
+        for n in row:
+            out.append((lo, lo + int(n)))
+            lo += int(n)
+    return out
+
+
+def dense_transformer_profile(hidden: int, ffn: int, heads: int, kv_heads: int, head_dim: int, vocab: int,
+                              seq_len: int) -> LayerProfile:
+    """Analytic :class:`LayerProfile` of a dense decoder (times in GFLOP per token, backward = 2 x
+    forward): enough to place the output head, which costs ``2 * hidden * vocab`` per token -- more
+    than two layers of an 8B model with a 128k vocabulary -- on a stage with fewer layers."""
+    mm = (heads + 2 * kv_heads) * head_dim * hidden + heads * head_dim * hidden + 3 * hidden * ffn
+    layer = (2.0 * mm + 4.0 * heads * head_dim * seq_len / 2) / 1e9
+    head = 2.0 * hidden * vocab / 1e9
+    return LayerProfile(dense_fw=layer, dense_bw=2 * layer, moe_fw=layer, moe_bw=2 * layer,
+                        head_fw=head, head_bw=2 * head)

@@ -136,3 +136,32 @@ def test_simulator_svg_rendering(tmp_path):
     assert text.count("<polyline") == 4 and "bubble" in text
     import xml.dom.minidom
     xml.dom.minidom.parseString(text)                  # well-formed
+
+
+def test_balanced_layer_ranges_put_fewer_layers_beside_the_head():
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pipeline_balance import (
+        dense_transformer_profile, layer_ranges)
+    prof = dense_transformer_profile(4096, 14336, 32, 8, 128, 128256, 4096)
+    assert prof.head_fw > 2 * prof.dense_fw            # Llama-3-8B: the head is worth more than two layers
+    for stages, chunks in ((2, 1), (4, 1), (2, 2), (4, 2)):
+        even = balance_pipeline(32, 32, stages, chunks, 8, prof, max_offset=0)
+        bal = balance_pipeline(32, 32, stages, chunks, 8, prof, max_offset=3)
+        assert bal.makespan < even.makespan
+        rng = layer_ranges(bal.layers)
+        assert len(rng) == stages * chunks and rng[0][0] == 0 and rng[-1][1] == 32
+        assert all(a[1] == b[0] for a, b in zip(rng, rng[1:]))           # contiguous, in model order
+        sizes = [hi - lo for lo, hi in rng]
+        assert sizes[-1] < 32 // (stages * chunks)                       # the head's stage is lighter
+
+
+def test_compiled_order_matches_full_simulation():
+    import random
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pp_simulator import CompiledOrder, compute_order, simulate
+    rnd = random.Random(0)
+    for kind, S, V, M in (("1f1b", 4, 1, 8), ("vpp", 4, 2, 8), ("vpp", 2, 3, 6), ("gpipe", 3, 1, 5), ("vpp", 4, 2, 6)):
+        order = compute_order(kind, M, S, V)
+        fast = CompiledOrder(order, S * V, S)
+        for p2p in (0.0, 0.3, 2.0):
+            f = [rnd.uniform(0.5, 2) for _ in range(S * V)]
+            b = [rnd.uniform(1, 4) for _ in range(S * V)]
+            assert abs(simulate(order, f, b, S, p2p).makespan - fast.makespan(f, b, p2p)) < 1e-9
