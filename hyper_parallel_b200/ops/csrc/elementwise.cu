@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "hpb_noalloc.h"
 
 namespace hpb {
 
@@ -614,11 +615,6 @@ static __device__ __align__(256) float g_noalloc_rmsnorm_scratch[kNoAllocMaxPart
 constexpr int kNoAllocMaxDevices = 64;
 static float* g_noalloc_scratch_addr[kNoAllocMaxDevices] = {};
 }  // namespace hpb
-
-#define HPB_NOALLOC_E_TOO_LARGE (-100)
-#define HPB_NOALLOC_E_BAD_SHAPE (-101)
-#define HPB_NOALLOC_E_DEVICE (-102)
-#define HPB_NOALLOC_E_SYMBOL (-103)
 
 extern "C" const char* hpb_noalloc_strerror(int code) {
   switch (code) {

@@ -9,6 +9,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Negative return codes of the entry points below (positive values are cudaError_t).
+#define HPB_NOALLOC_E_TOO_LARGE (-100)   // H above hpb_noalloc_max_h()
+#define HPB_NOALLOC_E_BAD_SHAPE (-101)   // H not a positive multiple of 8, or T < 0
+#define HPB_NOALLOC_E_DEVICE (-102)      // current device unknown, or its index is 64 or more
+#define HPB_NOALLOC_E_SYMBOL (-103)      // the device address of the scratch array could not be resolved
+
 #ifdef __cplusplus
 extern "C" {
 #endif
