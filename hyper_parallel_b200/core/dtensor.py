@@ -353,8 +353,25 @@ def _factory(fn, size, device_mesh, placements, **kwargs) -> DTensor:
         size = (size,)
     size = tuple(size)
     layout = _build_layout(device_mesh, placements, len(size))
-    local_shape = layout.get_local_shape(size)
-    return DTensor._wrap(fn(local_shape, **kwargs), layout)
+    return DTensor._wrap(fn(compute_local_shape(size, layout), **kwargs), layout)
+
+
+def compute_local_shape(global_shape, layout: Layout) -> Tuple[int, ...]:
+    """This rank's shard shape of a tensor of ``global_shape`` under ``layout``, with ``torch.chunk``
+    semantics where a dimension does not divide evenly: chunks of ``ceil(n / parts)``, a shorter last
+    one, empty ones after it.  The factory functions use it (reference dtensor.py:334-369,
+    ``compute_local_shape_and_global_offset``); the layout algebra itself (``shape``,
+    redistribution) assumes even shards, as the reference's does."""
+    from .random import local_shard_size_and_offset
+    mesh = layout.mesh
+    coord = mesh.get_coordinate()
+    out = []
+    for d, n in enumerate(global_shape):
+        n = int(n)
+        for a in layout.dim_axes[d]:
+            n, _ = local_shard_size_and_offset(n, mesh.mesh_shape[a], coord[a])
+        out.append(n)
+    return tuple(out)
 
 
 def ones(size, device_mesh=None, placements=None, **kwargs) -> DTensor:

@@ -24,6 +24,28 @@ from .layout import Layout
 
 logger = logging.getLogger(__name__)
 
+__all__ = ["OffsetBasedRNGTracker", "is_rng_supported_mesh", "fork_rng", "local_shard_size_and_offset",
+           "get_rng_tracker", "manual_seed", "distributed_rand_like"]
+
+
+def is_rng_supported_mesh() -> bool:
+    """Whether sharded random ops are supported here (reference random.py:31-45 asks the device
+    handle for ``set_rng_state``).  Always true: CUDA generators expose their Philox state and the
+    CPU generator is handled by re-seeding per offset window."""
+    return True
+
+
+def local_shard_size_and_offset(curr_local_size: int, num_chunks: int, rank: int):
+    """``(size, start)`` of chunk ``rank`` when ``curr_local_size`` elements are split into
+    ``num_chunks`` chunks the way ``torch.chunk`` does: chunks of ``ceil(size / chunks)``, a
+    shorter last one, empty ones after it (their start is the end of the data).  Counterpart of
+    reference random.py:386-419."""
+    full = -(-curr_local_size // num_chunks)
+    start = full * rank
+    if start > curr_local_size:
+        return 0, curr_local_size
+    return min(curr_local_size, start + full) - start, start
+
 
 class _PhiloxState:
     """View of a CUDA generator state as (seed, offset)."""
@@ -79,6 +101,17 @@ class OffsetBasedRNGTracker:
     def manual_seed(self, seed: int) -> None:
         self._seed, self._offset = int(seed), 0
 
+    _manual_seed = manual_seed          # the reference's spelling (random.py:119)
+
+    @property
+    def distribute_region_enabled(self) -> bool:
+        """False: ``_distribute_region`` leaves offsets alone and random ops draw from the local generator."""
+        return self._enabled
+
+    @distribute_region_enabled.setter
+    def distribute_region_enabled(self, value: bool) -> None:
+        self._enabled = bool(value)
+
     def get_seed(self) -> int:
         return self._seed
 
@@ -101,10 +134,30 @@ class OffsetBasedRNGTracker:
         return idx
 
     @contextlib.contextmanager
-    def _distribute_region(self, layout: Layout, local_shape: Sequence[int]):
-        """Random ops inside produce shard-consistent values for a tensor laid out as ``layout``."""
+    def _distribute_region(self, layout=None, local_shape=None, global_shape: Optional[Sequence[int]] = None, *,
+                           device_mesh=None, placements=None):
+        """Random ops inside produce shard-consistent values for a tensor laid out as ``layout``.
+
+        Two call forms: ``(layout, local_shape)``, and the reference's
+        ``(device_mesh, placements, global_shape)`` (random.py:161-196), positional or by keyword.
+        In the second form the window of a shard is sized by the first (largest) shard, so that
+        every rank computes the same offsets when the tensor does not divide evenly.  The local
+        generator state is restored on exit in both forms, also when the region is disabled."""
+        if device_mesh is not None:
+            layout, local_shape = device_mesh, placements
+        if not isinstance(layout, Layout):
+            from .dtensor import _build_layout
+            if global_shape is None:
+                raise TypeError("_distribute_region(device_mesh, placements, global_shape): global_shape is missing")
+            global_shape = tuple(int(g) for g in global_shape)
+            layout = _build_layout(layout, local_shape, len(global_shape))
+            local_shape = list(global_shape)
+            for d, axes in enumerate(layout.dim_axes):
+                for a in axes:
+                    local_shape[d] = -(-local_shape[d] // layout.mesh.mesh_shape[a])
         if not self._enabled:
-            yield
+            with self.fork_rng():
+                yield
             return
         local_numel = 1
         for s in local_shape:
@@ -150,6 +203,27 @@ class OffsetBasedRNGTracker:
             yield
         finally:
             self._enabled = prev
+
+
+@contextlib.contextmanager
+def fork_rng(devices=None, enabled: bool = True, device_type: str = "cuda"):
+    """Save the CPU generator state and that of ``devices`` (default: every visible GPU) and put
+    them back on exit; ``enabled=False`` does nothing.  Module-level counterpart of reference
+    random.py:424-475."""
+    if not enabled:
+        yield
+        return
+    if devices is None:
+        devices = range(torch.cuda.device_count()) if device_type == "cuda" and torch.cuda.is_available() else ()
+    devices = list(devices)
+    cpu_state = torch.get_rng_state()
+    dev_states = [torch.cuda.get_rng_state(d) for d in devices]
+    try:
+        yield
+    finally:
+        torch.set_rng_state(cpu_state)
+        for d, st in zip(devices, dev_states):
+            torch.cuda.set_rng_state(st, d)
 
 
 _TRACKER: Optional[OffsetBasedRNGTracker] = None

@@ -287,6 +287,39 @@ class LikeDistributedOp(DistributedOp):
         return make(x, x.dim_axes)
 
 
+def _in_rng_region(func, layout):
+    """``func`` run inside the distributed RNG tracker's region for ``layout``: distinct shards draw
+    from distinct Philox windows, replicas of a shard draw the same numbers, and every rank's
+    tracker advances by the same amount -- whatever the ranks' local generators hold."""
+    def impl(t, *a, **k):
+        from ...random import get_rng_tracker
+        with get_rng_tracker()._distribute_region(layout, tuple(t.shape)):
+            return func(t, *a, **k)
+    return impl
+
+
+class RandomLikeDistributedOp(LikeDistributedOp):
+    """rand_like / randn_like on a DTensor: the sharding of the input, values from the distributed
+    RNG tracker (core/random.py).  The reference ships the tracker (hyper_parallel/core/random.py:
+    123-296) but draws these from each rank's local generator, so ranks seeded alike give every
+    shard the same numbers and ranks seeded differently let replicas diverge."""
+
+    def get_expand_impl(self, func, output_layout, layouts, extra_args):
+        return _in_rng_region(func, output_layout)
+
+
+class DropoutDistributedOp(DistributedOp):
+    """dropout / bernoulli: element-wise in the layout of the input, mask drawn in the tracker's region."""
+
+    def infer_layout(self, layouts, extra_args):
+        self._check_partial_inputs(layouts)
+        x = layouts[0]
+        return make(x, x.dim_axes)
+
+    def get_expand_impl(self, func, output_layout, layouts, extra_args):
+        return _in_rng_region(func, output_layout)
+
+
 class TrilDistributedOp(DistributedOp):
     """tril / triu: the last two dims must be unsharded."""
 
