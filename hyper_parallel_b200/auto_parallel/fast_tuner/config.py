@@ -7,6 +7,7 @@ YAML, a Megatron / MindSpeed launch script (regex over ``--flag value``), or a p
 from __future__ import annotations
 
 import json
+import os
 import re
 from dataclasses import dataclass, field
 from typing import Any, Dict, Optional
@@ -94,7 +95,14 @@ class TunerConfig:
     def from_json(path: str) -> "TunerConfig":
         with open(path, "r", encoding="utf-8") as f:
             raw = json.load(f)
-        return TunerConfig.from_dict(raw)
+        cfg = TunerConfig.from_dict(raw)
+        # a model file named relative to the setup file (not to the working directory) is found too
+        base = os.path.dirname(os.path.abspath(path))
+        for k in ("model_json", "toml_path", "yaml_path", "shell_path"):
+            v = getattr(cfg, k)
+            if v and not os.path.isabs(v) and not os.path.exists(v) and os.path.exists(os.path.join(base, v)):
+                setattr(cfg, k, os.path.join(base, v))
+        return cfg
 
     @staticmethod
     def from_dict(raw: Dict[str, Any]) -> "TunerConfig":

@@ -61,9 +61,18 @@ def taylor_search_tool(cfg: TunerConfig, spec: Optional[ModelSpec] = None, hw: O
                 break
         with open(os.path.join(cfg.output_path, "search_summary.json"), "w") as f:
             json.dump(summary, f)
-    # analytic stand-in when nothing was profiled: a backward costs two forwards, a MoE layer as much
-    # as a dense one
-    lp_default = LayerProfile(dense_fw=1.0, dense_bw=2.0, moe_fw=1.0, moe_bw=2.0)
+    return rank_candidates(space, spec, cfg, hw, profile.to_layer_profile() if profile is not None else None, top_k)
+
+
+def rank_candidates(space: List[Config], spec: ModelSpec, cfg: TunerConfig, hw: Optional[Hardware] = None,
+                    lp: Optional[LayerProfile] = None, top_k: int = 20) -> List[dict]:
+    """Second half of the search, also the body of the stand-alone pipeline tool: score every
+    candidate with the cost model, balance the pipeline of the pipelined ones with the layer profile
+    ``lp`` (measured, or the analytic stand-in: a backward costs two forwards, a MoE layer as much as
+    a dense one), re-check the best ``top_k`` in the schedule simulator and write
+    ``pipeline_output/ranked_configs.csv``."""
+    hw = hw or Hardware(gpus_per_node=cfg.gpus_per_node)
+    lp = lp or LayerProfile(dense_fw=1.0, dense_bw=2.0, moe_fw=1.0, moe_bw=2.0)
     ranked = []
     scored = sorted(space, key=lambda c: estimate_step_time(spec, c, hw))[: max(top_k * 5, 50)]
     for c in scored:
@@ -73,7 +82,6 @@ def taylor_search_tool(cfg: TunerConfig, spec: Optional[ModelSpec] = None, hw: O
                  "mbs": mbs_of(c), "sp": sp_of(c), "step_time_us": t * 1e6}
         if pp > 1:
             micro = max(cfg.gbs // (dp_of(c) * mbs_of(c)), 1)
-            lp = profile.to_layer_profile() if profile is not None else lp_default
             bal = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp)
             entry.update({"layers": bal.layers, "offset": bal.offset, "recompute": bal.recompute,
                           "bubble": round(bal.bubble_ratio, 4)})
@@ -91,8 +99,7 @@ def taylor_search_tool(cfg: TunerConfig, spec: Optional[ModelSpec] = None, hw: O
         if c is None or e["pp"] <= 1 or "layers" not in e:
             e["check"] = "n/a"
             continue
-        e.update(_recheck(spec, c, e, profile.to_layer_profile() if profile is not None else lp_default, cfg,
-                          os.path.join(cfg.output_path, "pipeline_output")))
+        e.update(_recheck(spec, c, e, lp, cfg, os.path.join(cfg.output_path, "pipeline_output")))
     out_csv = os.path.join(cfg.output_path, "pipeline_output")
     os.makedirs(out_csv, exist_ok=True)
     with open(os.path.join(out_csv, "ranked_configs.csv"), "w", newline="") as f:

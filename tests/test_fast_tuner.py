@@ -165,3 +165,52 @@ def test_compiled_order_matches_full_simulation():
             f = [rnd.uniform(0.5, 2) for _ in range(S * V)]
             b = [rnd.uniform(1, 4) for _ in range(S * V)]
             assert abs(simulate(order, f, b, S, p2p).makespan - fast.makespan(f, b, p2p)) < 1e-9
+
+
+def test_pipeline_tool_ranks_the_candidates_of_an_earlier_search(tmp_path):
+    """Phase 1 leaves the candidate CSV; the stand-alone pipeline tool expands it over interleave depths
+    and micro-batch sizes, balances with the given ratios and writes the ranked CSV and drawings."""
+    import csv
+    from hyper_parallel_b200.auto_parallel.fast_tuner import pipeline_tool
+    mj = tmp_path / "model.json"
+    mj.write_text(json.dumps({k: getattr(LLAMA8B, k) for k in LLAMA8B.__dataclass_fields__}))
+    cfg = TunerConfig(rank_num=8, gbs=16, gpus_per_node=8, nnodes=1, output_path=str(tmp_path / "out"),
+                      dryrun=True, model_json=str(mj), strategy=Strategy(EP=False, CP=False), alg_phase=1)
+    assert "summary" in taylor_search_tool(cfg)[0]
+    nd = tmp_path / "out" / "nd_candidate_config.csv"
+    space = pipeline_tool.read_candidates(str(nd), LLAMA8B, 16, max_vpp=2)
+    assert space and all(c[0][1][2] == 1 for c in space if c[0][0][3] == 1)        # no pipeline: no interleaving
+    assert any(c[0][1][2] == 2 for c in space) and len({repr(c) for c in space}) == len(space)
+    rc = pipeline_tool.main(["--nd_path", str(nd), "--model_json", str(mj), "--gbs", "16", "--rank_num", "8",
+                             "--output_path", str(tmp_path / "out2"), "--head_loss", "2.2", "--topn", "6"])
+    assert rc == 0
+    rows = list(csv.DictReader(open(tmp_path / "out2" / "pipeline_output" / "ranked_configs.csv")))
+    assert 1 <= len(rows) <= 6
+    times = [float(r["step_time(us)"]) for r in rows]
+    assert times == sorted(times)
+    piped = [r for r in rows if int(r["pp"]) > 1]
+    for r in piped:                                                               # the head's stage is lighter
+        layers = json.loads(r["layers"])
+        assert sum(map(sum, layers)) == LLAMA8B.num_layers and layers[-1][-1] <= layers[0][0]
+        assert r["check"] in ("ok", "over budget")
+    lp = pipeline_tool.profile_from_ratios(backward_ratio=2.5, layer_ratio=0.33, head_loss=1.5, recompute_ratio=1.0)
+    assert (lp.dense_bw, lp.moe_fw, lp.head_bw) == (2.5, 0.33, 3.75) and abs(lp.moe_bw - 0.825) < 1e-9
+
+
+def test_shipped_examples_parse_and_search(tmp_path):
+    """Every example model file is read by its ingester, and the two setup files drive a dry-run search."""
+    from hyper_parallel_b200.auto_parallel.fast_tuner import config as tcfg
+    ex = os.path.join(os.path.dirname(tcfg.__file__), "examples")
+    titan = tcfg.model_from_toml(os.path.join(ex, "moe_16b_titan.toml"))
+    assert (titan.num_layers, titan.expert_num, titan.num_experts_per_tok, titan.first_k_dense) == (28, 64, 6, 1)
+    assert titan.moe_layers == 27 and titan.seq_length == 4096 and titan.global_batch_size == 64
+    mf = tcfg.model_from_yaml(os.path.join(ex, "dense_13b_mindformers.yaml"))
+    assert (mf.num_layers, mf.hidden_size, mf.ffn_hidden_size, mf.world_size, mf.global_batch_size) == (40, 5120, 13824, 8, 8)
+    mg = tcfg.model_from_shell(os.path.join(ex, "moe_megatron.sh"))
+    assert (mg.num_layers, mg.hidden_size, mg.expert_num, mg.num_kv_heads, mg.first_k_dense) == (24, 4096, 32, 8, 2)
+    for setup, pp_expected in (("args_for_parallel_tool.json", True), ("args_for_moe_search.json", True)):
+        cfg = TunerConfig.from_json(os.path.join(ex, setup))
+        cfg.output_path = str(tmp_path / setup[:-5])
+        ranked = taylor_search_tool(cfg, top_k=5)
+        assert ranked and "step_time_us" in ranked[0]
+        assert os.path.exists(os.path.join(cfg.output_path, "pipeline_output", "ranked_configs.csv"))
