@@ -214,3 +214,34 @@ def test_shipped_examples_parse_and_search(tmp_path):
         ranked = taylor_search_tool(cfg, top_k=5)
         assert ranked and "step_time_us" in ranked[0]
         assert os.path.exists(os.path.join(cfg.output_path, "pipeline_output", "ranked_configs.csv"))
+
+
+def test_memory_model_is_refitted_from_measured_peaks():
+    """The balancer's estimate of activation memory is 40 % low: the first balance overshoots the limit
+    when 'measured', the re-fit learns the true coefficients from the measured stage peaks and the next
+    balance recomputes more layers and fits."""
+    from hyper_parallel_b200.auto_parallel.fast_tuner import memory_fit
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pipeline_balance import _stage_memory
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pp_simulator import compute_order, simulate
+    S, V, M, L = 4, 1, 8, 32
+    truth = LayerProfile(act_mem=10.0, recomp_mem=1.0, layer_mem=3.0, static_mem=20.0, lm_head_mem=15.0)
+    guess = LayerProfile(act_mem=6.0, recomp_mem=1.0, layer_mem=3.0, static_mem=20.0, lm_head_mem=15.0)
+    live = simulate(compute_order("1f1b", M, S, V), [1.0] * S, [2.0] * S, S).peak_live
+
+    def measure(res):
+        return _stage_memory(res.layers, res.recompute, live, truth, S, V)
+
+    limit = 260.0
+    rounds = memory_fit.balance_with_memory_feedback(L, L, S, V, M, guess, limit, measure)
+    assert len(rounds) >= 2 and rounds[0].over_mb > 0          # the low estimate overshoots when measured
+    last = rounds[-1]
+    assert last.over_mb == 0 and max(last.measured_mb) <= limit
+    assert sum(map(sum, last.result.recompute)) > sum(map(sum, rounds[0].result.recompute))
+    assert abs(last.profile.act_mem - truth.act_mem) < 0.5     # learnt from the measured peaks
+    # a coefficient the observations cannot identify keeps its prior value
+    obs = [memory_fit.MemoryObservation(8, 0, 4.0, False, 20.0 + 8 * 3.0 + 8 * 4.0 * 10.0),
+           memory_fit.MemoryObservation(6, 0, 2.0, False, 20.0 + 6 * 3.0 + 6 * 2.0 * 10.0),
+           memory_fit.MemoryObservation(9, 0, 3.0, False, 20.0 + 9 * 3.0 + 9 * 3.0 * 10.0)]
+    fit = memory_fit.fit_memory(obs, guess)
+    assert fit.recomp_mem == guess.recomp_mem and fit.lm_head_mem == guess.lm_head_mem
+    assert abs(fit.act_mem - 10.0) < 1e-6 and abs(memory_fit.predict(fit, obs[0]) - obs[0].peak_mb) < 1e-6
