@@ -53,7 +53,8 @@ def build_initial_spaces(spec: ModelSpec, strategy: Strategy = Strategy(DP=True,
         ep_options = [1]
     out: List[Config] = []
     for dp, tp, cp, pp in part1:
-        vp_options = list(range(1, math.ceil(spec.num_layers / pp)))
+        # interleave depths: 1 without a pipeline, else every depth below ceil(layers / pp)
+        vp_options = [1] if pp == 1 else list(range(1, math.ceil(spec.num_layers / pp)))
         for ep, op, vp, mbs in itertools.product(ep_options, divisors(dp), vp_options, (1, 2, 4)):
             if not strategy.FSDP and op != dp:
                 op = -1

@@ -30,6 +30,16 @@ def test_space_sizes_and_rules():
     assert all(pp_of(c) <= 16 // c[0][0][0] // c[0][1][3] for c in pruned)              # pp <= gbs/dp/mbs
     no_pp = build_initial_spaces(LLAMA8B, Strategy(PP=False, CP=False, EP=False))
     assert all(pp_of(c) == 1 for c in no_pp)
+    assert all(c[0][1][2] == 1 for c in space if pp_of(c) == 1)                         # no pipeline: depth 1 only
+    # the size of the space follows from the rules: per (dp, tp, cp, pp): divisors(dp) FSDP degrees x
+    # depths below ceil(L / pp) (1 without a pipeline) x 3 micro-batch sizes x (1 + E / 2) expert
+    # degrees, doubled by the sequence-parallel switch where tp > 1
+    moe = ModelSpec(num_layers=12, expert_num=8, world_size=16)
+    want = 0
+    for dp, tp, cp, pp in factorizations4(16):
+        depths = 1 if pp == 1 else max(-(-12 // pp) - 1, 0)
+        want += sum(1 for d in range(1, dp + 1) if dp % d == 0) * depths * 3 * (1 + 8 // 2) * (2 if tp > 1 else 1)
+    assert len(build_initial_spaces(moe)) == want
 
 
 def test_memory_model_orders_and_prunes():
