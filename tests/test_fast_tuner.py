@@ -255,3 +255,22 @@ def test_memory_model_is_refitted_from_measured_peaks():
     fit = memory_fit.fit_memory(obs, guess)
     assert fit.recomp_mem == guess.recomp_mem and fit.lm_head_mem == guess.lm_head_mem
     assert abs(fit.act_mem - 10.0) < 1e-6 and abs(memory_fit.predict(fit, obs[0]) - obs[0].peak_mb) < 1e-6
+
+
+def test_grey_box_prune_reproduces_the_reference_unit_test_count():
+    """Golden vector of the reference's ``unit_tests/nd_search_test.py:28-84``: forty dry-run peaks
+    (20 (dp, tp, pp) groups at ep 4 and 8) of DeepSeek-V3 on 1024 ranks, a 55 GB limit and ep <= 64
+    leave exactly 10 candidates of 5 fields each."""
+    info = [[32, 2, 16, 8, 142786], [128, 2, 4, 8, 188944], [16, 2, 32, 4, 153480], [16, 8, 8, 8, 96950],
+            [64, 8, 2, 8, 825586], [64, 2, 8, 4, 221281], [8, 4, 32, 8, 81943], [64, 4, 4, 4, 283005],
+            [64, 1, 16, 8, 241679], [32, 8, 4, 4, 270048], [8, 4, 32, 4, 98967], [256, 2, 2, 4, 1656206],
+            [64, 4, 4, 8, 162045], [8, 8, 16, 8, 68632], [4, 8, 32, 8, 54686], [128, 1, 8, 4, 299846],
+            [8, 8, 16, 4, 101784], [32, 8, 4, 8, 148595], [256, 1, 4, 4, 363705], [32, 4, 8, 8, 116591],
+            [4, 8, 32, 4, 71710], [32, 4, 8, 4, 181999], [32, 2, 16, 4, 175938], [16, 2, 32, 8, 136456],
+            [64, 8, 2, 4, 1635569], [64, 2, 8, 8, 155874], [128, 1, 8, 8, 234458], [16, 4, 16, 8, 93350],
+            [256, 2, 2, 8, 847944], [128, 4, 2, 8, 832465], [16, 8, 8, 4, 162358], [32, 1, 32, 8, 245502],
+            [512, 1, 2, 8, 927251], [64, 1, 16, 4, 274811], [16, 4, 16, 4, 126502], [128, 2, 4, 4, 309904],
+            [32, 1, 32, 4, 262506], [256, 1, 4, 8, 242746], [128, 4, 2, 4, 1642448], [512, 1, 2, 4, 1687161]]
+    out = grey_box_memory_prune(ModelSpec(expert_num=256, world_size=1024), info, [4, 8], 64, max_mem_mib=55 * 1024)
+    assert len(out) == 10 and all(len(r) == 5 and r[3] <= 64 and r[4] <= 55 * 1024 for r in out)
+    assert [4, 8, 32, 8, 54686] in out            # a measured point that fits is returned as measured
