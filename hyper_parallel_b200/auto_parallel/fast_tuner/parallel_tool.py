@@ -84,7 +84,7 @@ def rank_candidates(space: List[Config], spec: ModelSpec, cfg: TunerConfig, hw: 
             micro = max(cfg.gbs // (dp_of(c) * mbs_of(c)), 1)
             bal = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp)
             entry.update({"layers": bal.layers, "offset": bal.offset, "recompute": bal.recompute,
-                          "bubble": round(bal.bubble_ratio, 4)})
+                          "select_recompute": bal.select_recompute, "bubble": round(bal.bubble_ratio, 4)})
             even = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp, max_offset=0)
             entry["step_time_us"] = t * 1e6 * bal.makespan / max(even.makespan, 1e-9)
         ranked.append(entry)
@@ -105,11 +105,11 @@ def rank_candidates(space: List[Config], spec: ModelSpec, cfg: TunerConfig, hw: 
     with open(os.path.join(out_csv, "ranked_configs.csv"), "w", newline="") as f:
         w = csv.writer(f)
         w.writerow(["rank", "dp", "tp", "pp", "ep", "op", "vp", "mbs", "sp", "step_time(us)", "layers", "offset",
-                    "recompute", "bubble", "sim_bubble", "sim_peak_gib", "check"])
+                    "recompute", "select_recompute", "bubble", "sim_bubble", "sim_peak_gib", "check"])
         for i, e in enumerate(ranked):
             w.writerow([i, e["dp"], e["tp"], e["pp"], e["ep"], e["op"], e["vp"], e["mbs"], e["sp"],
                         round(e["step_time_us"]), e.get("layers", ""), e.get("offset", ""), e.get("recompute", ""),
-                        e.get("bubble", ""), e.get("sim_bubble", ""), e.get("sim_peak_gib", ""), e.get("check", "")])
+                        e.get("select_recompute", ""), e.get("bubble", ""), e.get("sim_bubble", ""), e.get("sim_peak_gib", ""), e.get("check", "")])
     return ranked
 
 

@@ -30,11 +30,26 @@ class LayerProfile:
     embed_fw: float = 0.0         # embedding on the first virtual stage
     embed_bw: float = 0.0
     recompute_extra: float = 1.0  # extra backward time of a fully recomputed layer, in units of its forward
+    select_extra: float = 0.3     # the same for a selectively recomputed layer (attention core / activations only)
     act_mem: float = 1.0          # activation MB per layer per live micro-batch
     recomp_mem: float = 0.1       # the same for a fully recomputed layer
+    select_mem: Optional[float] = None    # the same for a selectively recomputed layer; None: no selective recompute
     layer_mem: float = 1.0        # static MB per layer (weights + optimizer)
     static_mem: float = 0.0       # static MB per stage
     lm_head_mem: float = 0.0
+    # MoE layers where they differ from dense ones, and the first stage (embedding) where it differs
+    # from the others (the reference's memory table keeps both apart, pipeline_conductor/memory.py:28-60)
+    moe_act_mem: Optional[float] = None
+    moe_recomp_mem: Optional[float] = None
+    moe_select_mem: Optional[float] = None
+    moe_layer_mem: Optional[float] = None
+    static_mem0: Optional[float] = None
+
+    def mem_of(self, moe: bool):
+        """``(act, recomp, select, layer)`` MB of a dense or a MoE layer."""
+        pick = (lambda m, d: d if m is None else m) if moe else (lambda m, d: d)
+        return (pick(self.moe_act_mem, self.act_mem), pick(self.moe_recomp_mem, self.recomp_mem),
+                pick(self.moe_select_mem, self.select_mem), pick(self.moe_layer_mem, self.layer_mem))
 
 
 @dataclass
@@ -46,9 +61,10 @@ class BalanceResult:
     bubble_ratio: float
     peak_mem: List[float]
     offset: List[List[int]] = field(default_factory=list)   # deviation from the even split
+    select_recompute: List[List[int]] = field(default_factory=list)   # [chunk][stage] selectively recomputed layers
 
 
-def _slot_times(dense, moe, rec, prof: LayerProfile, S: int, V: int):
+def _slot_times(dense, moe, rec, prof: LayerProfile, S: int, V: int, sel=None):
     fwd, bwd = [], []
     for v in range(S * V):
         c, s = divmod(v, S)
@@ -59,6 +75,8 @@ def _slot_times(dense, moe, rec, prof: LayerProfile, S: int, V: int):
         if total and r:
             avg_fw = f / total
             b += r * avg_fw * prof.recompute_extra
+        if total and sel is not None and sel[c][s]:
+            b += sel[c][s] * (f / total) * prof.select_extra
         if v == 0:
             f += prof.embed_fw
             b += prof.embed_bw
@@ -141,35 +159,84 @@ def balance_pipeline(num_layers: int, num_dense: int, stages: int, chunks: int, 
     dfs(0, [], num_layers)
     res, layers, dense, moe = evaluate(best["x"])
     rec = [[0] * S for _ in range(V)]
-    peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V)
+    sel = [[0] * S for _ in range(V)]
+    peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V, dense, sel)
     if mem_limit_mb is not None:
-        # greedy: recompute one more layer on the stage that exceeds its limit the most
-        for _ in range(num_layers):
-            over = [(peak_mem[s] - mem_limit_mb, s) for s in range(S) if peak_mem[s] > mem_limit_mb]
+        limits = list(mem_limit_mb) if isinstance(mem_limit_mb, (list, tuple)) else [float(mem_limit_mb)] * S
+        if len(limits) != S:
+            raise ValueError(f"mem_limit_mb needs one value or one per stage ({S}), got {len(limits)}")
+        # greedy: on the stage that exceeds its limit the most, take the move (selectively recompute one
+        # more layer / fully recompute one more layer, per chunk) that frees the most memory per unit
+        # of extra backward time
+        for _ in range(4 * num_layers):
+            over = [(peak_mem[s] - limits[s], s) for s in range(S) if peak_mem[s] > limits[s] + 1e-9]
             if not over:
                 break
             _, s = max(over)
-            cands = [(c, s) for c in range(V) if rec[c][s] < layers[c][s]]
-            if not cands:
+            best_move, best_score = None, 0.0
+            for c in range(V):
+                n = layers[c][s]
+                if not n:
+                    continue
+                avg_fw = (dense[c][s] * prof.dense_fw + moe[c][s] * prof.moe_fw) / n
+                moves = []
+                if rec[c][s] + sel[c][s] < n:
+                    moves.append(("rec", 0, prof.recompute_extra))
+                    if prof.select_mem is not None or prof.moe_select_mem is not None:
+                        moves.append(("sel", 0, prof.select_extra))
+                if sel[c][s] > 0:
+                    moves.append(("rec", -1, prof.recompute_extra - prof.select_extra))   # upgrade a selected layer
+                for kind, dsel, extra in moves:
+                    rec[c][s] += kind == "rec"
+                    sel[c][s] += (kind == "sel") + dsel
+                    saved = peak_mem[s] - _stage_memory(layers, rec, res.peak_live, prof, S, V, dense, sel)[s]
+                    rec[c][s] -= kind == "rec"
+                    sel[c][s] -= (kind == "sel") + dsel
+                    score = saved / max(extra * avg_fw, 1e-9)
+                    if saved > 1e-9 and score > best_score:
+                        best_move, best_score = (c, kind, dsel), score
+            if best_move is None:
                 break
-            c, _ = max(cands, key=lambda cs: layers[cs[0]][cs[1]] - rec[cs[0]][cs[1]])
-            rec[c][s] += 1
-            peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V)
-        fwd, bwd = _slot_times(dense, moe, rec, prof, S, V)
+            c, kind, dsel = best_move
+            rec[c][s] += kind == "rec"
+            sel[c][s] += (kind == "sel") + dsel
+            peak_mem = _stage_memory(layers, rec, res.peak_live, prof, S, V, dense, sel)
+        fwd, bwd = _slot_times(dense, moe, rec, prof, S, V, sel)
         res = simulate(order, fwd, bwd, S, p2p)
     offset = [[layers[c][s] - even[c * S + s] for s in range(S)] for c in range(V)]
-    return BalanceResult(layers, dense, rec, res.makespan, res.bubble_ratio, peak_mem, offset)
+    return BalanceResult(layers, dense, rec, res.makespan, res.bubble_ratio, peak_mem, offset, sel)
 
 
-def _stage_memory(layers, rec, peak_live, prof: LayerProfile, S: int, V: int) -> List[float]:
+def _stage_memory(layers, rec, peak_live, prof: LayerProfile, S: int, V: int, dense=None, sel=None) -> List[float]:
+    """Peak MB of every stage: static part (per stage, per layer by type, the head on the last stage)
+    plus the activations of the live micro-batches.  ``dense[c][s]`` of the ``layers[c][s]`` layers
+    are dense (all of them when not given); ``rec`` / ``sel`` of them are fully / selectively
+    recomputed -- MoE layers first, their activations being the larger ones."""
     out = []
+    act_d, rec_d, sel_d, lay_d = prof.mem_of(False)
+    act_m, rec_m, sel_m, lay_m = prof.mem_of(True)
+    sel_d = act_d if sel_d is None else sel_d
+    sel_m = act_m if sel_m is None else sel_m
     for s in range(S):
-        n = sum(layers[c][s] for c in range(V))
-        r = sum(rec[c][s] for c in range(V))
         live = max(peak_live[s], 1) / max(V, 1)
-        act = ((n - r) * prof.act_mem + r * prof.recomp_mem) * live
-        static = prof.static_mem + n * prof.layer_mem + (prof.lm_head_mem if s == S - 1 else 0.0)
-        out.append(static + act)
+        static = prof.static_mem0 if (s == 0 and prof.static_mem0 is not None) else prof.static_mem
+        if s == S - 1:
+            static += prof.lm_head_mem
+        act = 0.0
+        for c in range(V):
+            n = layers[c][s]
+            d = n if dense is None else dense[c][s]
+            m = n - d
+            r = rec[c][s]
+            q = sel[c][s] if sel is not None else 0
+            r_m = min(r, m)
+            r_d = r - r_m
+            q_m = min(q, m - r_m)
+            q_d = q - q_m
+            static += d * lay_d + m * lay_m
+            act += ((d - r_d - q_d) * act_d + r_d * rec_d + q_d * sel_d +
+                    (m - r_m - q_m) * act_m + r_m * rec_m + q_m * sel_m)
+        out.append(static + act * live)
     return out
 
 

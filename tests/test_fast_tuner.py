@@ -274,3 +274,41 @@ def test_grey_box_prune_reproduces_the_reference_unit_test_count():
     out = grey_box_memory_prune(ModelSpec(expert_num=256, world_size=1024), info, [4, 8], 64, max_mem_mib=55 * 1024)
     assert len(out) == 10 and all(len(r) == 5 and r[3] <= 64 and r[4] <= 55 * 1024 for r in out)
     assert [4, 8, 32, 8, 54686] in out            # a measured point that fits is returned as measured
+
+
+def test_balancer_two_layer_types_selective_recompute_and_per_stage_limits():
+    """Memory table in the reference's terms (pipeline_conductor/memory.py): dense and MoE layers with
+    their own activation / recompute / selective / weight sizes, a heavier first stage, the head on the
+    last, one limit for stage 0, one for the middle stages, one for the last."""
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pipeline_balance import _stage_memory
+    prof = LayerProfile(dense_fw=0.4, dense_bw=0.74, moe_fw=1.0, moe_bw=1.84, head_fw=1.5, head_bw=2.76,
+                        recompute_extra=1.0, select_extra=0.25,
+                        act_mem=479.0, recomp_mem=30.0, select_mem=400.0, layer_mem=866.0,
+                        moe_act_mem=765.0, moe_recomp_mem=30.0, moe_select_mem=500.0, moe_layer_mem=2600.0,
+                        static_mem0=3383.0, static_mem=2382.0, lm_head_mem=8675.0)
+    S, V, M, L, D = 4, 2, 8, 30, 3
+    free = balance_pipeline(L, D, S, V, M, prof)
+    assert sum(map(sum, free.layers)) == L and sum(map(sum, free.dense)) == D
+    assert not any(map(any, free.recompute)) and not any(map(any, free.select_recompute))
+    assert free.dense[0][0] >= 1 and sum(free.dense[1]) == 0               # dense layers lead the model
+    limits = [max(free.peak_mem) * 0.80] * S
+    limits[0] = free.peak_mem[0] * 0.85
+    limits[-1] = free.peak_mem[-1] * 0.9
+    tight = balance_pipeline(L, D, S, V, M, prof, mem_limit_mb=limits)
+    assert all(p <= l + 1e-6 for p, l in zip(tight.peak_mem, limits)), (tight.peak_mem, limits)
+    assert any(map(any, tight.select_recompute)) or any(map(any, tight.recompute))
+    assert tight.makespan > free.makespan                                   # recomputation costs time
+    for c in range(V):
+        for s in range(S):
+            assert tight.recompute[c][s] + tight.select_recompute[c][s] <= tight.layers[c][s]
+    # the reported peaks are those of the memory table
+    from hyper_parallel_b200.auto_parallel.fast_tuner.pp_simulator import compute_order, simulate
+    live = simulate(compute_order("vpp", M, S, V), [1.0] * (S * V), [2.0] * (S * V), S).peak_live
+    again = _stage_memory(tight.layers, tight.recompute, live, prof, S, V, tight.dense, tight.select_recompute)
+    assert all(abs(a - b) < 1e-6 for a, b in zip(again, tight.peak_mem))
+    # when only full recomputation exists it is used, and costs more time than the selective mix
+    full_only = balance_pipeline(L, D, S, V, M, LayerProfile(**{**prof.__dict__, "select_mem": None,
+                                                                "moe_select_mem": None}), mem_limit_mb=limits)
+    assert not any(map(any, full_only.select_recompute)) and any(map(any, full_only.recompute))
+    with pytest.raises(ValueError):
+        balance_pipeline(L, D, S, V, M, prof, mem_limit_mb=[1.0, 2.0])
