@@ -356,22 +356,29 @@ def _factory(fn, size, device_mesh, placements, **kwargs) -> DTensor:
     return DTensor._wrap(fn(compute_local_shape(size, layout), **kwargs), layout)
 
 
-def compute_local_shape(global_shape, layout: Layout) -> Tuple[int, ...]:
-    """This rank's shard shape of a tensor of ``global_shape`` under ``layout``, with ``torch.chunk``
-    semantics where a dimension does not divide evenly: chunks of ``ceil(n / parts)``, a shorter last
-    one, empty ones after it.  The factory functions use it (reference dtensor.py:334-369,
+def compute_local_shape_and_offset(global_shape, layout: Layout) -> Tuple[Tuple[int, ...], Tuple[int, ...]]:
+    """This rank's shard shape of a tensor of ``global_shape`` under ``layout`` and where the shard
+    starts in the global tensor, with ``torch.chunk`` semantics where a dimension does not divide
+    evenly: chunks of ``ceil(n / parts)``, a shorter last one, empty ones after it (their start is the
+    end of the data).  The factory functions use it (reference dtensor.py:334-369,
     ``compute_local_shape_and_global_offset``); the layout algebra itself (``shape``,
     redistribution) assumes even shards, as the reference's does."""
     from .random import local_shard_size_and_offset
     mesh = layout.mesh
     coord = mesh.get_coordinate()
-    out = []
+    shape, offset = [], []
     for d, n in enumerate(global_shape):
-        n = int(n)
+        n, start = int(n), 0
         for a in layout.dim_axes[d]:
-            n, _ = local_shard_size_and_offset(n, mesh.mesh_shape[a], coord[a])
-        out.append(n)
-    return tuple(out)
+            n, off = local_shard_size_and_offset(n, mesh.mesh_shape[a], coord[a])
+            start += off
+        shape.append(n)
+        offset.append(start)
+    return tuple(shape), tuple(offset)
+
+
+def compute_local_shape(global_shape, layout: Layout) -> Tuple[int, ...]:
+    return compute_local_shape_and_offset(global_shape, layout)[0]
 
 
 def ones(size, device_mesh=None, placements=None, **kwargs) -> DTensor:

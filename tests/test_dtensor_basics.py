@@ -90,6 +90,21 @@ def factory_empty(rank):
 
 
 @case
+def local_shape_and_offset_helper(rank):
+    from hyper_parallel_b200 import Replicate, Shard
+    from hyper_parallel_b200.core.utils import compute_local_shape_and_global_offset as f
+    mesh = _mesh((2, 4), ("dp", "tp"))
+    dp, tp = divmod(rank, 4)
+    assert f((8, 16), mesh, (Shard(0), Shard(1))) == ((4, 4), (dp * 4, tp * 4))
+    assert f((8, 16), mesh, (Replicate(), Shard(0))) == ((2, 16), (tp * 2, 0))
+    assert f((16, 3), mesh, (Shard(0), Shard(0))) == ((2, 3), (dp * 8 + tp * 2, 0))      # two axes on one dim
+    shape, off = f((10, 5), mesh, (Replicate(), Shard(0)))                                # 10 rows over 4: 3 3 3 1
+    assert shape == ((3, 5) if tp < 3 else (1, 5)) and off == (tp * 3, 0)
+    shape, off = f((2, 5), mesh, (Replicate(), Shard(0)))                                 # 2 rows over 4: 1 1 0 0
+    assert shape == ((1, 5) if tp < 2 else (0, 5)) and off == (min(tp, 2), 0)
+
+
+@case
 def numel_is_global(rank):
     from hyper_parallel_b200 import DTensor, Replicate, Shard
     mesh = _mesh((2, 4), ("dp", "tp"))
