@@ -149,6 +149,31 @@ def world_collective_groups(specs: Sequence[Tuple[Sequence[int], str]]) -> Dict[
     return mine
 
 
+def generate_groups_from_template(template: Sequence[int], world_size: int) -> List[List[int]]:
+    """The partition of ``range(world_size)`` into groups shaped like ``template``.
+
+    A mesh axis gives every rank a group that is an arithmetic progression ``base + i * step``
+    (``i < n``); all such groups together tile the world: blocks of ``n * step`` consecutive ranks,
+    ``step`` interleaved groups per block.  Given one of them the others follow -- what the reference
+    uses so that every process can take part in creating every group
+    (hyper_parallel/platform/torch/group_utils.py:47-140).  Raises if ``template`` is not an arithmetic
+    progression or does not tile ``world_size``."""
+    ranks = sorted(int(r) for r in template)
+    n = len(ranks)
+    if n == 0 or len(set(ranks)) != n:
+        raise ValueError(f"template {list(template)} must hold distinct ranks")
+    if n == 1:
+        return [[r] for r in range(world_size)]
+    step = ranks[1] - ranks[0]
+    if any(b - a != step for a, b in zip(ranks, ranks[1:])):
+        raise ValueError(f"template {ranks} is not an arithmetic progression")
+    block = n * step
+    if world_size % block or ranks[-1] >= world_size or (ranks[0] % block) >= step:
+        raise ValueError(f"template {ranks} does not tile a world of {world_size} ranks")
+    return [[start + off + i * step for i in range(n)]
+            for start in range(0, world_size, block) for off in range(step)]
+
+
 def split_group(parent_pg=None, split_ranks: Optional[Sequence[Sequence[int]]] = None, timeout=None,
                 pg_options=None, group_desc=None):
     """Create the sub-group of ``split_ranks`` that contains this rank (``None`` if none does).

@@ -125,3 +125,27 @@ def test_rng_tracker_shard_consistency():
     assert torch.equal(draws[0], draws[2]) and torch.equal(draws[1], draws[3])     # replicas agree
     assert not torch.equal(draws[0], draws[1])                                      # shards differ
     clear_mesh_cache()
+
+
+def test_groups_from_template_tile_the_world_like_mesh_axes():
+    from hyper_parallel_b200.collectives.cc import generate_groups_from_template as groups
+    assert groups([0, 1], 8) == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert groups([5, 7], 8) == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert groups([3], 4) == [[0], [1], [2], [3]]
+    # every axis of a mesh: the group of any one rank generates the groups of all ranks
+    shape = (2, 3, 4)
+    world = 24
+    for axis in range(3):
+        clear_mesh_cache()
+        per_rank = {}
+        for rank in range(world):
+            mesh = DeviceMesh("cpu", shape, mesh_dim_names=("a", "b", "c"), rank_list=range(world),
+                              _init_backend=False, _rank=rank)
+            per_rank[rank] = list(mesh.get_rank_list_along_axis(("a", "b", "c")[axis]))
+            clear_mesh_cache()
+        want = sorted({tuple(v) for v in per_rank.values()})
+        for rank in (0, 7, 23):
+            assert sorted(map(tuple, groups(per_rank[rank], world))) == want
+    for bad, world in (([0, 1, 3], 8), ([0, 2], 6), ([0, 0], 4), ([0, 4], 4)):
+        with pytest.raises(ValueError):
+            groups(bad, world)
