@@ -71,6 +71,15 @@ def test_save_4_ranks_layout_on_disk_then_load_4_and_2(tmp_path):
     run_distributed(_load_worker, 2, path, (2, 1))
 
 
+def test_save_8_ranks_4x2_then_load_on_4_and_on_8_with_another_mesh(tmp_path):
+    """The reference's resharding scenario (tests/torch/checkpoint/dcp_api.py: save on 8, load on 4)."""
+    path = str(tmp_path / "ckpt8")
+    run_distributed(_save_worker, 8, path, (4, 2), True)
+    assert all(os.path.exists(os.path.join(path, f"_rank{r}_.safetensors")) for r in range(8))
+    run_distributed(_load_worker, 4, path, (2, 2))
+    run_distributed(_load_worker, 8, path, (2, 4))
+
+
 def test_rank_local_metadata_without_collectives(tmp_path):
     path = str(tmp_path / "ckpt_local")
     run_distributed(_save_worker, 2, path, (1, 2), False)
