@@ -17,9 +17,16 @@ Behaviour follows hyper_parallel/core/shard/_op_dispatch.py:91-675 of the refere
 ``infer_layout_suffix`` selects what the rule receives in ``extra_args``:
 ``""`` the non-DTensor args; ``"WithShape"`` the same plus, appended, the list of
 input global shapes; ``"WithTupleExpand"`` expands a leading list/tuple of
-tensors into individual inputs (``cat``-like ops); ``"Reshape"`` and ``"Slice"``
-are aliases of ``"WithShape"`` (their rules rewrite the shape / index arguments
-from global to local through ``get_expand_impl``).
+tensors into individual inputs (``cat``-like ops).  ``"Reshape"`` and ``"Slice"``
+are the reference's two special forms (``_op_dispatch.py:372-417`` and ``:543-593``
+there): the rule of ``op(x, shape)`` receives ``[shape, global input shape]`` and
+returns ``(layout, local shape)``, the rule of ``op(x, begin, end)`` receives
+``[begin, end, global input shape]`` and returns ``(layout, local begin, local end)``;
+the op then runs as ``impl(local x, local shape)`` / ``impl(local x, begin, end)``.
+Rules written for the reference and registered with these suffixes work unchanged.
+This package's own reshape / slice rules set ``_with_shape_convention`` and are
+called in the ``"WithShape"`` form instead, which also serves ``view(*sizes)``,
+``flatten``, ``unflatten``, ``narrow``, ``select`` and ``__getitem__``.
 
 The cache key is a tuple of the input layouts' interned strings and the reprs of
 the scalar arguments, so a steady-state call costs one dict lookup.
@@ -53,6 +60,11 @@ _PASSTHROUGH = {
     "_foreach_reciprocal_", "_foreach_neg_", "_foreach_sqrt_", "_fused_adamw_", "_fused_adam_",
     "_fused_sgd_", "is_grads_batched", "_has_compatible_shallow_copy_type",
 }
+
+
+def _plain(a):
+    """torch.Size / nested lists as plain tuples (hashable, printable the same on every rank)."""
+    return tuple(_plain(i) for i in a) if isinstance(a, (list, tuple)) else a
 
 
 def get_op_name(func) -> str:
@@ -177,6 +189,8 @@ class OpDispatcher:
         if suffix == "WithTupleExpand" and args and isinstance(args[0], (list, tuple)):
             return self._dispatch_tuple_expand(func, name, rule, args, kwargs)
 
+        if suffix in ("Reshape", "Slice") and not getattr(rule, "_with_shape_convention", False):
+            return self._dispatch_reference_form(func, name, rule, suffix, args, kwargs)
         with_shape = suffix in ("WithShape", "Reshape", "Slice")
         layouts: List[Optional[Layout]] = []
         extra: List[Any] = []
@@ -236,6 +250,35 @@ class OpDispatcher:
         out_layout, impl = plan
         result = impl(*local_args, **local_kwargs)
         return self._wrap_outputs(result, out_layout)
+
+    def _dispatch_reference_form(self, func, name, rule, suffix, args, kwargs):
+        """``Reshape``: ``op(x, shape)``; ``Slice``: ``op(x, begin, end)`` -- the argument lists and
+        return tuples of the reference (see the module docstring)."""
+        n_extra = 1 if suffix == "Reshape" else 2
+        if kwargs or len(args) != 1 + n_extra or not isinstance(args[0], DTensor):
+            raise TypeError(f"{name}: the {suffix!r} calling convention takes (DTensor, "
+                            + ("shape)" if suffix == "Reshape" else "begin, end)") + " positionally")
+        x = args[0]
+        lay = x._layout
+        global_shape = tuple(lay.get_global_shape(x._local_tensor.shape))
+        extra = [_plain(a) for a in args[1:]] + [global_shape]
+        key = (name, suffix, lay.compact_str) + tuple(_key_of(e) for e in extra)
+        try:
+            plan = self._cache.get(key)
+        except TypeError:
+            key, plan = None, None
+        if plan is None:
+            inferred = rule.infer_layout([lay], extra)
+            if not isinstance(inferred, (tuple, list)) or len(inferred) != 1 + n_extra:
+                raise TypeError(f"{name}: a {suffix!r} rule must return (layout, "
+                                + ("local_shape)" if suffix == "Reshape" else "begin, end)"))
+            impl = rule.get_expand_impl(func, inferred, [lay], extra) or func
+            plan = (inferred, impl)
+            if key is not None:
+                self._cache[key] = plan
+        inferred, impl = plan
+        result = impl(x._local_tensor, *inferred[1:])
+        return DTensor(result, inferred[0]) if isinstance(result, torch.Tensor) else result
 
     def _dispatch_tuple_expand(self, func, name, rule, args, kwargs):
         seq = args[0]

@@ -97,6 +97,8 @@ def infer_reshape(op_name, layout, in_shape: Sequence[int], target: Sequence[int
 
 
 class ReshapeDistributedOp(DistributedOp):
+    _with_shape_convention = True     # called in the "WithShape" form although registered as "Reshape"
+
     def _target(self, extra, in_shape):
         if self.op_name == "flatten":
             ints = [a for a in extra if isinstance(a, int) and not isinstance(a, bool)]

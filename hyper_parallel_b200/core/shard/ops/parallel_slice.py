@@ -10,6 +10,8 @@ from .parallel_ops import DistributedOp
 
 
 class SliceDistributedOp(DistributedOp):
+    _with_shape_convention = True     # called in the "WithShape" form although registered as "Slice"
+
     _allow_partial_inputs = True
 
     def infer_layout(self, layouts, extra_args):

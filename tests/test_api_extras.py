@@ -2,6 +2,7 @@
 environment, DeviceMesh.from_group / flatten, and tied parameters across pipeline stages."""
 import os
 
+import pytest
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -63,6 +64,32 @@ def _custom_op_worker(rank, world):
     assert tuple(out.alias_tensor_map) == ("None", "dp", "None")
     # the built-in catalogue is still there
     assert get_distributed_op("matmul") is not None
+
+    # rules written for the reference's "Reshape" and "Slice" calling conventions run unchanged:
+    # [shape, global shape] -> (layout, local shape); [begin, end, global shape] -> (layout, begin, end)
+    def fold_rows(x, shape):
+        return x.reshape(shape)
+
+    def window(x, begin, end):
+        return x[tuple(slice(b, e) for b, e in zip(begin, end))]
+
+    full = torch.arange(4 * 6 * 2.0).reshape(4, 6, 2)
+    d = hp.distribute_tensor(full, lay("dp", "None", "None"))
+    disp = _op_dispatch._OP_DISPATCHER
+    for _ in range(2):                                       # the second call comes from the plan cache
+        y = disp.dispatch(fold_rows, (d, (4, 12)), {})
+        assert isinstance(y, hp.DTensor) and tuple(y.shape) == (4, 12) and y.to_local().shape == (2, 12)
+        assert torch.equal(y.full_tensor(), full.reshape(4, 12))
+        z = disp.dispatch(window, (d, (0, 1, 0), (4, 5, 1)), {})
+        assert tuple(z.shape) == (4, 4, 1) and z.to_local().shape == (2, 4, 1)
+        assert torch.equal(z.full_tensor(), full[:, 1:5, :1])
+    with pytest.raises(ValueError):
+        disp.dispatch(window, (d, (1, 0, 0), (4, 6, 2)), {})      # a sharded dim cut short
+    with pytest.raises(TypeError):
+        disp.dispatch(fold_rows, (d,), {"shape": (4, 12)})        # the form is positional
+    # the package's own reshape / slice keep serving every spelling of those ops
+    assert tuple(d.view(4, 12).shape) == (4, 12) and tuple(d.flatten(1).to_local().shape) == (2, 12)
+    assert tuple(d[:, 2:4].shape) == (4, 2, 2) and tuple(d.narrow(1, 0, 3).to_local().shape) == (2, 3, 2)
 
 
 def test_custom_distributed_op_registration_through_the_environment():
