@@ -62,6 +62,25 @@ _PASSTHROUGH = {
 }
 
 
+# Where the reference keeps a rule class in a file of another name (or under another class name), so
+# that a YAML entry written against the reference's catalogue -- an own op mapped onto a stock rule --
+# resolves here too.  Keys: the reference's ``distributed_op_file`` / ``distributed_op_class``.
+_AXIS_OPS_FILES = ("parallel_activation_with_axis", "parallel_concat", "parallel_cumsum", "parallel_gather",
+                   "parallel_isin", "parallel_masked_scatter", "parallel_multinomial", "parallel_new_ones",
+                   "parallel_one_hot_ext", "parallel_pad", "parallel_repeat_interleave", "parallel_scatter",
+                   "parallel_scatter_update", "parallel_sort", "parallel_split", "parallel_topk", "parallel_unbind")
+_FILE_ALIASES = {**{f: "parallel_axis_ops" for f in _AXIS_OPS_FILES},
+                 "parallel_argmax_with_value_ops": "parallel_reduce",
+                 "parallel_tuple_elementwise": "parallel_elementwise",
+                 "parallel_npu_flash_attention_score": "parallel_flash_attention_score",
+                 "parallel_ms_flash_attention_score": "parallel_flash_attention_score",
+                 "parallel_slice_ext": "parallel_slice"}
+_CLASS_ALIASES = {"GatherNdDistributedOp": "GatherDistributedOp", "ScatterUpdateDistributedOp": "ScatterDistributedOp",
+                  "SliceExtDistributedOp": "SliceDistributedOp", "SplitTensorDistributedOp": "SplitDistributedOp",
+                  "SplitTensorViewDistributedOp": "SplitDistributedOp", "SplitWithSizeDistributedOp": "SplitDistributedOp",
+                  "SplitWithSizeViewDistributedOp": "SplitDistributedOp"}
+
+
 def _plain(a):
     """torch.Size / nested lists as plain tuples (hashable, printable the same on every rank)."""
     return tuple(_plain(i) for i in a) if isinstance(a, (list, tuple)) else a
@@ -163,9 +182,16 @@ class OpDispatcher:
             try:
                 module = importlib.import_module(f"{__package__}.ops.{mod_file}")
             except ImportError:
-                if not self._env_python_path:
-                    raise
-                module = importlib.import_module(mod_file)
+                try:
+                    if not self._env_python_path:
+                        raise
+                    module = importlib.import_module(mod_file)
+                except ImportError:
+                    if mod_file not in _FILE_ALIASES:
+                        raise
+                    module = importlib.import_module(f"{__package__}.ops.{_FILE_ALIASES[mod_file]}")
+        if not hasattr(module, cls_name) and cls_name in _CLASS_ALIASES:
+            cls_name = _CLASS_ALIASES[cls_name]
         getattr(module, cls_name)(op_name)
         self._suffix[op_name] = cfg.get("infer_layout_suffix", "") or ""
 

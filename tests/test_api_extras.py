@@ -87,6 +87,9 @@ def _custom_op_worker(rank, world):
         disp.dispatch(window, (d, (1, 0, 0), (4, 6, 2)), {})      # a sharded dim cut short
     with pytest.raises(TypeError):
         disp.dispatch(fold_rows, (d,), {"shape": (4, 12)})        # the form is positional
+    # entries that name a stock rule by the reference's file / class names resolve to this package's rules
+    assert type(get_distributed_op("my_topk")).__name__ == "TopKDistributedOp"
+    assert type(get_distributed_op("my_split_view")).__name__ == "SplitDistributedOp"
     # the package's own reshape / slice keep serving every spelling of those ops
     assert tuple(d.view(4, 12).shape) == (4, 12) and tuple(d.flatten(1).to_local().shape) == (2, 12)
     assert tuple(d[:, 2:4].shape) == (4, 2, 2) and tuple(d.narrow(1, 0, 3).to_local().shape) == (2, 3, 2)
