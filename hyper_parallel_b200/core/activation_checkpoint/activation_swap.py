@@ -2,12 +2,25 @@
 (hyper_parallel/platform/torch/activation_checkpoint/activation_swap.py:54-192)."""
 from __future__ import annotations
 
+import enum
 from typing import Callable, Optional
 
 import torch
 from torch import nn
 
 from .swap import Storage, SwapManager, SwapTensor
+
+
+class ActivationPolicy(enum.Enum):
+    """What a ``policy_fn(tensor)`` may answer (reference activation_swap.py:35-38): keep the
+    activation on the device, or swap it to the host.  A plain ``bool`` is accepted too
+    (``True`` = swap)."""
+    SAVE = 0
+    SWAP = 1
+
+
+def _wants_swap(answer) -> bool:
+    return answer is ActivationPolicy.SWAP if isinstance(answer, ActivationPolicy) else bool(answer)
 
 
 class AsyncSaveOnCpu(torch.autograd.graph.saved_tensors_hooks):
@@ -23,7 +36,7 @@ class AsyncSaveOnCpu(torch.autograd.graph.saved_tensors_hooks):
         def pack(t: torch.Tensor):
             if not isinstance(t, torch.Tensor) or t.numel() < min_numel or isinstance(t, nn.Parameter):
                 return t
-            if policy_fn is not None and not policy_fn(t):
+            if policy_fn is not None and not _wants_swap(policy_fn(t)):
                 return t
             st = SwapTensor(t, pin_memory=pin_memory)
             if managed and mgr.current is not None:

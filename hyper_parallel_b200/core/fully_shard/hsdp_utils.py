@@ -1,0 +1,13 @@
+"""State names of a ``fully_shard`` parameter, under the reference's module path
+(hyper_parallel/core/fully_shard/hsdp_utils.py:76-83)."""
+import enum
+
+
+class ShardedState(enum.Enum):
+    """``FSDPParam.sharded_state``: the module holds the DTensor shard (``SHARDED``), or the gathered
+    full tensor (``UNSHARDED``).  ``SHARDED_POST_FORWARD`` (a differently sharded copy kept between
+    forward and backward) is named for completeness; this implementation always reshards to the
+    original shard."""
+    SHARDED = enum.auto()
+    SHARDED_POST_FORWARD = enum.auto()
+    UNSHARDED = enum.auto()

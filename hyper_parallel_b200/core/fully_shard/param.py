@@ -74,6 +74,11 @@ class FSDPParam:
             mod._parameters[name] = p
 
     @property
+    def sharded_state(self):
+        from .hsdp_utils import ShardedState
+        return ShardedState.SHARDED if self.is_sharded else ShardedState.UNSHARDED
+
+    @property
     def sharded_local(self) -> torch.Tensor:
         return self.sharded_param._local_tensor
 

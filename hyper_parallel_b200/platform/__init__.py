@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from .collectives import cc
+from ..collectives import cc
 
 
 class TorchPlatform:
@@ -19,7 +19,7 @@ class TorchPlatform:
 
     @property
     def DTensorBase(self):
-        from .core.dtensor import DTensor
+        from ..core.dtensor import DTensor
         return DTensor
 
     # rank / world ---------------------------------------------------------
@@ -59,7 +59,7 @@ class TorchPlatform:
 
     @staticmethod
     def get_op_name(func):
-        from .core.shard._op_dispatch import get_op_name
+        from ..core.shard._op_dispatch import get_op_name
         return get_op_name(func)
 
 

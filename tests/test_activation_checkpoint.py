@@ -107,3 +107,26 @@ def test_swap_tensor_state_machine():
         b = (a * a).sum()
     b.backward()
     assert torch.allclose(a.grad, 2 * a)
+
+
+def test_swap_policy_may_answer_with_the_enum_or_a_bool():
+    """A ``policy_fn`` written for the reference answers ``ActivationPolicy.SAVE`` / ``SWAP``; a plain
+    bool keeps working.  Import paths of the reference's torch backend resolve too."""
+    from hyper_parallel_b200.platform.torch.activation_checkpoint import ActivationPolicy, swap_wrapper
+    from hyper_parallel_b200.platform.torch.fully_shard.utils import CPUOffloadPolicy, MixedPrecisionPolicy, OffloadPolicy
+    from hyper_parallel_b200.platform.platform import get_torch_platform
+    from hyper_parallel_b200.core.activation_checkpoint.activation_swap import _wants_swap
+    assert _wants_swap(ActivationPolicy.SWAP) and not _wants_swap(ActivationPolicy.SAVE)
+    assert _wants_swap(True) and not _wants_swap(False)
+    assert issubclass(CPUOffloadPolicy, OffloadPolicy) and MixedPrecisionPolicy().cast_forward_inputs
+    assert get_torch_platform().get_world_size() == 1
+    seen = []
+
+    def policy(t):
+        seen.append(tuple(t.shape))
+        return ActivationPolicy.SAVE                      # nothing is swapped, so CPU tensors are fine
+
+    net = swap_wrapper(torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.GELU(), torch.nn.Linear(64, 64)), policy)
+    x = torch.randn(32, 64, requires_grad=True)
+    net(x).sum().backward()
+    assert seen and x.grad is not None

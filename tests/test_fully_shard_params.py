@@ -64,6 +64,8 @@ def _param_worker(rank, world, case):
     for _ in range(2):
         net.unshard()
     assert not fp.is_sharded and not isinstance(net.l1.weight, DTensor)
+    from hyper_parallel_b200.core.fully_shard.hsdp_utils import ShardedState
+    assert fp.sharded_state is ShardedState.UNSHARDED
     assert tuple(net.l1.weight.shape) == tuple(ref.l1.weight.shape)
     if case == "mp":
         assert net.l1.weight.dtype == torch.bfloat16 and fp.sharded_local.dtype == torch.float32
@@ -73,6 +75,7 @@ def _param_worker(rank, world, case):
     net.reshard()
     net.reshard()
     assert fp.is_sharded and fp.unsharded_param.numel() == 0 and isinstance(net.l1.weight, DTensor)
+    assert fp.sharded_state is ShardedState.SHARDED
 
     # asynchronous unshard (the prefetch path): the handle's wait completes the transition
     h = net.unshard(async_op=True)
