@@ -74,6 +74,46 @@ def _round4(n: int) -> int:
     return (n + 3) // 4 * 4
 
 
+# The three helpers below carry the names and argument lists of the reference's module-level
+# functions (random.py:300-375 there); code that computes expected offsets with them keeps working.
+def _calc_shard_info(mesh_coordinate, device_mesh, placements):
+    """Per tensor dim: the index of this rank's shard and the number of shards, from the rank's mesh
+    coordinate.  Several mesh dims sharding one tensor dim combine outer-to-inner.  Entries of
+    ``placements`` that are not ``Shard`` count as replication."""
+    from .placement_types import Shard
+    mesh_shape = tuple(device_mesh.mesh_shape)
+    by_dim = {}
+    for i, p in enumerate(placements):
+        if isinstance(p, Shard):
+            by_dim.setdefault(p.dim, []).append(i)
+    ndim = max([len(mesh_shape)] + [d + 1 for d in by_dim])
+    idx, total = [0] * ndim, [1] * ndim
+    for d, mesh_dims in by_dim.items():
+        for m in mesh_dims:
+            idx[d] = idx[d] * mesh_shape[m] + int(mesh_coordinate[m])
+            total[d] *= mesh_shape[m]
+    return idx, total
+
+
+def _calc_shard_linear_idx(shard_coord, shard_size) -> int:
+    """Row-major index of a shard coordinate."""
+    lin = 0
+    for c, n in zip(shard_coord, shard_size):
+        lin = lin * int(n) + int(c)
+    return lin
+
+
+def _calc_first_shard_size(device_mesh, placements, global_shape):
+    """Shape of the first (largest) shard: every sharded dim divided, rounding up, by the sizes of the
+    mesh dims that shard it."""
+    from .placement_types import Shard
+    size = [int(g) for g in global_shape]
+    for i, p in enumerate(placements):
+        if isinstance(p, Shard) and p.dim < len(size):
+            size[p.dim] = -(-size[p.dim] // int(device_mesh.mesh_shape[i]))
+    return size
+
+
 class OffsetBasedRNGTracker:
     def __init__(self, device: Optional[torch.device] = None, run_state_sync: bool = True, seed: int = 0):
         self.device = torch.device(device) if device is not None else (
@@ -102,6 +142,33 @@ class OffsetBasedRNGTracker:
         self._seed, self._offset = int(seed), 0
 
     _manual_seed = manual_seed          # the reference's spelling (random.py:119)
+
+    @property
+    def _device_handle(self):
+        """The module that owns the generator the tracker drives (``torch.cuda`` or ``torch``)."""
+        return torch.cuda if self.is_cuda else torch
+
+    def _get_device_state(self) -> torch.Tensor:
+        """The tracker's ``(seed, offset)`` as the 16 bytes of a Philox generator state, readable
+        through :class:`_PhiloxState` on CPU too."""
+        return torch.tensor([self._seed, self._offset], dtype=torch.int64).view(torch.uint8)
+
+    def _set_pre_op_offset(self, state: _PhiloxState, device_mesh, placements, global_shape) -> None:
+        """Advance ``state.offset`` to the window of this rank's shard (reference random.py:198-270)."""
+        idx, total = _calc_shard_info(device_mesh.get_coordinate(), device_mesh, placements)
+        numel = 1
+        for n in _calc_first_shard_size(device_mesh, placements, global_shape):
+            numel *= n
+        state.offset = state.offset + _round4(_calc_shard_linear_idx(idx, total) * numel)
+
+    def _set_post_op_offset(self, state: _PhiloxState, global_shape, old_offset: int) -> None:
+        """Put ``state.offset`` past the whole tensor (reference random.py:272-292; a device mesh may be
+        passed where the reference passes one: its shape is then what is counted, as there)."""
+        shape = getattr(global_shape, "mesh_shape", global_shape)
+        numel = 1
+        for n in shape:
+            numel *= int(n)
+        state.offset = int(old_offset) + _round4(numel)
 
     @property
     def distribute_region_enabled(self) -> bool:

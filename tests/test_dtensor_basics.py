@@ -269,6 +269,32 @@ def rng_offsets_on_a_two_axis_mesh(rank):
 
 
 @case
+def rng_offset_helpers_under_the_reference_names(rank):
+    """Expected offsets computed with the module-level helpers equal what the tracker sets."""
+    from hyper_parallel_b200 import Replicate, Shard
+    from hyper_parallel_b200.core.random import (OffsetBasedRNGTracker, _PhiloxState, _calc_first_shard_size,
+                                                 _calc_shard_info, _calc_shard_linear_idx)
+    mesh = _mesh((2, 4), ("dp", "tp"))
+    dp, tp = divmod(rank, 4)
+    tr = OffsetBasedRNGTracker(device="cpu", run_state_sync=False)
+    tr._manual_seed(42)
+    assert tr._device_handle is torch
+    for placements, lin, first in (([Shard(0), Shard(1)], dp * 4 + tp, [4, 2]), ([Shard(0), Replicate()], dp * 8, [4, 8]),
+                                   ([Replicate(), Shard(1)], tp, [8, 2]), ([Shard(1), Shard(1)], (dp * 4 + tp), [8, 1])):
+        idx, total = _calc_shard_info(mesh.get_coordinate(), mesh, placements)
+        assert _calc_first_shard_size(mesh, placements, (8, 8)) == first
+        state = _PhiloxState(tr._get_device_state())
+        assert state.seed == 42 and state.offset == 0
+        tr._set_pre_op_offset(state, mesh, placements, (8, 8))
+        numel = first[0] * first[1]
+        assert state.offset == (_calc_shard_linear_idx(idx, total) * numel + 3) // 4 * 4
+        if placements[1] != Replicate():
+            assert _calc_shard_linear_idx(idx, total) == lin
+        tr._set_post_op_offset(state, (8, 8), 100)
+        assert state.offset == 164
+
+
+@case
 def rng_replicated_draws_agree_whatever_the_local_seed(rank):
     import torch.distributed as dist
     from hyper_parallel_b200 import DTensor, Replicate
