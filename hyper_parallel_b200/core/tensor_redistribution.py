@@ -27,11 +27,17 @@ from .layout import Layout
 Step = tuple
 
 
+class MeshMismatchError(RuntimeError, ValueError):
+    """Redistribution between two different device meshes.  The reference raises ``RuntimeError``
+    here (tests/torch/shard/redistribute.py:84-115); earlier callers of this package caught
+    ``ValueError``: the class is both."""
+
+
 def plan_redistribution(src: Layout, dst: Layout) -> List[Step]:
     """Pure planning: the list of steps that turns ``src`` into ``dst`` (same mesh)."""
     if src.mesh != dst.mesh:
-        raise ValueError("redistribute between different device meshes is not supported: "
-                         f"{src.mesh} vs {dst.mesh}")
+        raise MeshMismatchError("redistribute between different device meshes is not supported: "
+                                f"{src.mesh} vs {dst.mesh}")
     if len(src.dim_axes) != len(dst.dim_axes):
         raise ValueError("source and target layouts describe tensors of different rank")
     cur = [list(a) for a in src.dim_axes]
