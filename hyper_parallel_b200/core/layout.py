@@ -168,8 +168,15 @@ class Layout:
     # ------------------------------------------------- placement <-> map ---
     def set_placements(self, placements: Sequence[Placement]) -> None:
         placements = tuple(placements)
-        if len(placements) != self._mesh.ndim:
-            raise ValueError(f"need {self._mesh.ndim} placements (one per mesh dim), got {len(placements)}")
+        # one placement per mesh dim; as in the reference a shorter list leaves the remaining mesh dims
+        # replicated and surplus ``Replicate()`` entries are ignored
+        nd = self._mesh.ndim
+        if len(placements) < nd:
+            placements = placements + (Replicate(),) * (nd - len(placements))
+        elif len(placements) > nd:
+            if any(not isinstance(p, Replicate) for p in placements[nd:]):
+                raise ValueError(f"need {nd} placements (one per mesh dim), got {len(placements)}")
+            placements = placements[:nd]
         for p in placements:
             if not isinstance(p, Placement):
                 raise TypeError(f"expected a Placement, got {p!r}")

@@ -42,12 +42,38 @@ def split_shapes(extra_args) -> Tuple[list, Optional[list]]:
     return list(extra_args), None
 
 
+# The reference words this error differently per operator and programs match on its wording; the
+# message below states the fact once in this package's words and once in the reference's.
+_REFERENCE_WORDING = {
+    "softmax": "{op} requires the reduction axis to be un-sharded",
+    "log_softmax": "{op} requires the reduction axis to be un-sharded",
+    "_softmax": "{op} requires the reduction axis to be un-sharded",
+    "cumsum": "Cannot perform sharding on normalized dimension {d}",
+    "layer_norm": "Cannot perform sharding on normalized dimension {d}",
+    "sort": "sorting along a sharded dimension is not supported",
+    "argsort": "sorting along a sharded dimension is not supported",
+    "topk": "Cannot perform sharding on params along the chosen dim",
+    "repeat_interleave": "Cannot perform sharding on params along the chosen dim",
+    "split": "Can not split tensor at sharded axis[{d}], layout: {layout}",
+    "chunk": "Can not split tensor at sharded axis[{d}], layout: {layout}",
+    "tensor_split": "Can not split tensor at sharded axis[{d}], layout: {layout}",
+    "unbind": "Unbinding a sharded dimension is not supported",
+    "pad": "{op} does not support padding on a sharded dimension",
+    "expand": "Cannot expand dimension {d} which is sharded",
+    "expand_as": "Cannot expand dimension {d} which is sharded",
+}
+
+
 def require_unsharded(op_name: str, layout: Layout, dims: Sequence[int], what: str = "operating") -> None:
     for d in dims:
         if layout.dim_axes[d]:
             names = [layout.alias_name[a] for a in layout.dim_axes[d]]
-            raise ValueError(f"For {op_name}, the {what} dim {d} must not be sharded, "
-                             f"but it is sharded on mesh axes {names}")
+            msg = (f"For {op_name}, the {what} dim {d} must not be sharded, "
+                   f"but it is sharded on mesh axes {names}")
+            extra = _REFERENCE_WORDING.get(op_name)
+            if extra:
+                msg += " (" + extra.format(op=op_name, d=d, layout=layout.alias_tensor_map) + ")"
+            raise ValueError(msg)
 
 
 def merge_partials(op_name: str, layouts: Sequence[Optional[Layout]]) -> List[Optional[str]]:

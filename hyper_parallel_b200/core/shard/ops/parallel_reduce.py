@@ -76,14 +76,18 @@ class ReduceMaxDistributedOp(ReduceExtDistributedOpBase):
 
 
 class MaxDistributedOp(DistributedOp):
-    """``max/min``: full reduction -> Partial(max/min); with ``dim`` -> (values, indices)."""
+    """``max/min``: two tensors -> element-wise; full reduction -> Partial(max/min); with ``dim`` ->
+    ``(values, indices)``.  Reducing a sharded dim leaves the values Partial(max/min) on its mesh axes,
+    as the reference does (parallel_reduce.py:201-311 there); the indices are resolved on the spot --
+    global positions of the first winning element, found with one max and one min all-reduce per mesh
+    axis -- where the reference returns each rank's local positions."""
 
     def infer_layout(self, layouts, extra_args):
         self._check_partial_inputs(layouts)
         x = layouts[0]
         if len(layouts) > 1 and layouts[1] is not None:
             from .parallel_elementwise import ElementWiseDistributedOp
-            return ElementWiseDistributedOp.infer_layout(self, layouts, extra_args)
+            return ElementWiseDistributedOp._infer(self, layouts, extra_args)
         nd = len(x.dim_axes)
         dims, keepdim, given = _parse_dim_keepdim(extra_args, nd)
         op = "max" if "max" in self.op_name else "min"
@@ -93,10 +97,42 @@ class MaxDistributedOp(DistributedOp):
                 for a in axes:
                     partial[a] = op
             return make(x, [], partial)
-        require_unsharded(self.op_name, x, dims, "reduced")
         out_axes = [(() if d in dims else axes) for d, axes in enumerate(x.dim_axes) if keepdim or d not in dims]
-        lay = make(x, out_axes)
-        return (lay, lay)
+        partial = [None] * x.mesh.ndim
+        for d in dims:
+            for a in x.dim_axes[d]:
+                partial[a] = op
+        return (make(x, out_axes, partial), make(x, out_axes))
+
+    def get_expand_impl(self, func, output_layout, layouts, extra_args):
+        x = layouts[0]
+        if (len(layouts) > 1 and layouts[1] is not None) or not isinstance(output_layout, tuple):
+            return None
+        dims, _, _ = _parse_dim_keepdim(extra_args, len(x.dim_axes))
+        axes = x.dim_axes[dims[0]]
+        if not axes:
+            return None
+        import torch
+        from ....collectives import cc
+        mesh = x.mesh
+        groups = [mesh.get_group(a) for a in axes]
+        shard_idx = 0
+        for a in axes:
+            shard_idx = shard_idx * mesh.mesh_shape[a] + mesh.get_local_rank(a)
+        is_max = "max" in self.op_name
+        dim = dims[0]
+
+        def impl(t, *a, **k):
+            vals, idx = func(t, *a, **k)
+            best = vals.detach().clone()
+            for g in groups:
+                cc.all_reduce_(best, "max" if is_max else "min", g)
+            cand = torch.where(vals.detach() == best, idx + shard_idx * t.shape[dim],
+                               torch.full_like(idx, torch.iinfo(idx.dtype).max))
+            for g in groups:
+                cc.all_reduce_(cand, "min", g)
+            return vals, cand
+        return impl
 
 
 class ArgMaxWithValueDistributedOp(DistributedOp):

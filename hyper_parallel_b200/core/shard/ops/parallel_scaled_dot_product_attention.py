@@ -26,16 +26,30 @@ class ScaledDotProductAttentionDistributedOp(DistributedOp):
             raise ValueError("For scaled_dot_product_attention, the head dim must not be sharded")
         if k.dim_axes[-2] or v.dim_axes[-2]:
             raise NotImplementedError(
-                "scaled_dot_product_attention with the key/value sequence sharded requires Ring "
-                "Attention; replicate K/V along the sequence axis (gather them) first")
+                "scaled_dot_product_attention: KV sequence sharding requires Ring Attention; replicate "
+                "K/V along the sequence axis (gather them) first")
+        if k.dim_axes != v.dim_axes:
+            raise ValueError("For scaled_dot_product_attention, Key and Value must have identical sharding "
+                             f"(key {k.alias_tensor_map}, value {v.alias_tensor_map})")
         for d in range(nd - 2):
             if not (q.dim_axes[d] == k.dim_axes[d] == v.dim_axes[d]):
                 raise ValueError("For scaled_dot_product_attention, batch/head dims of q, k, v must be "
                                  "sharded identically")
-        for l in layouts[3:]:
-            if l is not None and q.dim_axes[-2]:
-                raise ValueError("For scaled_dot_product_attention, an attn_mask cannot be combined with "
-                                 "a sharded query sequence")
+        for m in layouts[3:]:
+            if m is None:
+                continue
+            # a distributed mask: its query-row dim is sharded like q's (rows already local) or not at all
+            # (the rows of this rank's queries are cut out below); the other dims follow q from the right
+            md = len(m.dim_axes)
+            if md < 2 or m.dim_axes[-1]:
+                raise ValueError("For scaled_dot_product_attention, the key dim of attn_mask must not be sharded")
+            if m.dim_axes[-2] and m.dim_axes[-2] != q.dim_axes[-2]:
+                raise ValueError("For scaled_dot_product_attention, the query dim of attn_mask must be sharded "
+                                 "like the query sequence, or not at all")
+            for j in range(3, md + 1):
+                if m.dim_axes[-j] and (j > nd or m.dim_axes[-j] != q.dim_axes[-j]):
+                    raise ValueError("For scaled_dot_product_attention, batch/head dims of attn_mask must be "
+                                     "sharded like the query's, or not at all")
         return make(q, q.dim_axes)
 
     def get_expand_impl(self, func, output_layout, layouts, extra_args):
@@ -50,10 +64,12 @@ class ScaledDotProductAttentionDistributedOp(DistributedOp):
             n *= mesh.mesh_shape[a]
 
         def impl(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None, **kw):
+            sq = query.shape[-2]
             if not is_causal:
+                if attn_mask is not None and attn_mask.dim() >= 2 and attn_mask.shape[-2] == n * sq and n > 1:
+                    attn_mask = attn_mask.narrow(-2, idx * sq, sq)      # the rows of this rank's queries
                 return func(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p,
                             is_causal=False, scale=scale, **kw)
-            sq = query.shape[-2]
             kv_len = (idx + 1) * sq
             key = key.narrow(-2, 0, kv_len)
             value = value.narrow(-2, 0, kv_len)

@@ -179,6 +179,29 @@ def max_dim_values_and_indices(c):
 
 
 @case
+def max_over_sharded_dim_partial_values_global_indices(c):
+    """The values stay Partial(max) on the mesh axis of the reduced dim; the indices are global."""
+    for op in ("max", "min"):
+        got = getattr(c.d(c.X, "dp", "mp"), op)(0)
+        ref = getattr(c.X, op)(0)
+        vals, idx = got
+        assert vals.layout.is_partial() and not idx.layout.is_partial()
+        assert tuple(vals.layout.alias_tensor_map) == ("mp",)
+        c.same(vals, ref.values)
+        c.same(idx, ref.indices)
+    tie = torch.zeros(8, 4)
+    tie[2] = tie[6] = 5.0                                   # the winner appears in both shards: first one counts
+    _, idx = c.d(tie, "dp", "None").max(0, keepdim=True)
+    c.same(idx, tie.max(0, keepdim=True).indices)
+
+
+@case
+def max_of_two_tensors_is_elementwise(c):
+    c.same(torch.max(c.d(c.X, "dp", "mp"), c.d(c.Y, "dp", "mp")), torch.max(c.X, c.Y))
+    c.same(torch.min(c.d(c.X, "dp", "None"), c.d(c.Y, "dp", "None")), torch.min(c.X, c.Y))
+
+
+@case
 def max_all(c):
     c.same(c.d(c.X, "dp", "mp").max(), c.X.max())
 
@@ -585,6 +608,25 @@ def sdpa_with_additive_mask(c):
     s = ("dp", "mp", "None", "None")
     c.same(F.scaled_dot_product_attention(c.d(c.Q, *s), c.d(c.K, *s), c.d(c.V, *s), attn_mask=mask),
            F.scaled_dot_product_attention(c.Q, c.K, c.V, attn_mask=mask))
+
+
+@case
+def sdpa_query_sequence_sharded_with_explicit_mask(c):
+    """A full (S x S) mask with the query sequence sharded: every rank uses the rows of its own queries;
+    a mask distributed like the queries is taken as it is."""
+    mask = torch.ones(8, 8, dtype=torch.bool).tril()
+    q = ("dp", "None", "mp", "None")
+    kv = ("dp", "None", "None", "None")
+    ref = F.scaled_dot_product_attention(c.Q, c.K, c.V, attn_mask=mask)
+    c.same(F.scaled_dot_product_attention(c.d(c.Q, *q), c.d(c.K, *kv), c.d(c.V, *kv), attn_mask=mask), ref)
+    add = torch.randn(8, 8, generator=torch.Generator().manual_seed(5))
+    ref = F.scaled_dot_product_attention(c.Q, c.K, c.V, attn_mask=add)
+    c.same(F.scaled_dot_product_attention(c.d(c.Q, *q), c.d(c.K, *kv), c.d(c.V, *kv),
+                                          attn_mask=c.d(add, "mp", "None")), ref)
+    _raises(ValueError, lambda: F.scaled_dot_product_attention(
+        c.d(c.Q, *q), c.d(c.K, *kv), c.d(c.V, *kv), attn_mask=c.d(add, "None", "mp")))
+    _raises(ValueError, lambda: F.scaled_dot_product_attention(
+        c.d(c.Q, *kv), c.d(c.K, *kv), c.d(c.V, "dp", "mp", "None", "None")))          # key and value differ
 
 
 @case
