@@ -53,7 +53,8 @@ def _build_layout(device_mesh: DeviceMesh, placements: Sequence[Placement], ndim
     key = (device_mesh.to_hash(), tuple(placements), ndim)
     lay = _LAYOUT_CACHE.get(key)
     if lay is None:
-        lay = Layout.from_device_mesh(device_mesh)(tuple(placements))
+        given = tuple(placements) or (Replicate(),) * device_mesh.ndim      # none given: replicated everywhere
+        lay = Layout.from_device_mesh(device_mesh)(given)
         lay.placement_to_tensor_map(ndim)
         _LAYOUT_CACHE[key] = lay
     return lay

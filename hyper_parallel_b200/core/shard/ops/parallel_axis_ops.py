@@ -64,15 +64,25 @@ class TopKDistributedOp(DistributedOp):
 
 
 class RepeatInterleaveDistributedOp(DistributedOp):
+    """``repeat_interleave(x, repeats, dim=None)``; ``repeats`` an int or a (plain) tensor.  With a
+    ``dim`` that dim must be unsharded and the layout is kept.  Without one the input is flattened:
+    a sharding of dim 0 alone survives as the sharding of the flat result when every element repeats
+    equally often (each rank's rows are one contiguous run of the flat tensor); any other sharding
+    is refused."""
+
     def infer_layout(self, layouts, extra_args):
         self._check_partial_inputs(layouts)
         x = layouts[0]
         nd = len(x.dim_axes)
-        ints = [a for a in extra_args if isinstance(a, int) and not isinstance(a, bool)]
-        if len(ints) < 2:
-            require_unsharded(self.op_name, x, range(nd), "flattened")
-            return make(x, [()])
-        dim = norm_dim(ints[1], nd)
+        rest = [a for a in extra_args if not isinstance(a, bool) and a is not None]
+        repeats = rest[0] if rest else None
+        dim = next((a for a in rest[1:] if isinstance(a, int)), None)
+        if dim is None:
+            require_unsharded(self.op_name, x, range(1, nd), "flattened")
+            if x.dim_axes[0] and not isinstance(repeats, int):
+                require_unsharded(self.op_name, x, [0], "flattened")
+            return make(x, [x.dim_axes[0] if nd else ()])
+        dim = norm_dim(dim, nd)
         require_unsharded(self.op_name, x, [dim], "repeated")
         return make(x, x.dim_axes)
 
@@ -120,9 +130,10 @@ class ScatterDistributedOp(DistributedOp):
         x = layouts[0]
         dim = norm_dim(_first_int(extra_args, 0), len(x.dim_axes))
         require_unsharded(self.op_name, x, [dim], "scatter")
-        for l in layouts[1:]:
-            if l is not None and l.dim_axes != x.dim_axes:
-                raise ValueError(f"For {self.op_name}, index/src must be sharded like the input")
+        for what, l in zip(("Index", "Src"), [l for l in layouts[1:] if l is not None]):
+            if l.dim_axes != x.dim_axes:
+                raise ValueError(f"For {self.op_name}, index/src must be sharded like the input: {what} tensor "
+                                 f"layout {l.alias_tensor_map} must match input layout {x.alias_tensor_map}")
         return make(x, x.dim_axes)
 
 
@@ -134,9 +145,10 @@ class MaskedScatterDistributedOp(DistributedOp):
 
     def infer_layout(self, layouts, extra_args):
         self._check_partial_inputs(layouts)
-        for l in layouts:
+        for what, l in zip(("input", "mask", "source"), layouts):
             if l is not None and any(l.dim_axes):
-                raise ValueError(f"For {self.op_name}, all inputs must be replicated")
+                raise ValueError(f"For {self.op_name}, all inputs must be replicated, but {what} is sharded "
+                                 f"({l.alias_tensor_map})")
         x = layouts[0]
         return make(x, x.dim_axes)
 
@@ -250,7 +262,8 @@ class IsinDistributedOp(DistributedOp):
             raise ValueError("For isin, elements must be a distributed tensor")
         for l in layouts[1:]:
             if l is not None and any(l.dim_axes):
-                raise ValueError("For isin, test_elements must be replicated")
+                raise ValueError("For isin, 'test_elements' must be unsharded (replicated), got "
+                                 f"{l.alias_tensor_map}")
         return make(x, x.dim_axes)
 
 
