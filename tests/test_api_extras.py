@@ -171,3 +171,38 @@ def _tied_worker(rank, world):
 
 def test_pipeline_tied_parameters_are_broadcast_and_their_grads_summed():
     run_distributed(_tied_worker, 2)
+
+
+def test_reference_compat_runner_rewrites_and_runs_a_reference_style_test(tmp_path):
+    """A test file in the style of the reference's torch tests (NPU devices, HCCL, ``init_dist`` from a
+    helper module) runs against this package on two CPU ranks; a failing function is reported."""
+    from hyper_parallel_b200.utils import reference_compat as rc
+    root = tmp_path / "checkout"
+    (root / "tests" / "torch" / "demo").mkdir(parents=True)
+    (root / "tests" / "torch" / "demo" / "demo_case.py").write_text(
+        "import torch\n"
+        "import torch_npu\n"
+        "import torch.distributed as dist\n"
+        "from hyper_parallel import DTensor, init_device_mesh\n"
+        "from hyper_parallel.core.placement_types import Shard, Replicate\n"
+        "from tests.torch.utils import init_dist\n\n\n"
+        "def test_shard_round_trip():\n"
+        "    init_dist()\n"
+        "    mesh = init_device_mesh(device_type=\"npu\", mesh_shape=(2,), mesh_dim_names=(\"dp\",))\n"
+        "    x = DTensor.from_local(torch.ones(2, 4).npu() * dist.get_rank(), mesh, (Shard(0),))\n"
+        "    full = x.redistribute(mesh, (Replicate(),)).to_local()\n"
+        "    assert full.shape == (4, 4) and full[2:].eq(1).all() and dist.get_backend() == \"hccl\"\n\n\n"
+        "def test_that_fails():\n"
+        "    init_dist()\n"
+        "    assert False, 'as intended'\n")
+    text = rc.rewrite((root / "tests/torch/demo/demo_case.py").read_text())
+    assert "hyper_parallel_b200.core.placement_types" in text and "torch_npu" not in text
+    assert '"cpu"' in text and ".cpu()" in text and '"gloo"' in text and "npu" not in text
+    assert rc.rewrite("import hyper_parallel_b200") == "import hyper_parallel_b200"          # already migrated text is kept
+    assert rc.list_test_functions(str(root / "tests/torch/demo/demo_case.py")) == ["test_shard_round_trip", "test_that_fails"]
+    out = tmp_path / "gen"
+    path = rc.prepare(str(root), "tests/torch/demo/demo_case.py", str(out))
+    ok, tb = rc.run_function(str(out), path, "test_shard_round_trip", 2, timeout=120.0)
+    assert ok and tb is None
+    ok, tb = rc.run_function(str(out), path, "test_that_fails", 2, timeout=120.0)
+    assert not ok and "as intended" in tb
