@@ -170,10 +170,14 @@ class FSDPParam:
             g = g.to(self.orig_dtype)
         if self.offload:
             g = g.to("cpu")
+        # ``param.grad`` of a sharded parameter is a DTensor with the parameter's layout, as in the
+        # reference (platform/torch/fully_shard/param.py:120-172 there): the local tensor carries it
+        g = g.reshape(leaf.shape)
         if leaf.grad is None:
-            leaf.grad = g.reshape(leaf.shape)
+            leaf.grad = DTensor._wrap(g, self.sharded_param._layout)
         else:
-            leaf.grad.add_(g.reshape(leaf.shape))
+            acc = leaf.grad
+            (acc._local_tensor if isinstance(acc, DTensor) else acc).add_(g)
 
     # ------------------------------------------------------------ state dict --
     def full_tensor(self) -> torch.Tensor:

@@ -108,8 +108,8 @@ def _train(build, wrap, steps=2, batch=4, hidden=32, seed=5):
 
 
 def _local(g):
-    """``.grad`` of a sharded parameter is this rank's shard of the gradient (the DTensor's local
-    tensor carries it); accept a DTensor too."""
+    """``.grad`` of a sharded parameter is a DTensor laid out like the parameter; of an ignored
+    (plain) parameter a plain tensor."""
     return g.to_local() if hasattr(g, "to_local") else g
 
 
@@ -214,8 +214,8 @@ def _matsum_fully_shard(mesh, accumulate=False, sync_last_only=False, tol=1e-3, 
                 loss = net(x)
                 loss.backward(seed.to(loss.dtype))
                 if net.weight.grad is not None:
-                    assert isinstance(net.weight, DTensor)
-                    grad = _local(net.weight.grad).clone()
+                    assert isinstance(net.weight.grad, DTensor), type(net.weight.grad)
+                    grad = net.weight.grad.to_local().clone()
                 if not accumulate:
                     opt.step()
                     opt.zero_grad()

@@ -93,6 +93,8 @@ def _param_worker(rank, world, case):
     net(xs).float().sum().backward()
     tol = 5e-2 if case == "mp" else 1e-5
     got = net.l1.weight.grad
+    assert isinstance(got, DTensor) and tuple(got.placements) == tuple(net.l1.weight.placements)
+    got = got.to_local()                                  # the gradient is a DTensor laid out like the parameter
     assert got is not None and tuple(got.shape) == tuple(want)
     assert torch.allclose(got.float(), ref.l1.weight.grad.chunk(n, dim=dim)[sr], atol=tol, rtol=tol)
     # the buffer is untouched and not sharded
@@ -129,14 +131,14 @@ def _accum_worker(rank, world):
     net.set_requires_gradient_sync(True)
     net(xb.chunk(world)[rank]).sum().backward()
     want = ref.l1.weight.grad.chunk(2, dim=0)[sr]
-    assert torch.allclose(net.l1.weight.grad, want, atol=1e-5)
+    assert torch.allclose(net.l1.weight.grad.to_local(), want, atol=1e-5)
 
     # without the replica all-reduce each replica keeps the sum over its own shard group
     net.zero_grads()
     assert net.l1.weight.grad is None
     net.set_requires_all_reduce(False)
     net(xa.chunk(world)[rank]).sum().backward()
-    part = net.l1.weight.grad.clone()
+    part = net.l1.weight.grad.to_local().clone()
     import torch.distributed as dist
     dist.all_reduce(part, group=fp.mesh_info.replicate_group)
     ref.zero_grad()
