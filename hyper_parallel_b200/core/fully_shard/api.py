@@ -29,11 +29,57 @@ class _UnshardHandle:
             self.state.wait_for_unshard()
             self.state = None
 
+    _hsdp_state = property(lambda self: self.state)       # the reference's attribute name
+
+
+def _need_bool(name: str, value) -> bool:
+    if not isinstance(value, bool):
+        raise ValueError(f"{name} must be a bool, got {type(value).__name__}")
+    return value
+
+
+def _need_modules(name: str, modules) -> list:
+    if not isinstance(modules, (list, tuple)):
+        raise ValueError(f"{name} must be a list of fully_shard modules, got {type(modules).__name__}")
+    for m in modules:
+        if not isinstance(m, nn.Module) or "_fsdp_state" not in m.__dict__:
+            raise ValueError(f"{name}: {type(m).__name__} is not a fully_shard module")
+    return list(modules)
+
+
+class _SchedulerView:
+    """Read-only view of a module's :class:`FSDPState` under the attribute names of the reference's
+    scheduler object (``module.hsdp_scheduler`` there: core/fully_shard/hsdp_scheduler.py:32-194 and
+    hsdp_state.py:22-177), for code that inspects it: ``requires_grad_sync``, ``reshard_after_forward``,
+    ``forward_prefetch_cells`` / ``backward_prefetch_cells``, ``config.reshard_after_forward``,
+    ``scheduler_ctx.is_last_backward``, ``hsdp_state.{reduce_grads, requires_all_reduce,
+    reshard_after_backward, is_shard}``."""
+
+    def __init__(self, state: FSDPState):
+        self._s = state
+
+    requires_grad_sync = property(lambda self: self._s.requires_gradient_sync)
+    reduce_grads = property(lambda self: self._s.requires_gradient_sync)
+    requires_all_reduce = property(lambda self: self._s.requires_all_reduce)
+    reshard_after_forward = property(lambda self: self._s.reshard_after_forward)
+    reshard_after_backward = property(lambda self: self._s.reshard_after_backward)
+    is_last_backward = property(lambda self: self._s.is_last_backward)
+    is_shard = property(lambda self: self._s.is_sharded)
+    forward_prefetch_cells = property(lambda self: list(self._s.fwd_prefetch))
+    backward_prefetch_cells = property(lambda self: list(self._s.bwd_prefetch))
+    hsdp_state = property(lambda self: self)
+    config = property(lambda self: self)
+    scheduler_ctx = property(lambda self: self)
+
 
 class HSDPModule:
     """Methods added to a module by :func:`fully_shard`."""
 
     _fsdp_state: FSDPState
+
+    @property
+    def hsdp_scheduler(self) -> _SchedulerView:
+        return _SchedulerView(self._fsdp_state)
 
     def _states(self, recurse: bool = True) -> List[FSDPState]:
         mods = self.modules() if recurse else [self]
@@ -51,35 +97,29 @@ class HSDPModule:
 
     def set_requires_gradient_sync(self, requires_gradient_sync: bool, *, recurse: bool = True) -> None:
         for st in self._states(recurse):
-            st.requires_gradient_sync = bool(requires_gradient_sync)
+            st.requires_gradient_sync = _need_bool("requires_gradient_sync", requires_gradient_sync)
 
     def set_requires_all_reduce(self, requires_all_reduce: bool, *, recurse: bool = True) -> None:
         for st in self._states(recurse):
-            st.requires_all_reduce = bool(requires_all_reduce)
+            st.requires_all_reduce = _need_bool("requires_all_reduce", requires_all_reduce)
 
     def set_is_last_backward(self, is_last_backward: bool) -> None:
         for st in self._states():
-            st.is_last_backward = bool(is_last_backward)
+            st.is_last_backward = _need_bool("is_last_backward", is_last_backward)
 
     def set_reshard_after_forward(self, reshard_after_forward: bool, recurse: bool = True) -> None:
         for st in self._states(recurse):
-            st.reshard_after_forward = bool(reshard_after_forward)
+            st.reshard_after_forward = _need_bool("reshard_after_forward", reshard_after_forward)
 
     def set_reshard_after_backward(self, reshard_after_backward: bool, *, recurse: bool = True) -> None:
         for st in self._states(recurse):
-            st.reshard_after_backward = bool(reshard_after_backward)
+            st.reshard_after_backward = _need_bool("reshard_after_backward", reshard_after_backward)
 
     def set_modules_to_forward_prefetch(self, modules: List[nn.Module]) -> None:
-        for m in modules:
-            if "_fsdp_state" not in m.__dict__:
-                raise ValueError(f"{type(m).__name__} is not a fully_shard module")
-        self._fsdp_state.fwd_prefetch = list(modules)
+        self._fsdp_state.fwd_prefetch = _need_modules("modules_to_forward_prefetch", modules)
 
     def set_modules_to_backward_prefetch(self, modules: List[nn.Module]) -> None:
-        for m in modules:
-            if "_fsdp_state" not in m.__dict__:
-                raise ValueError(f"{type(m).__name__} is not a fully_shard module")
-        self._fsdp_state.bwd_prefetch = list(modules)
+        self._fsdp_state.bwd_prefetch = _need_modules("modules_to_backward_prefetch", modules)
 
     def zero_grads(self) -> None:
         """Drop the accumulated (sharded) gradients of every wrapped module below this one.  The

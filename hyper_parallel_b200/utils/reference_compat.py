@@ -21,7 +21,7 @@ not 1 is the identity as in torch (the reference raises).
 from __future__ import annotations
 
 import argparse
-import importlib.util
+import importlib
 import os
 import re
 import socket
@@ -30,9 +30,12 @@ import tempfile
 import traceback
 from typing import List
 
-_HELPERS = ("tests/torch/common_net.py", "tests/torch/hsdp/hsdp_test_common.py", "tests/torch/shard/utils.py")
+_HELPERS = ("tests/torch/common_net.py", "tests/torch/hsdp/hsdp_test_common.py", "tests/torch/shard/utils.py",
+            "tests/torch/shard/base_shard.py")
 _INIT_DIST = ("import torch.distributed as dist\n\n\ndef init_dist():\n    if not dist.is_initialized():\n"
-              "        dist.init_process_group('gloo')\n    return dist.get_rank(), 0\n")
+              "        dist.init_process_group('gloo')\n    return dist.get_rank(), 0\n\n\n"
+              "def torchrun_case(*args, **kwargs):\n    raise RuntimeError('launcher files are not run; name the worker file')\n")
+_MARK_UTILS = "def arg_mark(*args, **kwargs):\n    return lambda fn: fn\n"
 
 
 def rewrite(source: str, package: str = "hyper_parallel_b200") -> str:
@@ -77,6 +80,15 @@ def prepare(root: str, rel: str, out_root: str) -> str:
         open(os.path.join(out_root, d, "__init__.py"), "a").close()
     with open(os.path.join(out_root, "tests/torch/utils.py"), "w", encoding="utf-8") as f:
         f.write(_INIT_DIST)
+    os.makedirs(os.path.join(out_root, "tests/common"), exist_ok=True)
+    open(os.path.join(out_root, "tests/common/__init__.py"), "a").close()
+    with open(os.path.join(out_root, "tests/common/mark_utils.py"), "w", encoding="utf-8") as f:
+        f.write(_MARK_UTILS)
+    # siblings of the test file, for its relative imports
+    folder = os.path.dirname(rel)
+    for name in sorted(os.listdir(os.path.join(root, folder))):
+        if name.endswith(".py") and name != "__init__.py":
+            _generate(root, os.path.join(folder, name), out_root)
     return _generate(root, rel, out_root)
 
 
@@ -89,9 +101,12 @@ def _worker(rank: int, world: int, port: int, out_root: str, path: str, fn: str,
     torch.set_num_threads(1)
     try:
         dist.init_process_group("gloo", rank=rank, world_size=world)
-        spec = importlib.util.spec_from_file_location("reference_test", path)
-        module = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(module)
+        real_init = dist.init_process_group
+        # helpers of the tests initialise the default group themselves, unconditionally
+        dist.init_process_group = lambda *a, **k: None if dist.is_initialized() else real_init(*a, **k)
+        # imported under its package path so that relative imports of sibling files resolve
+        name = os.path.relpath(path, out_root)[:-3].replace(os.sep, ".")
+        module = importlib.import_module(name)
         getattr(module, fn)()
         if dist.is_initialized():           # some tests destroy the process group themselves
             dist.barrier()
