@@ -74,6 +74,23 @@ def _install_grads(state: HSDPState) -> None:
             if g.shape != hp.leaf.shape:
                 g = g.reshape(hp.leaf.shape)
             hp.leaf.grad = g
+    if state.config.requires_acc_grad and not state.grad_hook.requires_grad_sync:
+        # A micro-step without synchronisation: ``param.grad`` shows the running accumulator (this
+        # rank's rows of it where the accumulator is kept at full size), as the reference's hooks do by
+        # returning it (core/hsdp/hsdp_grad_hook.py:60-150 there).  It is a view, valid until the next
+        # forward of the cell, which takes it away again so that autograd never adds into it.
+        for hp in state.hsdp_params:
+            acc = hp.acc_grad
+            if acc is None or hp.leaf.grad is not None:
+                continue
+            if acc.shape != hp.leaf.shape:
+                if not hp.sharded or acc.shape != hp.full_shape:
+                    continue
+                acc = acc.chunk(hp.shard_size, dim=0)[hp.sharded_group_info.index]
+                if acc.shape != hp.leaf.shape:
+                    continue
+            hp.leaf.grad = acc.detach()
+            hp._acc_exposed = True
 
 
 def _root_backward_callback() -> None:
@@ -178,6 +195,11 @@ class HSDPScheduler:
             Variable._execution_engine.queue_callback(_root_backward_callback)
 
     def _forward_pre(self, cell, args, kwargs):
+        if self.config.requires_acc_grad:
+            for hp in self.hsdp_state.hsdp_params:
+                if getattr(hp, "_acc_exposed", False):
+                    hp.leaf.grad = None
+                    hp._acc_exposed = False
         self.hsdp_state.unshard()
         self.state = FwdBwdState.FORWARD
         for c in self.forward_prefetch_cells:

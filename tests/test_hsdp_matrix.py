@@ -151,3 +151,40 @@ def _unused_worker(rank, world, level):
 @pytest.mark.parametrize("level", ["level1", "level2", "level3"])
 def test_bucket_with_a_parameter_that_gets_no_gradient(level):
     run_distributed(_unused_worker, 2, level)
+
+
+def _acc_visible_worker(rank, world, level, shard_size):
+    """Between micro-steps ``param.grad`` shows the running accumulator; the synchronising micro-step
+    replaces it by the reduced gradient; the forward in between never lets autograd add into it."""
+    import hyper_parallel_b200 as hp
+    torch.manual_seed(3)
+    net = nn.Linear(8, 8, bias=False)
+    ref = nn.Linear(8, 8, bias=False)
+    ref.load_state_dict(net.state_dict())
+    hp.hsdp(net, shard_size=shard_size, threshold=0, optimizer_level=level, enable_grad_accumulation=True)
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.randn(4, 8, generator=g) for _ in range(3)]
+    rows = 8 // shard_size
+    lo = (rank % shard_size) * rows
+    total = torch.zeros(8, 8)
+    for i, x in enumerate(xs):
+        net.set_requires_grad_sync(i == 2)
+        net(x).sum().backward()
+        ref.zero_grad()
+        ref(x).sum().backward()
+        total += ref.weight.grad
+        got = net.weight.grad
+        assert got is not None, (level, i)
+        if i < 2:                                   # unreduced, accumulated so far (this rank's rows)
+            want = total[lo:lo + rows] if got.shape[0] == rows else total
+            if level == "level1" or shard_size == 1:
+                assert torch.allclose(got, want, atol=1e-5), (level, i)
+        else:                                       # every rank fed the same data: the sum is world x
+            assert torch.allclose(got, world * total[lo:lo + rows], atol=1e-4), (level, i)
+    net.zero_grads()
+    assert net.weight.grad is None
+
+
+@pytest.mark.parametrize("level,shard_size", [("level1", 2), ("level2", 2), ("level3", 2), ("level1", 1)])
+def test_accumulator_is_visible_between_micro_steps(level, shard_size):
+    run_distributed(_acc_visible_worker, 2, level, shard_size)
