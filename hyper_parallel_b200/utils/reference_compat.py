@@ -41,6 +41,11 @@ _MARK_UTILS = "def arg_mark(*args, **kwargs):\n    return lambda fn: fn\n"
 def rewrite(source: str, package: str = "hyper_parallel_b200") -> str:
     """The text of a reference test file with this package's name and CPU devices."""
     s = re.sub(r"\bhyper_parallel\b(?!_b200)", package, source)
+    if "torch_npu.npu_fusion_attention" in s:
+        # the fused-attention operator of the NPU extension has a same-named counterpart here
+        s = s.replace("torch_npu.npu_fusion_attention", "_hpb_fa.npu_fusion_attention")
+        s = re.sub(r"^(\s*)import torch_npu.*$", rf"\1from {package}.ops import flash_attention_score as _hpb_fa", s,
+                   count=1, flags=re.M)
     s = re.sub(r"^\s*import torch_npu.*$", "", s, flags=re.M)
     s = s.replace(".npu()", ".cpu()").replace('"npu"', '"cpu"').replace("'npu'", "'cpu'")
     s = s.replace("torch.npu.get_rng_state()", "torch.get_rng_state()")
