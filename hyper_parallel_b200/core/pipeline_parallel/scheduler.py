@@ -31,6 +31,7 @@ from .stage import PipelineStage
 from .utils import MicroBatch
 
 logger = logging.getLogger(__name__)
+_LOG = logger
 
 
 class MetaStepType(Enum):
@@ -137,40 +138,124 @@ def add_send_recv(compute_order: Dict[int, List[MetaStep]], stage_num: int, real
 
 
 # --------------------------------------------------------------------- validator --
-def generate_operations(order_list: Dict[int, List[MetaStep]]) -> List[Tuple[int, MetaStep]]:
-    return [(r, st) for r, prog in order_list.items() for st in prog]
+# Function names, arguments and return values follow the reference's static checker
+# (core/pipeline_parallel/scheduler.py:571-848 there), so tools written against it keep working:
+# ``generate_operations`` names every transfer of every rank, ``parse_and_validate`` checks that each
+# named transfer appears on both of its ranks, ``detect_cycle_in_graph`` looks for a cycle in the
+# "happens before on one rank" graph of those names (a cycle = ranks waiting for one another), and
+# ``validate_pipeline_execution`` runs all three.  On top of that the programs are replayed with
+# blocking receives, which also catches a receive whose send never comes.
+def _stage_owner(stage_index: int, com_type: str, total_stages: int, real_stage_num: int) -> int:
+    if com_type == "loop":
+        return stage_index % real_stage_num
+    if com_type == "v":
+        r = stage_index % (2 * real_stage_num)
+        return r if r < real_stage_num else 2 * real_stage_num - 1 - r
+    raise ValueError(f"com_type must be 'loop' or 'v', got {com_type!r}")
 
 
-def parse_and_validate(order_list: Dict[int, List[MetaStep]], chunk_num: int = 1, com_type: str = "loop"):
-    """Check that every SEND has exactly one matching RECV on the peer (and vice versa)."""
+def generate_operations(order_list: Dict[int, List[MetaStep]], chunk_num: int = 1,
+                        com_type: str = "loop") -> Dict[str, List[str]]:
+    """``{str(rank): ["Send_Receive_(src)->(dst)_micro<m>_<k>th", ...]}``: the transfers of every rank in
+    program order.  Both ends of a transfer get the same name; ``k`` counts the transfers of one
+    (src, dst, micro-batch) triple on that rank, so matching sends and receives pair up by name."""
     real = len(order_list)
+    total = real * chunk_num
+    out: Dict[str, List[str]] = {}
+    for rank, steps in order_list.items():
+        counter: Dict[tuple, int] = {}
+        ops = []
+        for st in steps:
+            t, s = st.type, st.stage_index
+            if t in (MetaStepType.FWD_SEND, MetaStepType.BWD_SEND):
+                peer_stage = s + 1 if t == MetaStepType.FWD_SEND else s - 1
+                if not 0 <= peer_stage < total:
+                    continue
+                pair = (rank, _stage_owner(peer_stage, com_type, total, real), st.micro_index)
+            elif t in (MetaStepType.FWD_RECV, MetaStepType.BWD_RECV):
+                peer_stage = s - 1 if t == MetaStepType.FWD_RECV else s + 1
+                if not 0 <= peer_stage < total:
+                    continue
+                pair = (_stage_owner(peer_stage, com_type, total, real), rank, st.micro_index)
+            else:
+                continue
+            counter[pair] = counter.get(pair, 0) + 1
+            ops.append(f"Send_Receive_({pair[0]})->({pair[1]})_micro{pair[2]}_{counter[pair]}th")
+        if ops:
+            out[str(rank)] = ops
+    return out
 
-    def owner(s):
-        if com_type == "v":
-            r = s % (2 * real)
-            return r if r < real else 2 * real - 1 - r
-        return s % real
-    sends, recvs = {}, {}
-    for r, prog in order_list.items():
-        for st in prog:
-            t, m, s = st.type, st.micro_index, st.stage_index
-            if t == MetaStepType.FWD_SEND:
-                sends[("f", m, s + 1)] = sends.get(("f", m, s + 1), 0) + 1
-            elif t == MetaStepType.FWD_RECV:
-                recvs[("f", m, s)] = recvs.get(("f", m, s), 0) + 1
-            elif t == MetaStepType.BWD_SEND:
-                sends[("b", m, s - 1)] = sends.get(("b", m, s - 1), 0) + 1
-            elif t == MetaStepType.BWD_RECV:
-                recvs[("b", m, s)] = recvs.get(("b", m, s), 0) + 1
-    errors = []
-    for k in set(sends) | set(recvs):
-        if sends.get(k, 0) != 1 or recvs.get(k, 0) != 1:
-            errors.append(f"transfer {k}: {sends.get(k, 0)} send(s), {recvs.get(k, 0)} recv(s)")
+
+def parse_and_validate(data, all_rank: bool = True) -> List[str]:
+    """Check a ``{rank: [transfer names]}`` table: every name must be listed by both ranks it mentions
+    (with ``all_rank`` a mentioned rank that has no entry at all is an error too).  Problems are logged
+    and returned as a list of messages; malformed input is reported, never raised."""
+    import re
+    errors: List[str] = []
+    if not isinstance(data, dict):
+        errors.append("input must be a dict of rank -> list of transfer names")
+    else:
+        good = {k: set(v) for k, v in data.items() if isinstance(v, list) and all(isinstance(i, str) for i in v)}
+        for key, values in data.items():
+            if key not in good:
+                errors.append(f"values for key {key!r} must be a list of strings")
+                continue
+            for value in values:
+                ranks = set(re.findall(r"\((\d+)\)", value)[:2])
+                if all_rank:
+                    missing = ranks - good.keys()
+                    if missing:
+                        errors.append(f"ranks {sorted(missing)} named by {value!r} have no entry")
+                        continue
+                for r in (ranks if all_rank else ranks & good.keys()):
+                    if value not in good[r]:
+                        errors.append(f"rank {r} lacks the transfer {value!r}")
+    for e in errors:
+        _LOG.error("pipeline schedule: %s", e)
     return errors
 
 
-def detect_cycle_in_graph(order_list: Dict[int, List[MetaStep]]) -> Optional[str]:
-    """Replay with blocking receives and ordered (tag-less) p2p per pair; returns a message on deadlock."""
+def detect_cycle_in_graph(ranks_map: Dict[str, List[str]]):
+    """``(cycle_path, cycle_ranks)`` of the first cycle in the graph whose edges join consecutive entries
+    of each rank's list -- ``cycle_path`` the nodes (first = last), ``cycle_ranks`` one
+    ``"<rank> <u> -> <v>"`` per edge -- or ``(None, None)``."""
+    graph: Dict[str, List[str]] = {}
+    edge_rank: Dict[tuple, str] = {}
+    for rank, nodes in (ranks_map or {}).items():
+        for u, v in zip(nodes, nodes[1:]):
+            graph.setdefault(u, []).append(v)
+            graph.setdefault(v, [])
+            edge_rank[(u, v)] = rank
+    done = set()
+    for root in graph:
+        if root in done:
+            continue
+        path, on_path, iters = [root], {root}, [iter(graph[root])]
+        while iters:
+            nxt = next(iters[-1], None)
+            if nxt is None:                         # every edge of the last node followed: leave it
+                node = path.pop()
+                on_path.discard(node)
+                done.add(node)
+                iters.pop()
+            elif nxt in on_path:
+                cyc = path[path.index(nxt):] + [nxt]
+                return cyc, [f"{edge_rank[(u, v)]} {u} -> {v}" for u, v in zip(cyc, cyc[1:])]
+            elif nxt not in done:
+                path.append(nxt)
+                on_path.add(nxt)
+                iters.append(iter(graph[nxt]))
+    return None, None
+
+
+def output_cycle_results(cycle_path, cycle_ranks) -> None:
+    if cycle_path:
+        _LOG.error("pipeline schedule: ranks wait for one another: %s (%s)", " -> ".join(cycle_path),
+                   "; ".join(cycle_ranks))
+
+
+def _replay_blocking(order_list: Dict[int, List[MetaStep]]) -> Optional[str]:
+    """Replay with blocking receives; returns a message when some rank can never proceed."""
     ptr = {r: 0 for r in order_list}
     sent: Dict[Tuple[str, int, int], bool] = {}
     progress = True
@@ -199,15 +284,25 @@ def detect_cycle_in_graph(order_list: Dict[int, List[MetaStep]]) -> Optional[str
 
 
 def validate_pipeline_execution(order_list: Dict[int, List[MetaStep]], chunk_num: int = 1,
-                                com_type: str = "loop") -> bool:
-    """Raise ``RuntimeError`` if the programs contain unmatched transfers or can deadlock."""
-    errors = parse_and_validate(order_list, chunk_num, com_type)
-    if errors:
-        raise RuntimeError("unmatched pipeline transfers: " + "; ".join(errors))
-    msg = detect_cycle_in_graph(order_list)
-    if msg:
-        raise RuntimeError(msg)
-    return True
+                                com_type: str = "loop", raise_on_error: bool = False) -> dict:
+    """Static check of per-rank programs.  Returns ``{"formatted_operations", "cycle_path",
+    "cycle_ranks", "has_cycle"}`` as the reference does, plus ``"error_messages"`` (unmatched transfers,
+    the cycle, a replay that gets stuck) and ``"has_errors"``.  With ``raise_on_error`` any error raises
+    ``RuntimeError`` instead -- the form the schedules use on themselves."""
+    ops = generate_operations(order_list, chunk_num, com_type)
+    messages = list(parse_and_validate(ops, True))
+    cycle_path, cycle_ranks = detect_cycle_in_graph(ops)
+    output_cycle_results(cycle_path, cycle_ranks)
+    if cycle_path:
+        messages.append("ranks wait for one another: " + " -> ".join(cycle_path))
+    stuck = _replay_blocking(order_list)
+    if stuck:
+        messages.append(stuck)
+    result = {"formatted_operations": ops, "cycle_path": cycle_path, "cycle_ranks": cycle_ranks,
+              "has_cycle": bool(cycle_path), "error_messages": messages, "has_errors": bool(messages)}
+    if raise_on_error and messages:
+        raise RuntimeError("invalid pipeline programs: " + "; ".join(messages))
+    return result
 
 
 # ----------------------------------------------------------------------- runtime --

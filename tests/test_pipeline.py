@@ -23,7 +23,8 @@ def _compute_order(kind, M, S, V=1):
                                         ("vpp", 6, 4, 2), ("vpp", 8, 2, 3), ("1f1b", 16, 8, 1)])
 def test_generated_programs_are_matched_and_deadlock_free(kind, M, S, V):
     progs = add_send_recv(_compute_order(kind, M, S, V), S * V, S)
-    assert validate_pipeline_execution(progs, V)
+    res = validate_pipeline_execution(progs, V)
+    assert not res["has_errors"] and not res["has_cycle"], res["error_messages"]
     for r, prog in progs.items():
         f = [s for s in prog if s.type == MetaStepType.FWD]
         b = [s for s in prog if s.type == MetaStepType.BWD]
@@ -33,13 +34,46 @@ def test_generated_programs_are_matched_and_deadlock_free(kind, M, S, V):
 def test_validator_detects_unmatched_and_deadlock():
     T = MetaStepType
     bad = {0: [MetaStep(0, T.FWD, 0), MetaStep(0, T.FWD_SEND, 0)], 1: [MetaStep(0, T.FWD, 1)]}
-    with pytest.raises(RuntimeError, match="unmatched"):
-        validate_pipeline_execution(bad)
+    res = validate_pipeline_execution(bad)                       # the reference's form: a report, no exception
+    assert res["has_errors"] and not res["has_cycle"] and "have no entry" in res["error_messages"][0]
+    with pytest.raises(RuntimeError, match="have no entry"):
+        validate_pipeline_execution(bad, raise_on_error=True)
     dead = {0: [MetaStep(0, T.BWD_RECV, 0), MetaStep(0, T.FWD, 0), MetaStep(0, T.FWD_SEND, 0), MetaStep(0, T.BWD, 0)],
             1: [MetaStep(0, T.FWD_RECV, 1), MetaStep(0, T.FWD, 1), MetaStep(0, T.BWD, 1), MetaStep(0, T.BWD_SEND, 1)]}
+    res = validate_pipeline_execution(dead)
+    assert res["has_cycle"] and res["cycle_path"][0] == res["cycle_path"][-1] and len(res["cycle_ranks"]) == 2
     with pytest.raises(RuntimeError, match="deadlock"):
-        validate_pipeline_execution(dead)
+        validate_pipeline_execution(dead, raise_on_error=True)
     assert MetaStep.from_str("FWD_RECV_3_1") == MetaStep(3, T.FWD_RECV, 1)
+
+
+def test_validator_building_blocks_keep_the_reference_contracts():
+    """Names of transfers, the both-ends check and the cycle search, with the inputs and outputs of the
+    reference's unit tests (tests/mindspore/st/pipeline_parallel/test_order.py:28-175 and :835-905)."""
+    from hyper_parallel_b200.core.pipeline_parallel.scheduler import (detect_cycle_in_graph, generate_operations,
+                                                                      parse_and_validate)
+    T = MetaStepType
+    pair = {0: [MetaStep(0, T.FWD, 0), MetaStep(0, T.FWD_SEND, 0)], 1: [MetaStep(0, T.FWD_RECV, 1), MetaStep(0, T.FWD, 1)]}
+    ops = generate_operations(pair, chunk_num=1, com_type="loop")
+    assert ops == {"0": ["Send_Receive_(0)->(1)_micro0_1th"], "1": ["Send_Receive_(0)->(1)_micro0_1th"]}
+    assert parse_and_validate(ops) == []
+    assert parse_and_validate({"1": ["Send_Receive_(1)->(2)_micro0_1th"]}, all_rank=True)          # rank 2 has no entry
+    assert parse_and_validate({"1": ["Send_Receive_(1)->(2)_micro0_1th"],
+                               "2": ["Send_Receive_(1)->(2)_micro0_1th", "Send_Receive_(1)->(2)_micro0_2th"]})
+    assert parse_and_validate({"1": "not_a_list", "2": [1, 2, 3], "3": ["a", "b"]})                 # reported, not raised
+    assert parse_and_validate({"1": [], "2": [""]}) == []
+    assert detect_cycle_in_graph({"1": ["A", "B", "C", "A"]}) == (["A", "B", "C", "A"], ["1 A -> B", "1 B -> C", "1 C -> A"])
+    assert detect_cycle_in_graph({"r1": ["A", "B", "C"], "r2": ["D", "E"]}) == (None, None)
+    assert detect_cycle_in_graph({}) == (None, None)
+    assert detect_cycle_in_graph({"1": ["A", "B", "C"], "2": ["C", "D", "E"], "3": ["E", "A"]}) == (
+        ["A", "B", "C", "D", "E", "A"], ["1 A -> B", "1 B -> C", "2 C -> D", "2 D -> E", "3 E -> A"])
+    assert detect_cycle_in_graph({"1": ["A", "B", "C"], "2": ["D", "E", "D"]}) == (["D", "E", "D"], ["2 D -> E", "2 E -> D"])
+    assert detect_cycle_in_graph({"1": ["A", "B"], "2": ["B", "A"]}) == (["A", "B", "A"], ["1 A -> B", "2 B -> A"])
+    assert detect_cycle_in_graph({"1": ["A", "A"]}) == (["A", "A"], ["1 A -> A"])
+    # 'v' placement: virtual stage 3 of a 2-rank pipeline lives on rank 0 again
+    v = {0: [MetaStep(0, T.FWD_SEND, 0), MetaStep(0, T.FWD_RECV, 3)], 1: [MetaStep(0, T.FWD_RECV, 1), MetaStep(0, T.FWD_SEND, 2)]}
+    assert generate_operations(v, chunk_num=2, com_type="v")["1"] == ["Send_Receive_(0)->(1)_micro0_1th",
+                                                                      "Send_Receive_(1)->(0)_micro0_1th"]
 
 
 # ------------------------------------------------------------------ distributed --
