@@ -199,6 +199,9 @@ def test_reference_compat_runner_rewrites_and_runs_a_reference_style_test(tmp_pa
     assert "hyper_parallel_b200.core.placement_types" in text and "torch_npu" not in text
     assert '"cpu"' in text and ".cpu()" in text and '"gloo"' in text and "npu" not in text
     assert rc.rewrite("import hyper_parallel_b200") == "import hyper_parallel_b200"          # already migrated text is kept
+    fa = rc.rewrite("import torch_npu\nout = torch_npu.npu_fusion_attention(q, k, v, 8)\n")
+    assert "from hyper_parallel_b200.ops import flash_attention_score as _hpb_fa" in fa
+    assert "_hpb_fa.npu_fusion_attention(q, k, v, 8)" in fa and "torch_npu" not in fa
     assert rc.list_test_functions(str(root / "tests/torch/demo/demo_case.py")) == ["test_shard_round_trip", "test_that_fails"]
     out = tmp_path / "gen"
     path = rc.prepare(str(root), "tests/torch/demo/demo_case.py", str(out))
