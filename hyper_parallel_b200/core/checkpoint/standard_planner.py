@@ -68,7 +68,8 @@ class StandardSavePlanner(SavePlanner):
             for it in plan.items:
                 if it.type == WriteItemType.BYTE_IO:
                     md.setdefault(it.index.fqn, BytesStorageMetadata())
-                    new_items.append(WriteItem(MetadataIndex(it.index.fqn, (), r), it.type))
+                    # keyed without a chunk index, as the reference's reader looks it up
+                    new_items.append(WriteItem(MetadataIndex(it.index.fqn, (), None), it.type))
                     continue
                 td = it.tensor_data
                 entry = md.get(it.index.fqn)

@@ -93,6 +93,12 @@ def test_metadata_pickle_names_reference_modules_and_reads_back(tmp_path):
     ckpt.save(sd, checkpoint_id=str(tmp_path), no_dist=True)
     raw = open(tmp_path / ".metadata", "rb").read()
     assert b"hyper_parallel.core.checkpoint.metadata" in raw       # readable by the reference
+    md = ckpt.FileSystemReader(str(tmp_path)).load_metadata()
+    keys = {k.fqn: k for k in md.storage_data}
+    # the reference's reader looks a pickled (non-tensor) entry up without a chunk index, a tensor chunk
+    # with its position in the chunk list
+    assert keys["meta.epoch"].index is None and tuple(keys["meta.epoch"].offset) == ()
+    assert keys["a"].index == 0 and tuple(keys["a"].offset) == (0, 0)
     out = {"a": torch.zeros(2, 3), "meta": {"epoch": 0}}
     ckpt.load(out, checkpoint_id=str(tmp_path), no_dist=True)
     assert torch.equal(out["a"], sd["a"]) and out["meta"]["epoch"] == 3
