@@ -72,7 +72,9 @@ def destroy_process_group(group=None) -> None:
     if not is_initialized():
         return
     if group is None:
+        global _SELF_GROUP
         _GROUP_CACHE.clear()
+        _SELF_GROUP = None
         dist.destroy_process_group()
     else:
         for k, v in list(_GROUP_CACHE.items()):
@@ -122,6 +124,22 @@ def group_for_ranks(ranks: Sequence[int], timeout=None, pg_options=None, group_d
         grp = dist.new_group(list(ranks_key), use_local_synchronization=True, **kwargs)
     _GROUP_CACHE[key] = grp
     return grp
+
+
+_SELF_GROUP = None
+
+
+def self_group():
+    """A process group whose only member is this rank.  ``None`` means "the world" to
+    ``torch.distributed``, so a mesh axis of size one must not hand out ``None`` to callers that pass
+    it on to ``dist.*``; this package's own collectives treat the group like ``None`` (size 1 = no-op)."""
+    global _SELF_GROUP
+    if _SELF_GROUP is None and is_initialized():
+        if dist.get_world_size() == 1:
+            _SELF_GROUP = dist.group.WORLD
+        else:
+            _SELF_GROUP = dist.new_group([dist.get_rank()], use_local_synchronization=True)
+    return _SELF_GROUP
 
 
 def world_collective_groups(specs: Sequence[Tuple[Sequence[int], str]]) -> Dict[Tuple[Tuple[int, ...], str], object]:

@@ -87,7 +87,9 @@ class DeviceMesh:
             self._groups_ready = self._groups_ready or not cc.is_initialized()
             return
         for d in range(self.ndim):
-            self._groups[d] = cc.group_for_ranks(self.get_rank_list_along_axis(d))
+            ranks = self.get_rank_list_along_axis(d)
+            # an axis of size one gets a real one-member group: ``None`` would mean the world
+            self._groups[d] = cc.group_for_ranks(ranks) if len(ranks) > 1 else cc.self_group()
         self._groups_ready = True
 
     def get_rank_list_along_axis(self, dim: Union[int, str]) -> List[int]:

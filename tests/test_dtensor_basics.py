@@ -212,6 +212,22 @@ def process_groups_and_split_group(rank):
 
 
 @case
+def size_one_mesh_axis_has_a_group_of_its_own(rank):
+    """``None`` means "the world" to torch.distributed: an axis of size one must hand out a real
+    one-member group, on the mesh and on its sub-mesh."""
+    import torch.distributed as dist
+    mesh = _mesh((1, 8), ("dp", "tp"))
+    for group in (mesh.get_group("dp"), mesh["dp"].get_group()):
+        assert group is not None and dist.get_process_group_ranks(group) == [rank]
+        t = torch.ones(1) * rank
+        dist.all_reduce(t, group=group)
+        assert t.item() == rank
+    t = torch.ones(1)
+    dist.all_reduce(t, group=mesh.get_group("tp"))
+    assert t.item() == 8
+
+
+@case
 def rng_tracker_construction_and_switch(rank):
     from hyper_parallel_b200.core.random import OffsetBasedRNGTracker, is_rng_supported_mesh
     assert is_rng_supported_mesh()
