@@ -218,12 +218,16 @@ def test_shipped_examples_parse_and_search(tmp_path):
     assert (mf.num_layers, mf.hidden_size, mf.ffn_hidden_size, mf.world_size, mf.global_batch_size) == (40, 5120, 13824, 8, 8)
     mg = tcfg.model_from_shell(os.path.join(ex, "moe_megatron.sh"))
     assert (mg.num_layers, mg.hidden_size, mg.expert_num, mg.num_kv_heads, mg.first_k_dense) == (24, 4096, 32, 8, 2)
-    for setup, pp_expected in (("args_for_parallel_tool.json", True), ("args_for_moe_search.json", True)):
-        cfg = TunerConfig.from_json(os.path.join(ex, setup))
-        cfg.output_path = str(tmp_path / setup[:-5])
-        ranked = taylor_search_tool(cfg, top_k=5)
-        assert ranked and "step_time_us" in ranked[0]
-        assert os.path.exists(os.path.join(cfg.output_path, "pipeline_output", "ranked_configs.csv"))
+    cfg = TunerConfig.from_json(os.path.join(ex, "args_for_parallel_tool.json"))
+    cfg.output_path = str(tmp_path / "dense")
+    ranked = taylor_search_tool(cfg, top_k=5)
+    assert ranked and "step_time_us" in ranked[0]
+    assert os.path.exists(os.path.join(cfg.output_path, "pipeline_output", "ranked_configs.csv"))
+    moe = TunerConfig.from_json(os.path.join(ex, "args_for_moe_search.json"))
+    moe.output_path, moe.alg_phase = str(tmp_path / "moe"), 1            # the pruning phases only: 32 ranks, EP on
+    summary = taylor_search_tool(moe)[0]["summary"]
+    assert summary["initial"] > summary["after_expert_rules"] >= summary["after_memory"] > 0
+    assert os.path.exists(os.path.join(moe.output_path, "nd_candidate_config.csv"))
 
 
 def test_memory_model_is_refitted_from_measured_peaks():
