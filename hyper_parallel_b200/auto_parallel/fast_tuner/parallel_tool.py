@@ -75,6 +75,15 @@ def rank_candidates(space: List[Config], spec: ModelSpec, cfg: TunerConfig, hw: 
     lp = lp or LayerProfile(dense_fw=1.0, dense_bw=2.0, moe_fw=1.0, moe_bw=2.0)
     ranked = []
     scored = sorted(space, key=lambda c: estimate_step_time(spec, c, hw))[: max(top_k * 5, 50)]
+    memo = {}                                   # many candidates share (stages, chunks, micro-batches)
+
+    def balanced(pp, vp, micro, max_offset=None):
+        key = (pp, vp, micro, max_offset)
+        if key not in memo:
+            kw = {} if max_offset is None else {"max_offset": max_offset}
+            memo[key] = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, micro, lp, **kw)
+        return memo[key]
+
     for c in scored:
         t = estimate_step_time(spec, c, hw)
         pp, vp = pp_of(c), vp_of(c)
@@ -82,10 +91,10 @@ def rank_candidates(space: List[Config], spec: ModelSpec, cfg: TunerConfig, hw: 
                  "mbs": mbs_of(c), "sp": sp_of(c), "step_time_us": t * 1e6}
         if pp > 1:
             micro = max(cfg.gbs // (dp_of(c) * mbs_of(c)), 1)
-            bal = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp)
+            bal = balanced(pp, vp, min(micro, 4 * pp))
             entry.update({"layers": bal.layers, "offset": bal.offset, "recompute": bal.recompute,
                           "select_recompute": bal.select_recompute, "bubble": round(bal.bubble_ratio, 4)})
-            even = balance_pipeline(spec.num_layers, spec.dense_layers, pp, vp, min(micro, 4 * pp), lp, max_offset=0)
+            even = balanced(pp, vp, min(micro, 4 * pp), 0)
             entry["step_time_us"] = t * 1e6 * bal.makespan / max(even.makespan, 1e-9)
         ranked.append(entry)
     ranked.sort(key=lambda e: e["step_time_us"])
