@@ -134,10 +134,17 @@ def test_layout_json_and_single_file_helpers(tmp_path):
     layout = Layout((1, 1), ("dp", "tp"), init_backend=False)
     lin = torch.nn.Linear(4, 4)
     lin.weight = torch.nn.Parameter(distribute_tensor(lin.weight.detach(), layout("None", "tp")))
-    cur = ckpt.get_current_layout(lin)
-    assert cur["weight"]["tensor_map"] == [-1, 0] and cur["weight"]["alias_name"] == ["dp", "tp"]
+    cur = ckpt.get_current_layout(lin)                      # keyed by rank id, then by parameter, as the reference's
+    w = cur["0"]["weight"]
+    assert w["tensor_map"] == [-1, 0] and w["alias_name"] == ["dp", "tp"]
+    assert w["type"] == "torch.float32" and w["full_shape"] == [4, 4] and "bias" not in cur["0"]
+    assert ckpt.get_global_layout(lin) == cur                # no process group: this rank alone
     ckpt.save_layout(cur, str(tmp_path / "rank0.layout"))
-    assert ckpt.combine_layout(str(tmp_path))["rank0"] == cur
+    ckpt.save_layout({"1": cur["0"]}, str(tmp_path / "rank1.layout"))
+    assert ckpt.combine_layout(str(tmp_path)) == {"0": cur["0"], "1": cur["0"]}
+    ckpt.save_layout(cur, str(tmp_path / "again.layout"))
+    with pytest.raises(ValueError):
+        ckpt.combine_layout(str(tmp_path))                   # rank 0 twice
     ckpt.save_checkpoint({"x": torch.ones(2)}, str(tmp_path / "one.pt"))
     assert torch.equal(ckpt.load_checkpoint(str(tmp_path / "one.pt"))["x"], torch.ones(2))
     with pytest.raises(ValueError):
