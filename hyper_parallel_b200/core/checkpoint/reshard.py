@@ -5,7 +5,7 @@ slice that ``to_rank_id`` owns under ``to_layout``.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
@@ -36,49 +36,78 @@ def infer_intersection(area_a, area_b):
 
 
 class ReshardHandler:
-    """Plans and performs the conversion of one parameter from ``from_layout`` to ``to_layout``."""
+    """Plans and performs the conversion of one parameter from ``from_layout`` to ``to_layout`` offline
+    (numpy arrays or torch tensors, no process group).  Contract of the reference's class
+    (core/checkpoint/reshard.py:190-398 there): ``infer_all_tensor_offset()`` names, per source rank
+    that holds a needed and not redundant piece, the area of that piece *inside the source rank's
+    shard*; the caller cuts those pieces out and hands them to ``get_real_tensor``, which places them
+    into the target rank's shard.  A layout of ``None`` means the whole tensor on rank 0.  Beyond the
+    reference, ``get_real_tensor`` also accepts the source ranks' whole shards and cuts the pieces
+    itself."""
 
-    def __init__(self, param_name: str, full_shape, from_layout: Layout, to_layout: Layout, to_rank_id: int):
+    def __init__(self, param_name: str, full_shape, from_layout: Optional[Layout], to_layout: Optional[Layout],
+                 to_rank_id: int):
+        if from_layout is None and to_layout is None:
+            raise ValueError("`from_layout` and `to_layout` cannot both be None.")
         self.param_name = param_name
-        self.full_shape = tuple(full_shape)
+        self.full_shape = tuple(int(s) for s in full_shape)
         self.from_layout, self.to_layout = from_layout, to_layout
-        self.to_rank_id = to_rank_id
-        for lay in (from_layout, to_layout):
+
+        def unpack(lay):
+            if lay is None:
+                return (1,), tuple(-1 for _ in self.full_shape), [0]
             if lay.tensor_map is None:
                 lay.placement_to_tensor_map(len(self.full_shape))
-        self.to_area = infer_slice_area_by_rank(to_layout.mesh_shape, to_layout.tensor_map,
-                                                to_layout.rank_list.index(to_rank_id), self.full_shape)
+            return tuple(lay.mesh_shape), tuple(lay.tensor_map), [int(r) for r in lay.rank_list]
+        self.from_mesh_shape, self.from_tensor_map, self.from_rank_list = unpack(from_layout)
+        self.to_mesh_shape, self.to_tensor_map, self.to_rank_list = unpack(to_layout)
+        self.to_rank_id = 0 if to_layout is None else int(to_rank_id)
+        if self.to_rank_id not in self.to_rank_list:
+            raise ValueError("Input to_rank_id is not in to_rank_list.")
+        self.to_area = infer_slice_area_by_rank(self.to_mesh_shape, self.to_tensor_map,
+                                                self.to_rank_list.index(self.to_rank_id), self.full_shape)
+        self.global_union_area_map: Dict[int, tuple] = {}     # source rank -> area of its piece in the full tensor
+        self._from_area: Dict[int, tuple] = {}                 # source rank -> area of its whole shard
 
-    def infer_all_tensor_offset(self) -> Dict[int, Tuple[list, list]]:
-        """``{source rank: (slice inside the source shard, slice inside the target shard)}`` --
-        one entry per distinct source slice (replicas are taken from the lowest rank)."""
+    def infer_all_tensor_offset(self) -> Dict[int, tuple]:
+        """``{source rank: ((begin, end) per dim) inside that rank's shard}``: one entry per distinct
+        source slice that overlaps the target shard (replicas are taken from the lowest rank)."""
         seen, out = set(), {}
-        for inner, rank in enumerate(self.from_layout.rank_list):
-            src = infer_slice_area_by_rank(self.from_layout.mesh_shape, self.from_layout.tensor_map, inner,
-                                           self.full_shape)
-            key = tuple(src)
-            if key in seen:
+        self.global_union_area_map.clear()
+        self._from_area.clear()
+        for inner, rank in enumerate(self.from_rank_list):
+            src = tuple(infer_slice_area_by_rank(self.from_mesh_shape, self.from_tensor_map, inner, self.full_shape))
+            if src in seen:
                 continue
+            seen.add(src)
             hit = infer_intersection(src, self.to_area)
             if hit is None:
                 continue
-            seen.add(key)
-            in_src = [(s - a0, e - a0) for (s, e), (a0, _) in zip(hit, src)]
-            in_dst = [(s - b0, e - b0) for (s, e), (b0, _) in zip(hit, self.to_area)]
-            out[rank] = (in_src, in_dst)
+            self.global_union_area_map[rank] = tuple(hit)
+            self._from_area[rank] = src
+            out[rank] = tuple((s - a0, e - a0) for (s, e), (a0, _) in zip(hit, src))
         return out
 
     def get_real_tensor(self, from_tensor_map: Dict[int, "np.ndarray"]):
-        """Assemble the target shard from ``{source rank: source shard}``."""
-        plan = self.infer_all_tensor_offset()
+        """The target rank's shard, assembled from ``{source rank: piece}`` (or ``{source rank: whole
+        shard}``).  ``ValueError`` when a needed piece is missing or has neither of the two shapes."""
+        if not from_tensor_map:
+            raise ValueError("Input from_tensor_map cannot be empty")
+        local = self.infer_all_tensor_offset()
         first = next(iter(from_tensor_map.values()))
         shape = [e - b for b, e in self.to_area]
-        is_torch = hasattr(first, "new_empty")
-        dst = first.new_empty(shape) if is_torch else np.empty(shape, dtype=first.dtype)
-        for rank, (in_src, in_dst) in plan.items():
+        dst = first.new_zeros(shape) if hasattr(first, "new_zeros") else np.zeros(shape, dtype=first.dtype)
+        for rank, area in self.global_union_area_map.items():
             if rank not in from_tensor_map:
-                raise KeyError(f"{self.param_name}: shard of source rank {rank} is required but missing")
-            s = tuple(slice(b, e) for b, e in in_src)
-            d = tuple(slice(b, e) for b, e in in_dst)
-            dst[d] = from_tensor_map[rank][s]
+                raise ValueError(f"{self.param_name}: missing slice data from rank {rank}; provide every slice that "
+                                 "infer_all_tensor_offset names")
+            piece = from_tensor_map[rank]
+            want = tuple(e - b for b, e in area)
+            whole = tuple(e - b for b, e in self._from_area[rank])
+            if tuple(piece.shape) != want:
+                if tuple(piece.shape) != whole:
+                    raise ValueError(f"{self.param_name}: slice from rank {rank} has incorrect shape. Expected {want} "
+                                     f"(or the whole shard {whole}), got {tuple(piece.shape)}.")
+                piece = piece[tuple(slice(b, e) for b, e in local[rank])]
+            dst[tuple(slice(b - t0, e - t0) for (b, e), (t0, _) in zip(area, self.to_area))] = piece
         return dst

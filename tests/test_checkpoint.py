@@ -123,6 +123,24 @@ def test_reshard_handler_and_slice_area():
         got = h.get_real_tensor(shards)
         a = infer_slice_area_by_rank(dst.mesh_shape, dst.tensor_map, r, full.shape)
         assert np.array_equal(got, full[tuple(slice(b, e) for b, e in a)])
+    # the reference's contract: the caller cuts the named pieces out of the source shards itself
+    h = ReshardHandler("w", full.shape, src, dst, 2)
+    need = h.infer_all_tensor_offset()
+    assert need == {2: ((0, 2), (0, 6)), 3: ((0, 2), (0, 6))}                 # rows 4..5 of the shards of ranks 2, 3
+    pieces = {r: shards[r][tuple(slice(b, e) for b, e in a)] for r, a in need.items()}
+    assert np.array_equal(h.get_real_tensor(pieces), full[4:6])
+    with pytest.raises(ValueError):
+        h.get_real_tensor({2: pieces[2]})                                      # a needed piece is missing
+    with pytest.raises(ValueError):
+        h.get_real_tensor({2: pieces[2][:1], 3: pieces[3]})                    # neither the piece nor the shard
+    # None = the whole tensor on rank 0, on either side
+    assert np.array_equal(ReshardHandler("w", full.shape, src, None, 0).get_real_tensor(shards), full)
+    part = ReshardHandler("w", full.shape, None, dst, 3).get_real_tensor({0: full})
+    assert np.array_equal(part, full[6:8])
+    t = ReshardHandler("w", full.shape, None, dst, 1).get_real_tensor({0: torch.from_numpy(full)})
+    assert isinstance(t, torch.Tensor) and torch.equal(t, torch.from_numpy(full[2:4]))
+    with pytest.raises(ValueError):
+        ReshardHandler("w", full.shape, None, None, 0)
     assert infer_intersection([(0, 4), (0, 4)], [(4, 8), (0, 4)]) is None
     with pytest.raises(ValueError):
         infer_slice_area_by_rank((2, 2), (1, 0), 0, (7, 12))
