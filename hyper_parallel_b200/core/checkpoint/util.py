@@ -2,7 +2,8 @@
 from __future__ import annotations
 
 import os
-from typing import Dict, List, Sequence, Tuple
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -23,17 +24,28 @@ def str_to_dtype(name: str) -> torch.dtype:
     return _DTYPE_NAMES[name]
 
 
-def check_file_name(path: str, suffixes: Sequence[str] = (".safetensors", ".pt", ".ckpt")) -> str:
-    """Validate a single-file checkpoint path (no traversal, known suffix, parent exists)."""
+def has_valid_filename(path) -> bool:
+    """The reference's rule (core/checkpoint/util.py:49-70 there): a file name with a stem and a suffix,
+    each containing at least one letter."""
+    p = Path(path)
+    return bool(p.name and p.stem and len(p.suffix) > 1 and any(c.isalpha() for c in p.stem)
+                and any(c.isalpha() for c in p.suffix[1:]))
+
+
+def check_file_name(path, suffixes: Optional[Sequence[str]] = None) -> str:
+    """Validate a single-file checkpoint path (a ``str`` or ``Path``) and return it as an absolute string;
+    the parent directory is created when missing.  ``suffixes`` restricts the extension when given."""
+    if isinstance(path, Path):
+        path = str(path)
     if not isinstance(path, str) or not path:
-        raise ValueError("checkpoint file path must be a non-empty string")
+        raise ValueError("checkpoint file path must be a non-empty string or Path")
     if "\x00" in path:
         raise ValueError("checkpoint file path contains a NUL byte")
-    if not path.endswith(tuple(suffixes)):
+    if not has_valid_filename(path):
+        raise ValueError(f"Saver file_path should contains valid filename but get: {path}")
+    if suffixes is not None and not path.endswith(tuple(suffixes)):
         raise ValueError(f"checkpoint file must end with one of {tuple(suffixes)}, got {path!r}")
-    parent = os.path.dirname(os.path.abspath(path))
-    if not os.path.isdir(parent):
-        raise ValueError(f"directory {parent!r} does not exist")
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     return os.path.abspath(path)
 
 

@@ -165,8 +165,12 @@ def test_layout_json_and_single_file_helpers(tmp_path):
         ckpt.combine_layout(str(tmp_path))                   # rank 0 twice
     ckpt.save_checkpoint({"x": torch.ones(2)}, str(tmp_path / "one.pt"))
     assert torch.equal(ckpt.load_checkpoint(str(tmp_path / "one.pt"))["x"], torch.ones(2))
-    with pytest.raises(ValueError):
-        ckpt.save_checkpoint({}, str(tmp_path / "bad.txt"))
+    # the reference's file-name rule: a stem and a suffix with a letter each; missing folders are created
+    ckpt.save_checkpoint({"x": torch.zeros(1)}, tmp_path / "new_folder" / "model_1.safetensors")
+    assert (tmp_path / "new_folder" / "model_1.safetensors").exists()
+    for bad in ("noext", "1234.5", ".hidden", "name.123"):
+        with pytest.raises(ValueError):
+            ckpt.save_checkpoint({}, str(tmp_path / bad))
 
 
 def _async_save_worker(rank, world, ckpt):
