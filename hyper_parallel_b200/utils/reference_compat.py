@@ -147,6 +147,18 @@ def run_function(out_root: str, path: str, fn: str, world: int, timeout: float =
     return ok, (first if not ok else None)
 
 
+def run_unittest_file(out_root: str, path: str) -> int:
+    """Files made of ``unittest.TestCase`` classes (pure-Python unit tests, no ranks): run them in this
+    process; returns the number of failures and errors."""
+    import importlib
+    import unittest
+    sys.path.insert(0, out_root)
+    module = importlib.import_module(os.path.relpath(path, out_root)[:-3].replace(os.sep, "."))
+    suite = unittest.defaultTestLoader.loadTestsFromModule(module)
+    result = unittest.TextTestRunner(verbosity=1).run(suite)
+    return len(result.failures) + len(result.errors)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--root", required=True, help="checkout of the reference project (the folder holding tests/)")
@@ -158,7 +170,10 @@ def main(argv=None) -> int:
     failed = 0
     with tempfile.TemporaryDirectory(prefix="hpb_compat_") as out_root:
         path = prepare(ns.root, ns.file, out_root)
-        for fn in ([ns.function] if ns.function else list_test_functions(os.path.join(ns.root, ns.file))):
+        functions = [ns.function] if ns.function else list_test_functions(os.path.join(ns.root, ns.file))
+        if not functions:                                   # unittest classes only
+            return 1 if run_unittest_file(out_root, path) else 0
+        for fn in functions:
             ok, tb = run_function(out_root, path, fn, ns.world, ns.timeout)
             print(("PASS " if ok else "FAIL ") + f"{ns.file}::{fn}", flush=True)
             if not ok:
