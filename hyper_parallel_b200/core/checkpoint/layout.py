@@ -48,9 +48,7 @@ def get_global_layout(cell) -> Dict[str, Dict[str, dict]]:
 
 
 def save_layout(layout_dict: dict, path: str) -> None:
-    if not str(path).endswith(".layout"):
-        raise ValueError("layout files must end with .layout")
-    path = str(path)
+    path = str(path)              # any name is accepted; ``combine_layout`` reads the ``*.layout`` files of a folder
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     tmp = path + ".tmp"
     with open(tmp, "w", encoding="utf-8") as f:
