@@ -35,10 +35,16 @@ def no_partial(like: Layout) -> List[Optional[str]]:
 
 
 def split_shapes(extra_args) -> Tuple[list, Optional[list]]:
-    """Separate the trailing input-shape list (``WithShape`` convention) from the scalars."""
-    if extra_args and isinstance(extra_args[-1], list) and all(
-            s is None or isinstance(s, tuple) for s in extra_args[-1]):
-        return list(extra_args[:-1]), extra_args[-1]
+    """Separate the trailing input-shape list (``WithShape`` convention) from the scalars.  A shape may
+    be a tuple, a ``torch.Size`` or a list of ints; ``None`` stands for a non-tensor input."""
+    if isinstance(extra_args, dict):                       # {"input_shapes": [...]}: an older spelling
+        shapes = extra_args.get("input_shapes")
+        rest = [v for k, v in extra_args.items() if k != "input_shapes"]
+        return rest, ([None if s is None else tuple(s) for s in shapes] if shapes is not None else None)
+    if extra_args and isinstance(extra_args[-1], list) and extra_args[-1] and all(
+            s is None or (isinstance(s, (tuple, list)) and all(isinstance(i, int) for i in s))
+            for s in extra_args[-1]):
+        return list(extra_args[:-1]), [None if s is None else tuple(s) for s in extra_args[-1]]
     return list(extra_args), None
 
 

@@ -121,6 +121,12 @@ class ReshapeDistributedOp(DistributedOp):
 
     def infer_layout(self, layouts, extra_args):
         x = layouts[0]
+        if (len(extra_args) == 2 and all(isinstance(a, (tuple, list)) and a and all(isinstance(i, int) for i in a)
+                                         for a in extra_args)):
+            # the reference's "Reshape" form, for code that calls the rule directly:
+            # (target shape, global input shape) -> (layout, local target shape)
+            out_axes, local = infer_reshape(self.op_name, x, tuple(extra_args[1]), list(extra_args[0]))
+            return make(x, out_axes, x.partial), list(local)
         extra, shapes = split_shapes(extra_args)
         in_shape = shapes[0]
         target = self._target(extra, in_shape)
