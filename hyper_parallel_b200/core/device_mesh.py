@@ -115,6 +115,37 @@ class DeviceMesh:
     def get_comm_group_by_axis(self, dim):
         return self.get_group(dim)
 
+    # names of the reference's helpers (core/device_mesh.py:320-327, 751-769, 905-969 there)
+    def axis_index(self, axis: str) -> int:
+        """Position of the named dim in ``mesh_shape``."""
+        if axis not in self._dim_names:
+            raise ValueError(f"The axis name must be one of mesh dim names {self._dim_names}, but got {axis}")
+        return self._dim_names.index(axis)
+
+    def axis_id(self, axis: str) -> int:
+        """The number a ``tensor_map`` uses for the named dim (dims count from the last one; "None" is -1)."""
+        if axis == "None":
+            return -1
+        return self.ndim - 1 - self.axis_index(axis)
+
+    def get_devices_for_axis(self, mesh_dim: Union[str, int], rank: int) -> List[int]:
+        """Ranks that differ from ``rank`` only in mesh dimension ``mesh_dim`` (any member rank)."""
+        if isinstance(mesh_dim, str) and mesh_dim not in self._dim_names:
+            raise ValueError(f"mesh_dim '{mesh_dim}' not found in mesh_dim_names {self._dim_names}")
+        if not isinstance(mesh_dim, str) and not 0 <= int(mesh_dim) < self.ndim:
+            raise ValueError(f"mesh_dim {mesh_dim} can not out of range [0, {self.ndim})")
+        d = self._dim_index(mesh_dim)
+        idx = list(self.coordinate_of(int(rank)))
+        idx[d] = slice(None)
+        return [int(r) for r in self._mesh[tuple(idx)]]
+
+    def get_flatten_mapping(self) -> Dict[str, "DeviceMesh"]:
+        """``{name: 1-D mesh}`` of the ``flatten()`` calls registered on this (root) mesh."""
+        return self.root_mesh._flatten_cache
+
+    def add_flatten_mapping(self, name: str, mesh: "DeviceMesh") -> None:
+        self.root_mesh._flatten_cache[name] = mesh
+
     # ----------------------------------------------------------- queries --
     def _dim_index(self, dim: Union[int, str]) -> int:
         if isinstance(dim, str):
@@ -223,6 +254,8 @@ class DeviceMesh:
         names = tuple(names)
         if names in self._sub_cache:
             return self._sub_cache[names]
+        if len(names) == 1 and names[0] not in self._dim_names and names[0] in self.root_mesh._flatten_cache:
+            return self.root_mesh._flatten_cache[names[0]]        # the name of an earlier ``flatten()``
         dims = [self._dim_index(n) for n in names]
         if len(set(dims)) != len(dims):
             raise KeyError(f"duplicate mesh dims in {names}")

@@ -149,3 +149,18 @@ def test_groups_from_template_tile_the_world_like_mesh_axes():
     for bad, world in (([0, 1, 3], 8), ([0, 2], 6), ([0, 0], 4), ([0, 4], 4)):
         with pytest.raises(ValueError):
             groups(bad, world)
+
+
+def test_device_mesh_helper_names_of_the_reference():
+    clear_mesh_cache()
+    m = DeviceMesh("cpu", (2, 2, 2), mesh_dim_names=("dp", "cp", "tp"), rank_list=range(8), _init_backend=False, _rank=5)
+    assert (m.axis_index("dp"), m.axis_index("tp")) == (0, 2)
+    assert (m.axis_id("dp"), m.axis_id("tp"), m.axis_id("None")) == (2, 0, -1)        # tensor_map numbering
+    assert m.get_devices_for_axis("cp", 0) == [0, 2] and m.get_devices_for_axis(2, 6) == [6, 7]
+    flat = m["dp", "cp"].flatten("dp_cp")
+    assert flat.rank_list == (1, 3, 5, 7) and m["dp_cp"] is flat and m.get_flatten_mapping() == {"dp_cp": flat}
+    with pytest.raises(ValueError):
+        m.axis_index("xx")
+    with pytest.raises(ValueError):
+        m.get_devices_for_axis(3, 0)
+    clear_mesh_cache()
