@@ -138,6 +138,12 @@ class SwapTensor:
         return t
 
 
+# the reference's method names (core/activation_checkpoint/swap.py:51-131 there)
+SwapTensor.async_offload = SwapTensor.launch_offload
+SwapTensor.async_load = SwapTensor.launch_load
+SwapTensor.get_val = SwapTensor.get
+
+
 class SwapGroup:
     """The swap tensors that belong to one layer."""
 
@@ -191,6 +197,39 @@ class SwapManager:
         if self.current is not None:
             self.group_of(self.current).add(st)
 
+    # Groups driven by hand under a name of the caller's choosing -- the reference's manual interface
+    # (core/activation_checkpoint/swap.py:267-309 there): collect tensors with ``add_storage``, then
+    # ``launch_offload`` / ``wait_offload`` after the forward and ``launch_load`` / ``wait_load`` before
+    # the backward of the layer they belong to.
+    def _named(self, group_name: str, create: bool = False) -> SwapGroup:
+        named = self.__dict__.setdefault("named_groups", {})
+        if group_name not in named:
+            if not create:
+                raise RuntimeError(f"Group {group_name} does not exist.")
+            named[group_name] = SwapGroup(group_name)
+        return named[group_name]
+
+    def add_storage(self, group_name: str, storage) -> None:
+        self._named(group_name, create=True).add(storage.swap_tensor if isinstance(storage, Storage) else storage)
+
+    def launch_offload(self, group_name: str, copy_stream=None) -> None:
+        self._named(group_name).launch_offload()
+
+    def wait_offload(self, group_name: str) -> None:
+        self._named(group_name).wait_offload()
+
+    def launch_load(self, group_name: str, copy_stream=None) -> None:
+        self._named(group_name).launch_load()
+
+    def wait_load(self, group_name: str) -> None:
+        self._named(group_name).wait_load()
+
+    def get_current_group_name(self) -> str:
+        return self.__dict__.get("current_group_name", "")
+
+    def set_current_group_name(self, group_name: str) -> None:
+        self.__dict__["current_group_name"] = group_name
+
     def set_forward_prefetch_layer(self, layer, next_layer) -> None:
         """Overlap ``layer``'s offload with ``next_layer``'s forward and its reload with
         ``next_layer``'s backward."""
@@ -226,3 +265,5 @@ class SwapManager:
         self.groups.clear()
         self._prev_of.clear()
         self.current = None
+        self.__dict__.pop("named_groups", None)
+        self.__dict__.pop("current_group_name", None)

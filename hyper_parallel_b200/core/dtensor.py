@@ -175,6 +175,13 @@ class DTensor(torch.Tensor):
             value = value._local_tensor
         self._local_tensor.grad = value
 
+    def grad_zero_(self):
+        """Zero the local gradient in place (reference platform/torch/dtensor.py:108-111)."""
+        if self._local_tensor.grad is not None:
+            g = self._local_tensor.grad
+            (g._local_tensor if isinstance(g, DTensor) else g).zero_()
+        return self
+
     @property
     def requires_grad(self) -> bool:
         return self._local_tensor.requires_grad

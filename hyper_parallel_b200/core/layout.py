@@ -363,6 +363,30 @@ class Layout:
             used *= self._mesh.mesh_shape[a]
         return self._mesh.size() // used
 
+    # helper names of the reference's Layout (core/layout.py:447-468, 483-495, 550-580 there)
+    def is_dev_axis_apply_shard(self, axis: str) -> bool:
+        """Whether the named mesh axis shards some tensor dim."""
+        a = self._axis_index(axis)
+        return any(a in axes for axes in (self.dim_axes or ()))
+
+    def get_dev_axis_apply_shard_axis(self, axis: str) -> Optional[int]:
+        """The tensor dim that the named mesh axis shards, or ``None``."""
+        a = self._axis_index(axis)
+        for d, axes in enumerate(self.dim_axes or ()):
+            if a in axes:
+                return d
+        return None
+
+    def get_devices_for_axis(self, axis, rank: int):
+        """Ranks that differ from ``rank`` only along the named mesh axis."""
+        return self._mesh.get_devices_for_axis(axis, rank)
+
+    def to_string(self) -> str:
+        """A multi-line dump: mesh shape, axis names, rank list, Partial status and tensor map."""
+        tm = "Not configured" if self._dim_axes is None else str(tuple(self.alias_tensor_map))
+        return "\n".join((f"Mesh shape: {tuple(self.mesh_shape)}", f"Alias Names: {tuple(self.alias_name)}",
+                          f"Rank List: {list(self.rank_list)}", f"Partial: {list(self.partial)}", f"Tensor Map: {tm}"))
+
     def get_comm_group_by_axis(self, axis):
         return self._mesh.get_group(self._axis_index(axis))
 

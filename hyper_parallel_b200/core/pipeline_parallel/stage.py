@@ -136,6 +136,8 @@ class PipelineStage:
         self._pending_sends: list = []
 
     # ------------------------------------------------------------------ p2p --
+    clear_states = clear_cache          # the reference's name (core/pipeline_parallel/stage.py:115-118)
+
     def _dev(self):
         if self.device is not None:
             return torch.device(self.device)

@@ -1,6 +1,7 @@
 """Activation checkpoint / swap: identical losses and gradients with and without it (CPU)."""
 import copy
 
+import pytest
 import torch
 from torch import nn
 
@@ -130,3 +131,30 @@ def test_swap_policy_may_answer_with_the_enum_or_a_bool():
     x = torch.randn(32, 64, requires_grad=True)
     net(x).sum().backward()
     assert seen and x.grad is not None
+
+
+def test_swap_manager_manual_interface_by_group_name():
+    """Collect tensors under a name, offload / reload the group by hand; on CPU the copies are no-ops but
+    the state machine and the method names are those of the reference's manager."""
+    from hyper_parallel_b200.core.activation_checkpoint import Storage, SwapManager, SwapTensor
+    mgr = SwapManager()
+    mgr.reset()
+    a, b = torch.randn(64, 64), torch.randn(32)
+    sa, sb = SwapTensor(a), SwapTensor(b)
+    mgr.add_storage("layer0", Storage(sa))
+    mgr.add_storage("layer0", sb)
+    mgr.set_current_group_name("layer0")
+    assert mgr.get_current_group_name() == "layer0"
+    mgr.launch_offload("layer0")
+    mgr.wait_offload("layer0")
+    mgr.launch_load("layer0")
+    mgr.wait_load("layer0")
+    assert torch.equal(sa.get_val(), a) and torch.equal(sb.get(), b)
+    sa.async_offload()
+    sa.wait_offload()
+    sa.async_load()
+    assert torch.equal(sa.wait_load(), a)
+    with pytest.raises(RuntimeError):
+        mgr.launch_offload("no such group")
+    mgr.reset()
+    assert mgr.get_current_group_name() == ""
