@@ -4,8 +4,9 @@ from .layout import combine_layout, get_current_layout, get_global_layout, load_
 from .loader import load_checkpoint  # noqa: F401
 from .metadata import (BytesStorageMetadata, ChunkStorageMetadata, Metadata, MetadataIndex,  # noqa: F401
                        TensorProperties, TensorStorageMetadata)
-from .planner import LoadPlan, LoadPlanner, ReadItem, SavePlan, SavePlanner, WriteItem  # noqa: F401
+from .planner import (LoadItemType, LoadPlan, LoadPlanner, ReadItem, SavePlan, SavePlanner, WriteItem,  # noqa: F401
+                      WriteItemType)
 from .reshard import ReshardHandler, infer_intersection, infer_slice_area_by_rank  # noqa: F401
 from .saver import save_checkpoint  # noqa: F401
 from .standard_planner import StandardLoadPlanner, StandardSavePlanner  # noqa: F401
-from .storage import StorageInfo  # noqa: F401
+from .storage import StorageInfo, StorageReader, StorageWriter, WriteResult  # noqa: F401

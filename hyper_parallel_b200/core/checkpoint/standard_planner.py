@@ -195,3 +195,21 @@ class StandardLoadPlanner(LoadPlanner):
 
     def commit_tensor(self, read_item, tensor) -> None:
         pass
+
+
+def create_read_items_for_chunk_list(fqn: str, checkpoint_md, local_chunks) -> List[ReadItem]:
+    """Read items that fill ``local_chunks`` (what this rank needs) from the saved chunks of
+    ``checkpoint_md``: one item per overlap, with offsets inside the destination chunk and inside the
+    saved chunk (reference standard_planner.py:324-370)."""
+    items: List[ReadItem] = []
+    for li, lc in enumerate(local_chunks or ()):
+        for si, sc in enumerate(checkpoint_md.chunks or ()):
+            hit = _intersect(tuple(lc.offsets), tuple(lc.sizes), tuple(sc.offsets), tuple(sc.sizes))
+            if hit is None:
+                continue
+            lo, ln = hit
+            items.append(ReadItem(LoadItemType.TENSOR, MetadataIndex(fqn, tuple(lc.offsets), li),
+                                  tuple(a - b for a, b in zip(lo, lc.offsets)),
+                                  MetadataIndex(fqn, tuple(sc.offsets), si),
+                                  tuple(a - b for a, b in zip(lo, sc.offsets)), tuple(ln)))
+    return items

@@ -98,3 +98,37 @@ def dedup_plans(plans, save_to_minimum_rank: bool = False):
         items = [it for it in plan.items if keep[(it.index.fqn, it.index.offset)] == r]
         out.append(type(plan)(items=items, storage_data=plan.storage_data, planner_data=plan.planner_data, rank=r))
     return out
+
+
+# ---- helpers for planners written against the reference (its core/checkpoint/util.py:31-235) ----------
+def check_path(path) -> None:
+    """Create the folder ``path`` names -- its parent when ``path`` has a suffix -- unless it exists."""
+    p = Path(path)
+    if p.exists():
+        return
+    (p.parent if p.suffix else p).mkdir(parents=True, exist_ok=True)
+
+
+def narrow_tensor_by_index(tensor, offsets: tuple, lengths: tuple):
+    """``tensor[off : off + len]`` per dimension (the whole tensor when either tuple is empty)."""
+    if not offsets or not lengths:
+        return tensor
+    return tensor[tuple(slice(int(o), int(o) + int(n)) for o, n in zip(offsets, lengths))]
+
+
+def chunk_to_area(chunk) -> Tuple[Tuple[int, int], ...]:
+    """``((start, end), ...)`` of a ``ChunkStorageMetadata``."""
+    return tuple((int(o), int(o) + int(n)) for o, n in zip(chunk.offsets, chunk.sizes))
+
+
+def create_chunk_list_for_tensor(obj) -> list:
+    """The chunks of the global tensor that this rank holds: one for a DTensor (its slice area), the
+    whole tensor for a plain one."""
+    from .metadata import ChunkStorageMetadata
+    _, _, offsets, sizes = local_chunk_of(obj)
+    return [ChunkStorageMetadata(offsets=tuple(offsets), sizes=tuple(sizes))]
+
+
+def remove_redundant_plans(all_plans, save_to_minimum_rank: bool = False):
+    """Keep every duplicated entry in one plan only (the least loaded plan, or the minimum rank)."""
+    return dedup_plans(all_plans, save_to_minimum_rank)

@@ -224,6 +224,13 @@ def fully_shard(module: nn.Module, *, mesh: Optional[DeviceMesh] = None,
     return module
 
 
+def hsdp_sync_stream() -> None:
+    """Wait for every gradient reduction of ``fully_shard`` modules that is still in flight (the root
+    backward callback already does so at the end of ``backward``; reference core/fully_shard/api.py:495-499)."""
+    from .state import _drain
+    _drain(0)
+
+
 def get_model_state_dict(model: nn.Module, *, options: Optional[StateDictOptions] = None) -> Dict[str, Any]:
     """State dict of a ``fully_shard`` model (hyper_parallel/core/fully_shard/api.py:443-490).
 

@@ -254,3 +254,29 @@ def test_hsdp_model_and_optimizer_resume_on_another_rank_count(tmp_path):
     ckpt = str(tmp_path / "hsdp_ckpt")
     run_distributed(_hsdp_resume_worker, 4, ckpt, "save")
     run_distributed(_hsdp_resume_worker, 2, ckpt, "resume")     # resumes sharded 2 ways instead of 4
+
+
+def test_planner_utilities_of_the_reference(tmp_path):
+    """Small helpers that planners written against the reference import: areas of chunks, narrowing, the
+    chunks a rank holds, read items from chunk overlaps, folder creation, exports of the package."""
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    from hyper_parallel_b200.core.checkpoint.standard_planner import create_read_items_for_chunk_list
+    from hyper_parallel_b200.core.checkpoint.util import (check_path, chunk_to_area, create_chunk_list_for_tensor,
+                                                         narrow_tensor_by_index, remove_redundant_plans)
+    t = torch.arange(24).reshape(4, 6)
+    assert narrow_tensor_by_index(t, (1, 2), (2, 3)).tolist() == [[8, 9, 10], [14, 15, 16]]
+    assert narrow_tensor_by_index(t, (), ()) is t
+    assert chunk_to_area(ckpt.ChunkStorageMetadata((1, 2), (2, 3))) == ((1, 3), (2, 5))
+    assert create_chunk_list_for_tensor(t) == [ckpt.ChunkStorageMetadata((0, 0), (4, 6))]
+    md = ckpt.TensorStorageMetadata(ckpt.TensorProperties("torch.int64", False, None), (4, 6),
+                                    [ckpt.ChunkStorageMetadata((0, 0), (2, 6)), ckpt.ChunkStorageMetadata((2, 0), (2, 6))])
+    items = create_read_items_for_chunk_list("w", md, [ckpt.ChunkStorageMetadata((1, 0), (2, 3))])
+    assert [(i.dest_offsets, i.storage_index.index, i.storage_offsets, i.lengths) for i in items] == \
+        [((0, 0), 0, (1, 0), (1, 3)), ((1, 0), 1, (0, 0), (1, 3))]
+    assert all(i.type is ckpt.LoadItemType.TENSOR for i in items)
+    check_path(tmp_path / "a" / "b.txt")
+    check_path(tmp_path / "c")
+    assert (tmp_path / "a").is_dir() and not (tmp_path / "a" / "b.txt").exists() and (tmp_path / "c").is_dir()
+    assert remove_redundant_plans([ckpt.SavePlan(items=[]), ckpt.SavePlan(items=[])]) is not None
+    for name in ("StorageReader", "StorageWriter", "WriteResult", "WriteItemType", "LoadItemType"):
+        assert hasattr(ckpt, name)
