@@ -11,3 +11,15 @@ class ShardedState(enum.Enum):
     SHARDED = enum.auto()
     SHARDED_POST_FORWARD = enum.auto()
     UNSHARDED = enum.auto()
+
+
+class FSDPSchedulerState(enum.Enum):
+    """Where a wrapped module is within one step: its pre-forward hook has run, its post-forward
+    hook has run, its pre-backward hook has run, its post-backward hook has run."""
+    PRE_FORWARD = enum.auto()
+    FORWARD = enum.auto()
+    PRE_BACKWARD = enum.auto()
+    BACKWARD = enum.auto()
+
+
+from ..hsdp.hsdp_utils import GroupInfo, OptimizerLevel  # noqa: E402,F401  (shared with ``hsdp``)
