@@ -209,3 +209,34 @@ def test_reference_compat_runner_rewrites_and_runs_a_reference_style_test(tmp_pa
     assert ok and tb is None
     ok, tb = rc.run_function(str(out), path, "test_that_fails", 2, timeout=120.0)
     assert not ok and "as intended" in tb
+
+
+def test_platform_facade_offers_the_reference_method_names():
+    """Code written against ``get_platform()`` of the reference finds the same helpers here."""
+    from hyper_parallel_b200.platform import get_platform
+    p = get_platform()
+    assert p.ones((2,)).tolist() == [1.0, 1.0] and p.full((1,), 3.0).item() == 3.0 and p.empty((2, 3)).shape == (2, 3)
+    assert p.tensor_type_cast(torch.ones(2), "float16").dtype == torch.float16
+    assert p.cast_fp_tensor(torch.bfloat16, torch.ones(2)).dtype == torch.bfloat16
+    assert p.cast_fp_tensor(torch.bfloat16, torch.ones(2, dtype=torch.int32)).dtype == torch.int32
+    assert p.chunk(torch.arange(8), 0, 4, 1).tolist() == [2, 3]
+    assert p.tensor_to_numpy(torch.arange(3)).tolist() == [0, 1, 2]
+    assert p.apply_to_tensors(lambda t: t + 1, {"a": [torch.zeros(1), 3]}) == {"a": [torch.ones(1), 3]}
+    m = torch.nn.Sequential(torch.nn.Linear(2, 2))
+    found = p.search_parameter_by_name(m, "0.weight")
+    assert found[0] is m[0] and found[1] == "weight" and p.search_parameter_by_name(m, "0.nope") is None
+    new = torch.nn.Parameter(torch.zeros(2, 2))
+    assert p.update_parameter_by_name(m, found, new) and m[0].weight is new
+    assert dict(p.parameters_dict(m)).keys() == {"0.weight", "0.bias"} and len(list(p.get_cells_and_names(m))) == 2
+    assert p.get_param_type_size(new) == 4 and tuple(p.get_param_local_shape(new)) == (2, 2)
+    assert p.device_type() == "cuda" and p.get_device_handle() is torch.cuda
+    assert p.checkpoint is torch.utils.checkpoint.checkpoint
+    state = p.get_rng_state()
+    p.manual_seed(3)
+    p.set_rng_state(state)
+    assert torch.equal(p.get_rng_state(), state)
+    mb = p.micro_batch(2)
+    assert mb is not None
+    p.wait_grad_handle()                                     # nothing in flight: returns
+    with pytest.raises(ValueError):
+        p.tensor_type_cast(torch.ones(1), "not_a_dtype")
