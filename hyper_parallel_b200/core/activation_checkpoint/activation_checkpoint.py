@@ -134,10 +134,12 @@ def checkpoint(function: Callable, *args, swap_inputs: bool = False, policy_fn: 
 
 
 class CheckpointWrapper(nn.Module):
-    def __init__(self, module: nn.Module, policy_fn=None, swap_inputs: bool = False):
+    def __init__(self, module: nn.Module, policy_fn=None, swap_inputs: bool = False, checkpoint_fn=None,
+                 **checkpoint_fn_kwargs):
         super().__init__()
         self._checkpoint_wrapped_module = module
         self.policy_fn, self.swap_inputs = policy_fn, swap_inputs
+        self.checkpoint_fn, self.checkpoint_fn_kwargs = checkpoint_fn, checkpoint_fn_kwargs
         self._register_state_dict_hook(self._strip)
         self._register_load_state_dict_pre_hook(self._add)
 
@@ -157,9 +159,18 @@ class CheckpointWrapper(nn.Module):
                 state_dict[tag + k[len(prefix):]] = state_dict.pop(k)
 
     def forward(self, *args, **kwargs):
+        if self.checkpoint_fn is not None and self.checkpoint_fn is not checkpoint:
+            # a checkpoint function of the caller's (e.g. torch.utils.checkpoint.checkpoint with its own
+            # keyword arguments), as the reference's wrapper takes it
+            return self.checkpoint_fn(self._checkpoint_wrapped_module, *args, **self.checkpoint_fn_kwargs, **kwargs)
         return checkpoint(self._checkpoint_wrapped_module, *args, swap_inputs=self.swap_inputs,
                           policy_fn=self.policy_fn, **kwargs)
 
 
-def checkpoint_wrapper(module: nn.Module, policy_fn=None, swap_inputs: bool = False) -> CheckpointWrapper:
-    return CheckpointWrapper(module, policy_fn, swap_inputs)
+def checkpoint_wrapper(module: nn.Module, policy_fn=None, swap_inputs: bool = False, *, checkpoint_fn=None,
+                       **checkpoint_fn_kwargs) -> CheckpointWrapper:
+    """Wrap ``module`` so that its forward runs under activation checkpointing.  Either this package's
+    :func:`checkpoint` with ``policy_fn`` / ``swap_inputs``, or -- the reference's form
+    (core/activation_checkpoint/activation_checkpoint.py:60-79 there) -- ``checkpoint_fn`` with the keyword
+    arguments to hand to it."""
+    return CheckpointWrapper(module, policy_fn, swap_inputs, checkpoint_fn, **checkpoint_fn_kwargs)

@@ -246,25 +246,46 @@ def shard(model, sharding_plan, device_mesh: Optional[DeviceMesh] = None):
     return shard_module(model, device_mesh, plan)
 
 
-def parallelize_value_and_grad(fn: Callable, params=None, *, loss_layout: Optional[Layout] = None):
-    """Return ``f(*args) -> (loss, grads)`` that seeds the backward with ``1 / repeat_num``.
+def parallelize_value_and_grad(fn: Callable, weights=None, sens=None, *, params=None,
+                               loss_layout: Optional[Layout] = None):
+    """Return ``f(*args) -> (outputs, grads)`` that seeds the backward with ``1 / repeat_num``.
 
     A loss replicated on ``repeat_num`` ranks would be counted that many times by the
     gradient reductions; seeding with ``1 / repeat_num`` makes the summed gradients equal
     the single-process ones (hyper_parallel/core/shard/api.py:470-577 of the reference, there
-    a MindSpore ``GradOperation`` wrapper).
-    """
+    a MindSpore ``GradOperation`` wrapper with the same arguments).
+
+    ``weights`` (``params`` is the older spelling): the parameters to differentiate; without them
+    the gradients are accumulated into ``.grad`` and ``grads`` is ``None``.  ``sens``: when ``fn``
+    returns several outputs, one sensitivity per output (multiplied into the seed); without it only
+    the first output is differentiated."""
+    weights = params if weights is None else weights
+    if isinstance(weights, torch.Tensor):
+        weights = [weights]
+
     def wrapped(*args, **kwargs):
-        loss = fn(*args, **kwargs)
-        lay = loss.layout if isinstance(loss, DTensor) else loss_layout
-        rep = lay.repeat_num() if lay is not None else 1
-        local = loss.to_local() if isinstance(loss, DTensor) else loss
-        plist = list(params) if params is not None else None
-        seed = torch.full_like(local, 1.0 / rep)
-        if plist is None:
-            local.backward(seed)
-            return loss, None
-        targets = [p.to_local() if isinstance(p, DTensor) else p for p in plist]
-        grads = torch.autograd.grad(local, targets, grad_outputs=seed, allow_unused=True)
-        return loss, grads
+        out = fn(*args, **kwargs)
+        outs = list(out) if isinstance(out, (tuple, list)) else [out]
+        if sens is not None and len(sens) != len(outs):
+            raise ValueError(f"sens has {len(sens)} entries but fn returned {len(outs)} outputs")
+        locals_, seeds = [], []
+        for i, o in enumerate(outs):
+            if not isinstance(o, torch.Tensor):
+                continue
+            weight = (1.0 if i == 0 else 0.0) if sens is None else float(sens[i])
+            if weight == 0.0:
+                continue
+            lay = o.layout if isinstance(o, DTensor) else loss_layout
+            rep = lay.repeat_num() if lay is not None else 1
+            local = o.to_local() if isinstance(o, DTensor) else o
+            if local.requires_grad:
+                locals_.append(local)
+                seeds.append(torch.full_like(local, weight / rep))
+        if weights is None:
+            if locals_:
+                torch.autograd.backward(locals_, grad_tensors=seeds)
+            return out, None
+        targets = [p.to_local() if isinstance(p, DTensor) else p for p in weights]
+        grads = torch.autograd.grad(locals_, targets, grad_outputs=seeds, allow_unused=True)
+        return out, grads
     return wrapped

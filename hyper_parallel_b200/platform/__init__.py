@@ -201,8 +201,7 @@ class TorchPlatform:
     @staticmethod
     def ckpt_wrapper(module, checkpoint_fn=None, **kw):
         from ..core.activation_checkpoint import checkpoint_wrapper
-        return checkpoint_wrapper(module, checkpoint_fn=checkpoint_fn, **kw) if checkpoint_fn is not None \
-            else checkpoint_wrapper(module, **kw)
+        return checkpoint_wrapper(module, checkpoint_fn=checkpoint_fn, **kw)
 
     @staticmethod
     def create_selective_checkpoint_contexts(policy_fn_or_list, allow_cache_entry_mutation=False):

@@ -158,3 +158,23 @@ def test_swap_manager_manual_interface_by_group_name():
         mgr.launch_offload("no such group")
     mgr.reset()
     assert mgr.get_current_group_name() == ""
+
+
+def test_checkpoint_wrapper_with_a_checkpoint_function_of_the_callers():
+    import torch.utils.checkpoint as tuc
+    calls = []
+
+    def my_ckpt(fn, *args, use_reentrant=False, **kw):
+        calls.append(use_reentrant)
+        return tuc.checkpoint(fn, *args, use_reentrant=use_reentrant, **kw)
+
+    torch.manual_seed(0)
+    block = nn.Sequential(nn.Linear(8, 8), nn.GELU(), nn.Linear(8, 8))
+    ref = copy.deepcopy(block)
+    wrapped = checkpoint_wrapper(block, checkpoint_fn=my_ckpt, use_reentrant=False)
+    x = torch.randn(4, 8, requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+    wrapped(x).sum().backward()
+    ref(xr).sum().backward()
+    assert calls == [False] and torch.allclose(x.grad, xr.grad)
+    assert set(wrapped.state_dict()) == set(ref.state_dict())          # keys keep the inner names

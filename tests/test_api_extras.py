@@ -240,3 +240,21 @@ def test_platform_facade_offers_the_reference_method_names():
     p.wait_grad_handle()                                     # nothing in flight: returns
     with pytest.raises(ValueError):
         p.tensor_type_cast(torch.ones(1), "not_a_dtype")
+
+
+def test_value_and_grad_with_weights_and_sensitivities():
+    """The reference's arguments: ``(fn, weights, sens)``; several outputs with and without ``sens``."""
+    from hyper_parallel_b200 import parallelize_value_and_grad
+    w = torch.nn.Parameter(torch.tensor([1.0, 2.0]))
+    x = torch.tensor([3.0, 4.0])
+
+    def two(x):
+        return (w * x).sum(), (w * w * x).sum()
+    (o1, o2), g = parallelize_value_and_grad(two, [w])(x)
+    assert (o1.item(), o2.item()) == (11.0, 19.0) and g[0].tolist() == [3.0, 4.0]      # the first output only
+    _, g = parallelize_value_and_grad(two, w, sens=[1.0, 0.5])(x)
+    assert g[0].tolist() == [6.0, 12.0]
+    with pytest.raises(ValueError):
+        parallelize_value_and_grad(two, [w], sens=[1.0])(x)
+    out, none = parallelize_value_and_grad(lambda x: (w * x).sum())(x)                  # no weights: into .grad
+    assert none is None and w.grad.tolist() == [3.0, 4.0]
