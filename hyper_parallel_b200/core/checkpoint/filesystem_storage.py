@@ -67,7 +67,11 @@ class FileSystemWriter(StorageWriter):
         tensors: Dict[str, torch.Tensor] = {}
         tfile = f"_rank{self.rank}_.safetensors"
         for it in plan.items:
-            data = planner.resolve_data(it)
+            attached = getattr(it, "bytes_io_data", None) if it.type == WriteItemType.BYTE_IO else None
+            if attached is not None:
+                data = attached if isinstance(attached, bytes) else pickle.dumps(attached)
+            else:
+                data = planner.resolve_data(it)
             if it.type == WriteItemType.BYTE_IO:
                 rel = f"{_safe_name(it.index.fqn)}_rank{self.rank}.bytes"
                 _atomic_write(os.path.join(self.path, rel), lambda f, d=data: f.write(d))

@@ -31,6 +31,9 @@ class WriteItem:
     index: MetadataIndex
     type: WriteItemType
     tensor_data: Optional[TensorWriteData] = None
+    # bytes (or any picklable object) a planner attaches to a BYTE_IO item itself, as the reference's
+    # planner does; without it the writer asks ``planner.resolve_data``
+    bytes_io_data: Any = field(default=None, compare=False, hash=False)
 
 
 @dataclass
