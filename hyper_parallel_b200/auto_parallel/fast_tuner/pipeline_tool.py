@@ -88,7 +88,19 @@ def main(argv=None) -> int:
     ap.add_argument("--mbs", type=int, nargs="*", help="micro-batch sizes to try (default 1 2 4)")
     ap.add_argument("--topn", type=int, default=20)
     ap.add_argument("--select_recompute", action="store_true")
+    ap.add_argument("--profile_data_dir", help="folder of a profiling run; its first *.records.jsonl is the profile "
+                                               "when --parser_result is not given")
+    # accepted for command lines written for the reference's tool; they have no effect here (no external
+    # trainer is driven, the balancer is the built-in one, the re-check is the schedule simulator)
+    for flag in ("--files_dir", "--mindformers_dir", "--mindspeed_path", "--solver_name", "--env_json",
+                 "--register_path", "--parallel_num", "--dryrun", "--check"):
+        ap.add_argument(flag, help=argparse.SUPPRESS)
     ns = ap.parse_args(argv)
+    if not ns.parser_result and ns.profile_data_dir:
+        import glob
+        import os
+        found = sorted(glob.glob(os.path.join(ns.profile_data_dir, "*.records.jsonl")))
+        ns.parser_result = found[0] if found else None
     cfg = TunerConfig.from_json(ns.config) if ns.config else TunerConfig()
     for k in ("toml_path", "yaml_path", "shell_path", "model_json", "rank_num", "gbs", "gpus_per_node", "output_path"):
         if getattr(ns, k) is not None:
