@@ -1,21 +1,21 @@
-"""The single (torch) platform object.
+"""The single (_torch) platform object.
 
-The reference selects a MindSpore or torch backend at import time
-(hyper_parallel/platform/platform.py:63-90); here torch is the only backend, and
+The reference selects a MindSpore or _torch backend at import time
+(hyper_parallel/platform/platform.py:63-90); here _torch is the only backend, and
 ``get_platform()`` returns a small facade over :mod:`hyper_parallel_b200.collectives.cc`
 for code that was written against the reference's ``platform`` object.
 """
 from __future__ import annotations
 
-import torch
+import torch as _torch      # not ``torch``: the sub-package ``platform.torch`` takes that name in this namespace
 
 from ..collectives import cc
 
 
 class TorchPlatform:
-    Tensor = torch.Tensor
-    Module = torch.nn.Module
-    Parameter = torch.nn.Parameter
+    Tensor = _torch.Tensor
+    Module = _torch.nn.Module
+    Parameter = _torch.nn.Parameter
 
     @property
     def DTensorBase(self):
@@ -53,38 +53,38 @@ class TorchPlatform:
 
     @staticmethod
     def device():
-        if torch.cuda.is_available():
-            return torch.device("cuda", torch.cuda.current_device())
-        return torch.device("cpu")
+        if _torch.cuda.is_available():
+            return _torch.device("cuda", _torch.cuda.current_device())
+        return _torch.device("cpu")
 
     # tensors -----------------------------------------------------------------------
-    ones = staticmethod(lambda size, dtype=None: torch.ones(size, dtype=dtype))
-    zeros = staticmethod(lambda size, dtype=None: torch.zeros(size, dtype=dtype))
-    full = staticmethod(lambda size, fill_value, dtype=None: torch.full(size, fill_value, dtype=dtype))
-    empty = staticmethod(lambda size, dtype=None: torch.empty(size, dtype=dtype))
-    full_like = staticmethod(lambda tensor, fill_value, dtype=None: torch.full_like(tensor, fill_value, dtype=dtype))
+    ones = staticmethod(lambda size, dtype=None: _torch.ones(size, dtype=dtype))
+    zeros = staticmethod(lambda size, dtype=None: _torch.zeros(size, dtype=dtype))
+    full = staticmethod(lambda size, fill_value, dtype=None: _torch.full(size, fill_value, dtype=dtype))
+    empty = staticmethod(lambda size, dtype=None: _torch.empty(size, dtype=dtype))
+    full_like = staticmethod(lambda tensor, fill_value, dtype=None: _torch.full_like(tensor, fill_value, dtype=dtype))
     empty_like = staticmethod(lambda tensor, *, dtype=None, device=None, pin_memory=False:
-                              torch.empty_like(tensor, dtype=dtype, device=device, pin_memory=pin_memory))
-    new_tensor = staticmethod(lambda shape, dtype, device: torch.empty(size=shape, dtype=dtype, device=device))
-    new_zero_parameter = staticmethod(lambda shape, dtype, requires_grad, device: torch.nn.Parameter(
-        torch.zeros(shape, dtype=dtype, device=device), requires_grad=requires_grad))
-    chunk = staticmethod(lambda data, split_dim, split_size, index: torch.chunk(data, split_size, dim=split_dim)[index])
+                              _torch.empty_like(tensor, dtype=dtype, device=device, pin_memory=pin_memory))
+    new_tensor = staticmethod(lambda shape, dtype, device: _torch.empty(size=shape, dtype=dtype, device=device))
+    new_zero_parameter = staticmethod(lambda shape, dtype, requires_grad, device: _torch.nn.Parameter(
+        _torch.zeros(shape, dtype=dtype, device=device), requires_grad=requires_grad))
+    chunk = staticmethod(lambda data, split_dim, split_size, index: _torch.chunk(data, split_size, dim=split_dim)[index])
     tensor_to_numpy = staticmethod(lambda tensor: tensor.detach().cpu().numpy())
-    no_grad = staticmethod(torch.no_grad)
-    manual_seed = staticmethod(torch.manual_seed)
+    no_grad = staticmethod(_torch.no_grad)
+    manual_seed = staticmethod(_torch.manual_seed)
 
     @staticmethod
     def tensor_type_cast(input_data, cast_type):
         """Cast to a dtype given by name (``"float32"``, ``"bfloat16"``, ...) or as a ``torch.dtype``."""
-        dtype = getattr(torch, cast_type, None) if isinstance(cast_type, str) else cast_type
-        if not isinstance(dtype, torch.dtype):
+        dtype = getattr(_torch, cast_type, None) if isinstance(cast_type, str) else cast_type
+        if not isinstance(dtype, _torch.dtype):
             raise ValueError(f"unknown dtype {cast_type!r}")
         return input_data.to(dtype)
 
     @staticmethod
     def cast_fp_tensor(dtype, x):
         """``x`` cast to ``dtype`` when it is a floating-point tensor of another dtype, else ``x``."""
-        if isinstance(x, torch.Tensor) and x.is_floating_point() and dtype is not None and x.dtype != dtype:
+        if isinstance(x, _torch.Tensor) and x.is_floating_point() and dtype is not None and x.dtype != dtype:
             return x.to(dtype)
         return x
 
@@ -96,49 +96,49 @@ class TorchPlatform:
 
     @staticmethod
     def tree_map(fn, tree):
-        return torch.utils._pytree.tree_map(fn, tree)
+        return _torch.utils._pytree.tree_map(fn, tree)
 
     @classmethod
     def apply_to_tensors(cls, fn, container):
         """``fn`` applied to every tensor inside nested lists / tuples / dicts; the rest is kept."""
-        return cls.tree_map(lambda x: fn(x) if isinstance(x, torch.Tensor) else x, container)
+        return cls.tree_map(lambda x: fn(x) if isinstance(x, _torch.Tensor) else x, container)
 
     # devices, streams, generators ---------------------------------------------------------
     @staticmethod
     def get_device_handle():
         """``torch.cuda`` (the module that owns devices, streams, events and generators)."""
-        return torch.cuda
+        return _torch.cuda
 
-    device_count = staticmethod(lambda device_handle=None: (device_handle or torch.cuda).device_count())
+    device_count = staticmethod(lambda device_handle=None: (device_handle or _torch.cuda).device_count())
     device_type = staticmethod(lambda: "cuda")
-    new_stream = staticmethod(lambda: torch.cuda.Stream())
-    new_event = staticmethod(lambda: torch.cuda.Event())
-    get_current_stream = staticmethod(lambda: torch.cuda.current_stream())
-    get_stream_context = staticmethod(lambda: torch.cuda.stream)
+    new_stream = staticmethod(lambda: _torch.cuda.Stream())
+    new_event = staticmethod(lambda: _torch.cuda.Event())
+    get_current_stream = staticmethod(lambda: _torch.cuda.current_stream())
+    get_stream_context = staticmethod(lambda: _torch.cuda.stream)
 
     @staticmethod
     def get_rng_state(device=None, device_handle=None):
         if device_handle is None:
-            return torch.get_rng_state()
+            return _torch.get_rng_state()
         return device_handle.get_rng_state() if device is None else device_handle.get_rng_state(device)
 
     @staticmethod
     def set_rng_state(state, device=None, device_handle=None):
         if device_handle is None:
-            return torch.set_rng_state(state)
+            return _torch.set_rng_state(state)
         return device_handle.set_rng_state(state) if device is None else device_handle.set_rng_state(state, device)
 
     # point-to-point and object collectives -------------------------------------------------------
     @staticmethod
     def get_global_rank(group, group_rank):
-        return torch.distributed.get_global_rank(group, group_rank)
+        return _torch.distributed.get_global_rank(group, group_rank)
 
-    isend = staticmethod(lambda tensor, dst=None, group=None, tag=0: torch.distributed.isend(tensor, dst, group, tag))
-    irecv = staticmethod(lambda tensor, src=None, group=None, tag=0: torch.distributed.irecv(tensor, src, group, tag))
+    isend = staticmethod(lambda tensor, dst=None, group=None, tag=0: _torch.distributed.isend(tensor, dst, group, tag))
+    irecv = staticmethod(lambda tensor, src=None, group=None, tag=0: _torch.distributed.irecv(tensor, src, group, tag))
     send_object_list = staticmethod(lambda obj_list, dst=None, group=None:
-                                    torch.distributed.send_object_list(obj_list, dst, group))
+                                    _torch.distributed.send_object_list(obj_list, dst, group))
     recv_object_list = staticmethod(lambda obj_list, src=None, group=None:
-                                    torch.distributed.recv_object_list(obj_list, src, group))
+                                    _torch.distributed.recv_object_list(obj_list, src, group))
 
     # modules and parameters -------------------------------------------------------------------
     get_cells_and_names = staticmethod(lambda cell: cell.named_modules())
@@ -184,19 +184,19 @@ class TorchPlatform:
         from ..core.dtensor import DTensor, distribute_tensor
         if isinstance(param, DTensor):
             return param
-        return torch.nn.Parameter(distribute_tensor(param.detach(), layout), requires_grad=param.requires_grad)
+        return _torch.nn.Parameter(distribute_tensor(param.detach(), layout), requires_grad=param.requires_grad)
 
     # checkpoints, activation checkpointing, pipelines, gradient handles ------------------------------------
-    save_checkpoint = staticmethod(lambda cell, file_path: torch.save(obj=cell, f=file_path))
-    load_checkpoint = staticmethod(lambda file_path: torch.load(f=file_path, weights_only=False))
+    save_checkpoint = staticmethod(lambda cell, file_path: _torch.save(obj=cell, f=file_path))
+    load_checkpoint = staticmethod(lambda file_path: _torch.load(f=file_path, weights_only=False))
 
     @property
     def checkpoint(self):
-        return torch.utils.checkpoint.checkpoint
+        return _torch.utils.checkpoint.checkpoint
 
     @property
     def noop_context_fn(self):
-        return torch.utils.checkpoint.noop_context_fn
+        return _torch.utils.checkpoint.noop_context_fn
 
     @staticmethod
     def ckpt_wrapper(module, checkpoint_fn=None, **kw):

@@ -213,7 +213,8 @@ def test_reference_compat_runner_rewrites_and_runs_a_reference_style_test(tmp_pa
 
 def test_platform_facade_offers_the_reference_method_names():
     """Code written against ``get_platform()`` of the reference finds the same helpers here."""
-    from hyper_parallel_b200.platform import get_platform
+    import hyper_parallel_b200.platform.torch.fully_shard.utils  # noqa: F401  (binds ``platform.torch``: must not
+    from hyper_parallel_b200.platform import get_platform        # hide the torch module from the facade)
     p = get_platform()
     assert p.ones((2,)).tolist() == [1.0, 1.0] and p.full((1,), 3.0).item() == 3.0 and p.empty((2, 3)).shape == (2, 3)
     assert p.tensor_type_cast(torch.ones(2), "float16").dtype == torch.float16
