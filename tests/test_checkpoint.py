@@ -80,6 +80,28 @@ def test_save_8_ranks_4x2_then_load_on_4_and_on_8_with_another_mesh(tmp_path):
     run_distributed(_load_worker, 8, path, (2, 4))
 
 
+def _subset_load_worker(rank, world, path):
+    """Ranks 0-3 of an 8-rank job load onto a 2 x 2 mesh of their own; ranks 4-7 do not take part."""
+    from hyper_parallel_b200 import Layout, distribute_tensor
+    from hyper_parallel_b200.core import checkpoint as ckpt
+    if rank >= 4:
+        return
+    lay = Layout((2, 2), ("dp", "tp"), [0, 1, 2, 3])
+    sd = {k: distribute_tensor(torch.zeros(*shape), lay(*spec)) for k, (shape, spec) in SPECS.items()}
+    sd["plain"] = torch.zeros(5, 3)
+    sd["nested"] = {"step": 0, "lr": 0.0, "t": torch.zeros(4)}
+    ckpt.load(sd, checkpoint_id=path)
+    for k, (shape, _) in SPECS.items():
+        assert torch.allclose(sd[k].full_tensor(), _full(k, shape), atol=1e-5), k
+    assert sd["nested"]["step"] == 7
+
+
+def test_a_subset_of_the_ranks_loads_what_all_ranks_saved(tmp_path):
+    path = str(tmp_path / "ckpt_subset")
+    run_distributed(_save_worker, 8, path, (4, 2), True)
+    run_distributed(_subset_load_worker, 8, path)
+
+
 def test_rank_local_metadata_without_collectives(tmp_path):
     path = str(tmp_path / "ckpt_local")
     run_distributed(_save_worker, 2, path, (1, 2), False)
