@@ -73,8 +73,9 @@ def _materialise(root: nn.Module, p: nn.Parameter, value: torch.Tensor) -> None:
 
 def init_parameters(module: nn.Module, stage_index: int = 0, *, device=None,
                     init_fn: Optional[Callable[[nn.Module], None]] = None,
-                    seed: Optional[int] = None) -> None:
-    """Materialise and initialise the (sharded) parameters of ``module`` in place.
+                    seed: Optional[int] = None) -> nn.Module:
+    """Materialise and initialise the (sharded) parameters of ``module`` in place; returns ``module``
+    (the reference's README writes ``model = init_parameters(model)``).
 
     Args:
         stage_index: pipeline stage of this module; added to ``seed`` so that stages draw
@@ -128,3 +129,4 @@ def init_parameters(module: nn.Module, stage_index: int = 0, *, device=None,
         if sch is not None:
             sch.hsdp_state.rebuild_param_buffers()
             sch._bind_symm_buffers()
+    return module

@@ -35,12 +35,18 @@ class ReduceExtDistributedOpBase(DistributedOp):
     partial_op = "sum"
 
     def infer_layout(self, layouts, extra_args):
-        self._check_partial_inputs(layouts)
         x = layouts[0]
         nd = len(x.dim_axes)
         dims, keepdim, _ = _parse_dim_keepdim(extra_args, nd)
         op = _PARTIAL_OF.get(self.op_name, self.partial_op)
-        partial = [None] * x.mesh.ndim
+        # sum and mean are linear: a pending sum (or average) of the input stays pending on the result
+        # -- e.g. the sum of a row-parallel product.  Every other reduction needs the reduced input.
+        # (The reference's rule builds the result's layout afresh and loses the input's Partial status.)
+        if op in ("sum", "avg") and all(p in (None, "sum", "avg") for p in x.partial):
+            partial = list(x.partial)
+        else:
+            self._check_partial_inputs(layouts)
+            partial = [None] * x.mesh.ndim
         out_axes = []
         for d, axes in enumerate(x.dim_axes):
             if d in dims:

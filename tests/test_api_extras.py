@@ -259,3 +259,38 @@ def test_value_and_grad_with_weights_and_sensitivities():
         parallelize_value_and_grad(two, [w], sens=[1.0])(x)
     out, none = parallelize_value_and_grad(lambda x: (w * x).sum())(x)                  # no weights: into .grad
     assert none is None and w.grad.tolist() == [3.0, 4.0]
+
+
+def _readme_worker(rank, world):
+    """The tensor-parallel example of the reference's README, line for line (torch meta device in place of
+    MindSpore's ``no_init_parameters``): dict plan for ``shard``, ``hsdp`` on top, ``model = init_parameters(model)``,
+    ``DTensor.from_local(local, layout)``."""
+    from hyper_parallel_b200 import DTensor, Layout, hsdp, init_parameters, shard
+    layout = Layout((2, 2), ("dp", "mp"))
+    x_layout, w_layout, out_layout = layout("dp", "mp"), layout("mp", "None"), layout()
+
+    class SimpleModel(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.ones(8, 4))
+
+        def reset_parameters(self):
+            torch.nn.init.ones_(self.weight)
+
+        def forward(self, x):
+            return torch.sum(torch.matmul(x, self.weight))
+
+    with torch.device("meta"):
+        model = SimpleModel()
+    plan = {"forward": {"input": (x_layout,), "output": (out_layout,)}, "parameter": {"weight": w_layout}}
+    model = shard(model, plan)
+    model = hsdp(model, shard_size=2, threshold=0)
+    model = init_parameters(model)
+    assert model is not None
+    out = model(DTensor.from_local(torch.ones(4, 4), x_layout))
+    assert isinstance(out, DTensor) and not out.layout.is_partial()
+    assert out.to_local().item() == 256.0                      # 8 x 8 ones times 8 x 4 ones, summed
+
+
+def test_reference_readme_tensor_parallel_example():
+    run_distributed(_readme_worker, 4)

@@ -202,6 +202,21 @@ def max_of_two_tensors_is_elementwise(c):
 
 
 @case
+def sum_and_mean_of_a_pending_sum_stay_pending(c):
+    """The product of a row-parallel matmul is Partial(sum); sum and mean are linear and keep it."""
+    prod = torch.matmul(c.d(c.X, "dp", "mp"), c.d(c.W2, "mp", "None"))
+    assert prod.layout.is_partial()
+    ref = c.X @ c.W2
+    s = prod.sum()
+    assert s.layout.is_partial()
+    c.same(s, ref.sum(), atol=1e-4)
+    c.same(prod.sum(1), ref.sum(1), atol=1e-4)
+    c.same(prod.mean(0, keepdim=True), ref.mean(0, keepdim=True), atol=1e-5)
+    _raises(ValueError, lambda: prod.prod())
+    _raises(ValueError, lambda: prod.amax(0))
+
+
+@case
 def max_all(c):
     c.same(c.d(c.X, "dp", "mp").max(), c.X.max())
 
